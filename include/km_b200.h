@@ -1,0 +1,199 @@
+/*
+ * km_b200 -- C ABI of the B200 (sm_100a) kernel-matmul hot path.
+ *
+ * One shared library, plain pointers and sizes, no framework types.  Every entry point is the
+ * drop-in for one native op of the reference project Turakar/kernel-matmul (one pybind11
+ * module per op there); the reference interface it replaces is cited above each declaration
+ * (path within the reference project : lines).
+ *
+ * Conventions shared by all entry points
+ *  - All data pointers are DEVICE pointers on the current CUDA device.  Floats are fp32,
+ *    ranges and indices are int32 (the reference's dtypes, native/common/entrypoint.h:3-14).
+ *  - Tensors are described by `km_view`: a base pointer plus ELEMENT strides (int64, so that
+ *    batch x rows x columns may exceed 2^31 elements; the reference's accessors use int32
+ *    offsets, native/common/accessor.cuh:13-24).  Up to KM_MAX_BATCH_DIMS leading batch
+ *    dimensions, shared by all arguments of a call and given once in `km_batch`; a batch
+ *    stride of 0 broadcasts the same data to every batch (the reference receives such views
+ *    from `Tensor.expand`, kernel_matmul/linear_operator.py:170-183).
+ *  - Inputs are borrowed and never written.  Outputs and workspaces are caller-allocated; the
+ *    library never allocates device memory and holds no device state.
+ *  - Launches are asynchronous on the `stream` argument (a cudaStream_t passed as void*).
+ *    The band-construction calls do not synchronise either.
+ *  - Return value: KM_OK or an error code; km_last_error() gives a message for the calling
+ *    thread.  Nothing traps or aborts.  Arguments are validated before anything is launched.
+ *  - Row blocks are KM_BLOCK_SIZE = 128 rows (kernel_matmul/__init__.py:1).  Row block r of
+ *    batch b sees columns [start[b,r], end[b,r]) only; every other entry of K is exactly 0.
+ *    Bands are clamped to [0, n].
+ */
+#ifndef KM_B200_H
+#define KM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define KM_API __attribute__((visibility("default")))
+#else
+#define KM_API
+#endif
+
+#define KM_BLOCK_SIZE 128
+#define KM_MAX_BATCH_DIMS 4
+#define KM_MAX_PARAMS 4
+
+/* status codes */
+#define KM_OK 0
+#define KM_ERR_INVALID_ARGUMENT 1
+#define KM_ERR_UNSUPPORTED 2
+#define KM_ERR_WORKSPACE 3
+#define KM_ERR_CUDA 4
+
+/* kernel types; parameter order as the reference's callers stack them
+ * (native/common/kernel_function.cuh:3-9, kernel_matmul/gpytorch/rbf.py:78-79,
+ *  spectral.py:102-103, locally_periodic.py:130-134) */
+#define KM_KERNEL_RBF 0              /* theta = [lengthscale, outputscale]                  */
+#define KM_KERNEL_SPECTRAL 1         /* theta = [lengthscale, frequency, outputscale]       */
+#define KM_KERNEL_LOCALLY_PERIODIC 2 /* theta = [l_rbf, l_periodic, period, outputscale]    */
+
+typedef struct km_batch {
+    int32_t ndim;                    /* 0 .. KM_MAX_BATCH_DIMS */
+    int64_t size[KM_MAX_BATCH_DIMS]; /* unused entries ignored */
+} km_batch;
+
+typedef struct km_view {
+    void *data;                              /* device pointer                              */
+    int64_t batch_stride[KM_MAX_BATCH_DIMS]; /* element strides of the batch dims (0 = broadcast) */
+    int64_t stride[2];                       /* element strides of the trailing dims        */
+} km_view;
+
+KM_API const char *km_last_error(void);
+KM_API int km_num_params(int kernel_type); /* 2 / 3 / 4, or -1 */
+KM_API const char *km_version(void);
+
+/* ---------------------------------------------------------------------------------------
+ * out[b, i, :] = sum_{j in band(b, i/128)} kappa(x1[b,i], x2[b,j]; theta[b]) * rhs[b, j, :]
+ * Replaces matmul.call(x1, x2, rhs, params, start, end) (native/matmul/matmul.cpp:6-17,
+ * native/matmul/matmul.cu:160-203).
+ *   x1 (B.., m)  x2 (B.., n)  rhs (B.., n, k)  params (B.., P)  start,end (B.., ceil(m/128)) i32
+ *   out (B.., m, k), every element written.
+ * Single-stride views (x1, x2, params, start, end) use stride[0].
+ * ------------------------------------------------------------------------------------- */
+KM_API int km_matmul_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
+                  const km_view *x1, const km_view *x2, const km_view *rhs,
+                  const km_view *params, const km_view *start, const km_view *end,
+                  const km_view *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * grad[b, q] = d/d theta_q  sum_{i, j in band, c} left[b,i,c] * kappa(x1[b,i], x2[b,j]) * right[b,j,c]
+ * Replaces bilinear_derivative.call(x1, x2, left, right, params, start, end)
+ * (native/bilinear_derivative/bilinear_derivative.cpp:6-21, .cu:138-183) and, with
+ * left = out_grad and right = rhs, matmul_bwd.call(x1, x2, rhs, params, start, end, out_grad)
+ * (native/matmul_bwd/matmul_bwd.cpp:6-19, matmul_bwd.cu:182-221): both are this contraction.
+ *   left (B.., m, k)  right (B.., n, k)  grad (B.., P) fp32, every element written.
+ * workspace: km_grad_workspace_bytes(...) bytes of device memory, 256-byte aligned, contents
+ * irrelevant on entry; per-row-block partial sums are written there and reduced in a fixed
+ * order, so results are deterministic.
+ * ------------------------------------------------------------------------------------- */
+KM_API size_t km_grad_workspace_bytes(int kernel_type, const km_batch *batch, int64_t m);
+
+KM_API int km_bilinear_derivative_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
+                               int64_t k, const km_view *x1, const km_view *x2,
+                               const km_view *left, const km_view *right, const km_view *params,
+                               const km_view *start, const km_view *end, const km_view *grad,
+                               void *workspace, size_t workspace_bytes, void *stream);
+
+KM_API int km_matmul_bwd_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
+                      const km_view *x1, const km_view *x2, const km_view *rhs,
+                      const km_view *params, const km_view *start, const km_view *end,
+                      const km_view *out_grad, const km_view *grad, void *workspace,
+                      size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Masked dense K: out (B.., m, n), exact zeros outside the band; every element written (no
+ * separate zero fill).  Replaces dense.call(x1, x2, params, start, end)
+ * (native/dense/dense.cpp:6-17, native/dense/dense.cu:73-98).
+ * ------------------------------------------------------------------------------------- */
+KM_API int km_dense_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
+                 const km_view *x1, const km_view *x2, const km_view *params,
+                 const km_view *start, const km_view *end, const km_view *out, void *stream);
+
+/* grad[b, q] = d/d theta_q sum_{i, j in band} out_grad[b,i,j] * kappa.  Replaces
+ * dense_bwd.call(x1, x2, params, start, end, out_grad) (native/dense_bwd/dense_bwd.cpp:6-17,
+ * dense_bwd.cu:86-116).  Workspace as for km_bilinear_derivative_f32. */
+KM_API int km_dense_bwd_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
+                     const km_view *x1, const km_view *x2, const km_view *params,
+                     const km_view *start, const km_view *end, const km_view *out_grad,
+                     const km_view *grad, void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Gather: out[l] = K[bidx_0[l], .., row[l], col[l]] if the column lies in the band of the
+ * row's block, else 0; every element written.  Replaces
+ * index.call(x1, x2, params, start, end, batch_indices, row_index, col_index)
+ * (native/index/index.cpp:6-24, native/index/index.cu:69-101).
+ *   batch_indices: batch->ndim device pointers to int32 arrays of L entries (contiguous);
+ *   row, col: int32[L] contiguous; out: float[L].  The index tensors' own leading shape is
+ *   flattened by the caller (L = number of lookups).
+ * ------------------------------------------------------------------------------------- */
+KM_API int km_index_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t L,
+                 const km_view *x1, const km_view *x2, const km_view *params,
+                 const km_view *start, const km_view *end,
+                 const int32_t *const *batch_indices, const int32_t *row, const int32_t *col,
+                 float *out, void *stream);
+
+/* grad[b, q] = d/d theta_q sum_l [batch(l) == b] out_grad[l] * K[b, row[l], col[l]].  Replaces
+ * index_bwd.call(..., out_grad) (native/index_bwd/index_bwd.cpp:6-27, index_bwd.cu:65-112).
+ * grad (B.., P) every element written.  workspace: km_index_bwd_workspace_bytes(...) bytes. */
+KM_API size_t km_index_bwd_workspace_bytes(int kernel_type, const km_batch *batch);
+
+KM_API int km_index_bwd_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t L,
+                     const km_view *x1, const km_view *x2, const km_view *params,
+                     const km_view *start, const km_view *end,
+                     const int32_t *const *batch_indices, const int32_t *row,
+                     const int32_t *col, const float *out_grad, const km_view *grad,
+                     void *workspace, size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Band construction on the device (the reference runs these on one CPU thread after a
+ * device-to-host copy, native/ranges/ranges.cpp:8-150).  x1 (B, m), x2 (B, n) contiguous fp32;
+ * start, end (B, ceil(m/block)) contiguous int32, every element written.  Results are
+ * bit-identical to the reference's sequential scans for any input: non-decreasing x2 (the
+ * case every caller produces) takes a parallel search, anything else a sequential scan on the
+ * device.  `flags` is a device int32[B] scratch (contents irrelevant on entry).
+ * ------------------------------------------------------------------------------------- */
+
+/* ranges.make_ranges(x1, x2, cutoff, block_size, align)  (native/ranges/ranges.cpp:8-62) */
+KM_API int km_make_ranges_f32(int64_t B, int64_t m, int64_t n, const float *x1, const float *x2,
+                       float cutoff, int32_t block_size, int32_t align, int32_t *start,
+                       int32_t *end, int32_t *flags, void *stream);
+
+/* ranges.make_ranges_symmetric(x, cutoff, block_size)  (native/ranges/ranges.cpp:64-101) */
+KM_API int km_make_ranges_symmetric_f32(int64_t B, int64_t n, const float *x, float cutoff,
+                                 int32_t block_size, int32_t *start, int32_t *end,
+                                 int32_t *flags, void *stream);
+
+/* ranges.transpose_ranges(start, end, x1_size, x2_size, block_size)
+ * (native/ranges/ranges.cpp:103-150).  start, end (B, R); start_t, end_t (B, ceil(x2_size/block)).
+ * The caller checks block alignment (kernel_matmul/ranges.py:110-113). */
+KM_API int km_transpose_ranges_i32(int64_t B, int64_t R, const int32_t *start, const int32_t *end,
+                            int64_t x1_size, int64_t x2_size, int32_t block_size,
+                            int32_t *start_t, int32_t *end_t, void *stream);
+
+/* Visited entries sum_b sum_r rows(r) * (end - start) (bands clamped), written to *count
+ * (device int64).  No reference counterpart; used for throughput accounting. */
+KM_API int km_count_entries(const km_batch *batch, int64_t m, int64_t n, const km_view *start,
+                     const km_view *end, int64_t *count, void *stream);
+
+/* FP32-pipe calibration: runs `iters` dependent-chain-free FFMA rounds on every SM and writes a
+ * checksum to *sink (device float, may be NULL).  flops = 2 * threads * iters * 64 are returned
+ * in *flops_out (host).  No reference counterpart; bench.py times it to obtain the measured
+ * FP32 FMA peak the roofline fractions are quoted against. */
+KM_API int km_probe_fp32_peak(int64_t iters, float *sink, double *flops_out, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* KM_B200_H */

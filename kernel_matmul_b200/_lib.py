@@ -1,0 +1,97 @@
+"""ctypes binding of ``libkm_b200.so`` (declarations in ``include/km_b200.h``).
+
+There is no fallback: if the library is missing, importing this module raises, and every op
+of the package raises with it.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+KM_MAX_BATCH_DIMS = 4
+KM_MAX_PARAMS = 4
+KM_OK = 0
+
+KERNEL_TYPES = {"rbf": 0, "spectral": 1, "locally_periodic": 2}
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libkm_b200.so")
+
+
+class KmBatch(ctypes.Structure):
+    _fields_ = [("ndim", ctypes.c_int32), ("size", ctypes.c_int64 * KM_MAX_BATCH_DIMS)]
+
+
+class KmView(ctypes.Structure):
+    _fields_ = [
+        ("data", ctypes.c_void_p),
+        ("batch_stride", ctypes.c_int64 * KM_MAX_BATCH_DIMS),
+        ("stride", ctypes.c_int64 * 2),
+    ]
+
+
+class KmError(RuntimeError):
+    """An entry point of libkm_b200 returned a non-zero status."""
+
+
+def _load() -> ctypes.CDLL:
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} not found: build it with `python -m kernel_matmul_b200.build` "
+            "(nvcc, sm_100a). There is no CPU or PyTorch fallback."
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i32, i64, sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t
+    bp, wp = ctypes.POINTER(KmBatch), ctypes.POINTER(KmView)
+    lib.km_last_error.restype = ctypes.c_char_p
+    lib.km_last_error.argtypes = []
+    lib.km_version.restype = ctypes.c_char_p
+    lib.km_version.argtypes = []
+    lib.km_num_params.restype = ctypes.c_int
+    lib.km_num_params.argtypes = [ctypes.c_int]
+    lib.km_matmul_f32.restype = ctypes.c_int
+    lib.km_matmul_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, vp]
+    lib.km_grad_workspace_bytes.restype = sz
+    lib.km_grad_workspace_bytes.argtypes = [ctypes.c_int, bp, i64]
+    lib.km_bilinear_derivative_f32.restype = ctypes.c_int
+    lib.km_bilinear_derivative_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, wp, vp, sz, vp]
+    lib.km_matmul_bwd_f32.restype = ctypes.c_int
+    lib.km_matmul_bwd_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, wp, vp, sz, vp]
+    lib.km_dense_f32.restype = ctypes.c_int
+    lib.km_dense_f32.argtypes = [ctypes.c_int, bp, i64, i64, wp, wp, wp, wp, wp, wp, vp]
+    lib.km_dense_bwd_f32.restype = ctypes.c_int
+    lib.km_dense_bwd_f32.argtypes = [ctypes.c_int, bp, i64, i64, wp, wp, wp, wp, wp, wp, wp, vp, sz, vp]
+    pp = ctypes.POINTER(ctypes.c_void_p)
+    lib.km_index_f32.restype = ctypes.c_int
+    lib.km_index_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, pp, vp, vp, vp, vp]
+    lib.km_index_bwd_workspace_bytes.restype = sz
+    lib.km_index_bwd_workspace_bytes.argtypes = [ctypes.c_int, bp]
+    lib.km_index_bwd_f32.restype = ctypes.c_int
+    lib.km_index_bwd_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, pp, vp, vp, vp, wp, vp, sz, vp]
+    lib.km_make_ranges_f32.restype = ctypes.c_int
+    lib.km_make_ranges_f32.argtypes = [i64, i64, i64, vp, vp, ctypes.c_float, i32, i32, vp, vp, vp, vp]
+    lib.km_make_ranges_symmetric_f32.restype = ctypes.c_int
+    lib.km_make_ranges_symmetric_f32.argtypes = [i64, i64, vp, ctypes.c_float, i32, vp, vp, vp, vp]
+    lib.km_transpose_ranges_i32.restype = ctypes.c_int
+    lib.km_transpose_ranges_i32.argtypes = [i64, i64, vp, vp, i64, i64, i32, vp, vp, vp]
+    lib.km_count_entries.restype = ctypes.c_int
+    lib.km_count_entries.argtypes = [bp, i64, i64, wp, wp, vp, vp]
+    lib.km_probe_fp32_peak.restype = ctypes.c_int
+    lib.km_probe_fp32_peak.argtypes = [i64, vp, ctypes.POINTER(ctypes.c_double), vp]
+    return lib
+
+
+lib = _load()
+
+EXPORTED = [
+    "km_last_error", "km_version", "km_num_params", "km_matmul_f32", "km_grad_workspace_bytes",
+    "km_bilinear_derivative_f32", "km_matmul_bwd_f32", "km_dense_f32", "km_dense_bwd_f32",
+    "km_index_f32", "km_index_bwd_workspace_bytes", "km_index_bwd_f32", "km_make_ranges_f32",
+    "km_make_ranges_symmetric_f32", "km_transpose_ranges_i32", "km_count_entries",
+    "km_probe_fp32_peak",
+]
+
+
+def check(status: int) -> None:
+    if status != KM_OK:
+        raise KmError(f"[km status {status}] {lib.km_last_error().decode()}")

@@ -1,0 +1,234 @@
+// Forward product  out = K(x1, x2; theta) . rhs  over banded row-block ranges (FMA path).
+//
+// One CTA owns one 128-row block of one batch (and one block of KB rhs columns) and walks the
+// block's column band [start, end) in tiles of TILE_N columns.  x2 and rhs tiles are staged in
+// shared memory with cp.async, double buffered.  Lanes own rows (RPT rows each, 32 apart, so
+// x1 is read coalesced and every shared-memory read in the inner loop is a broadcast); the WN
+// warps of a row group take interleaved columns of a tile and their partial sums are combined
+// through shared memory once, at the end of the band.  Each kernel entry is generated in
+// registers (SFU ex2 / sin / cos + FP32) and immediately contracted against KB rhs values
+// held in registers: RPT * KB independent FMAs per staged column and thread.
+//
+// Replaces kernel_matmul_cuda_kernel + the zero fill, parameter transform and column-slab sum
+// around it (reference: native/matmul/matmul.cu:13-203).
+#include "km_common.cuh"
+
+namespace km {
+
+template <typename T>
+struct MatmulArgs {
+    Batch batch;
+    int64_t m, n, k;
+    int64_t row_blocks;  // ceil(m / 128)
+    int k_blocks;        // ceil(k / KB)
+    View<const float> x1, x2, rhs, params;
+    View<const int> start, end;
+    View<float> out;
+    int rhs_vec_ok;  // rhs rows may be copied 16 bytes at a time
+    int out_vec_ok;  // out rows may be stored 16 bytes at a time
+};
+
+template <int KT, int KB, int RPT, int WN>
+__global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN)
+    matmul_fma_kernel(const MatmulArgs<float> a) {
+    constexpr int WM = 128 / (32 * RPT);
+    constexpr int THREADS = 32 * WM * WN;
+    constexpr int STAGE_FLOATS = TILE_N * KB + TILE_N;  // rhs tile then x2 tile
+
+    extern __shared__ __align__(16) float smem[];
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int wm = warp % WM;
+    const int wn = warp / WM;
+
+    // work item: batch fastest so that CTAs resident together share rhs / x2 tiles in L2
+    int64_t item = blockIdx.x;
+    const int64_t b = item % a.batch.count;
+    item /= a.batch.count;
+    const int64_t r = item % a.row_blocks;
+    const int kb = (int)(item / a.row_blocks);
+    const int64_t k0 = (int64_t)kb * KB;
+
+    const BatchIndex bi = decompose(a.batch, b);
+    const float *x1 = batch_ptr(a.x1, bi);
+    const float *x2 = batch_ptr(a.x2, bi);
+    const float *rhs = batch_ptr(a.rhs, bi);
+    const float *theta = batch_ptr(a.params, bi);
+    float *out = batch_ptr(a.out, bi);
+
+    KernelFn<KT> fn;
+    fn.init(theta, a.params.s0);
+
+    const int n = (int)a.n;
+    const int band_lo = clamp_int(batch_ptr(a.start, bi)[r * a.start.s0], 0, n);
+    const int band_hi = max(band_lo, min(batch_ptr(a.end, bi)[r * a.end.s0], n));
+
+    // rows of this thread
+    float x1r[RPT];
+    const int64_t row_base = r * KM_BLOCK_SIZE + wm * (32 * RPT) + lane;
+#pragma unroll
+    for (int i = 0; i < RPT; i++) {
+        const int64_t row = row_base + 32 * i;
+        x1r[i] = row < a.m ? x1[row * a.x1.s0] : 0.0f;
+    }
+
+    float acc[RPT][KB];
+#pragma unroll
+    for (int i = 0; i < RPT; i++)
+#pragma unroll
+        for (int c = 0; c < KB; c++) acc[i][c] = 0.0f;
+
+    const bool full_kb = (k0 + KB <= a.k);
+    const bool vec = (KB % 4 == 0) && a.rhs_vec_ok && full_kb;
+
+    auto stage_tile = [&](int buf, int n0) {
+        float *rs = smem + buf * STAGE_FLOATS;
+        stage_band_tile<KB, THREADS>(rs, rs + TILE_N * KB, x2, a.x2.s0, rhs, a.rhs.s0, a.rhs.s1, k0, a.k, n0,
+                                     min(TILE_N, band_hi - n0), vec, tid);
+    };
+
+    const int tiles = (band_hi - band_lo + TILE_N - 1) / TILE_N;
+    if (tiles > 0) {
+        stage_tile(0, band_lo);
+        cp_async_commit();
+    }
+    for (int t = 0; t < tiles; t++) {
+        const int n0 = band_lo + t * TILE_N;
+        if (t + 1 < tiles) {
+            stage_tile((t + 1) & 1, n0 + TILE_N);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+
+        const float *rs = smem + (t & 1) * STAGE_FLOATS;
+        const float *xs = rs + TILE_N * KB;
+        const int cnt = min(TILE_N, band_hi - n0);
+#pragma unroll 2
+        for (int j = wn; j < cnt; j += WN) {
+            const float xj = xs[j];
+            float rv[KB];
+            load_staged_row<KB>(rs, j, rv);
+#pragma unroll
+            for (int i = 0; i < RPT; i++) {
+                const float kv = fn.unscaled(x1r[i] - xj);
+#pragma unroll
+                for (int c = 0; c < KB; c++) acc[i][c] = fmaf(kv, rv[c], acc[i][c]);
+            }
+        }
+        __syncthreads();
+    }
+
+    // combine the WN column-interleaved partial sums, scale, store
+    const float scale = fn.scale;
+    if constexpr (WN > 1) {
+        // red[wn][row_local][KB]
+        float *red = smem;
+#pragma unroll
+        for (int i = 0; i < RPT; i++) {
+            const int row_local = wm * (32 * RPT) + lane + 32 * i;
+#pragma unroll
+            for (int c = 0; c < KB; c++) red[(wn * 128 + row_local) * KB + c] = acc[i][c];
+        }
+        __syncthreads();
+        for (int q = tid; q < 128 * KB; q += THREADS) {
+            const int row_local = q / KB, c = q % KB;
+            const int64_t row = r * KM_BLOCK_SIZE + row_local;
+            if (row < a.m && k0 + c < a.k) {
+                float s = 0.0f;
+#pragma unroll
+                for (int w = 0; w < WN; w++) s += red[(w * 128 + row_local) * KB + c];
+                out[row * a.out.s0 + (k0 + c) * a.out.s1] = s * scale;
+            }
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < RPT; i++) {
+            const int64_t row = row_base + 32 * i;
+            if (row < a.m) {
+#pragma unroll
+                for (int c = 0; c < KB; c++)
+                    if (k0 + c < a.k) out[row * a.out.s0 + (k0 + c) * a.out.s1] = acc[i][c] * scale;
+            }
+        }
+    }
+}
+
+template <int KT, int KB, int RPT, int WN>
+static int launch_matmul(const MatmulArgs<float> &a, cudaStream_t stream) {
+    constexpr int WM = 128 / (32 * RPT);
+    constexpr int THREADS = 32 * WM * WN;
+    constexpr size_t stage_bytes = 2 * (TILE_N * KB + TILE_N) * sizeof(float);
+    constexpr size_t red_bytes = WN > 1 ? (size_t)WN * 128 * KB * sizeof(float) : 0;
+    constexpr size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
+    auto kernel = matmul_fma_kernel<KT, KB, RPT, WN>;
+    if (smem > 48 * 1024) {
+        cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(matmul)");
+    }
+    const int64_t items = a.batch.count * a.row_blocks * a.k_blocks;
+    if (items > 0x7fffffffLL) {
+        set_error("km_matmul_f32: too many work items (%lld)", (long long)items);
+        return KM_ERR_UNSUPPORTED;
+    }
+    kernel<<<(unsigned)items, THREADS, smem, stream>>>(a);
+    KM_CHECK_LAUNCH("km_matmul_f32 launch");
+    return KM_OK;
+}
+
+template <int KT>
+static int dispatch_matmul(MatmulArgs<float> &a, cudaStream_t stream) {
+    const int64_t k = a.k;
+    auto with_kb = [&](int kb) { a.k_blocks = (int)ceil_div(k, kb); };
+    if (k <= 1) { with_kb(1); return launch_matmul<KT, 1, 4, 4>(a, stream); }
+    if (k <= 2) { with_kb(2); return launch_matmul<KT, 2, 4, 4>(a, stream); }
+    if (k <= 4) { with_kb(4); return launch_matmul<KT, 4, 4, 4>(a, stream); }
+    if (k <= 8) { with_kb(8); return launch_matmul<KT, 8, 4, 4>(a, stream); }
+    if (k <= 16) { with_kb(16); return launch_matmul<KT, 16, 4, 4>(a, stream); }
+    with_kb(32);
+    return launch_matmul<KT, 32, 2, 2>(a, stream);
+}
+
+}  // namespace km
+
+extern "C" int km_matmul_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
+                             const km_view *x1, const km_view *x2, const km_view *rhs,
+                             const km_view *params, const km_view *start, const km_view *end,
+                             const km_view *out, void *stream) {
+    using namespace km;
+    KM_REQUIRE(valid_kernel_type(kernel_type), KM_ERR_INVALID_ARGUMENT, "km_matmul_f32: unknown kernel type %d", kernel_type);
+    KM_REQUIRE(batch && x1 && x2 && rhs && params && start && end && out, KM_ERR_INVALID_ARGUMENT,
+               "km_matmul_f32: null argument");
+    KM_REQUIRE(m >= 0 && n >= 0 && k >= 0 && n <= 0x7fffffffLL && m <= 0x7fffffffLL * 64, KM_ERR_INVALID_ARGUMENT,
+               "km_matmul_f32: bad sizes m=%lld n=%lld k=%lld", (long long)m, (long long)n, (long long)k);
+    MatmulArgs<float> a;
+    int rc = make_batch(batch, &a.batch);
+    if (rc != KM_OK) return rc;
+    if (a.batch.count == 0 || m == 0 || k == 0) return KM_OK;
+    KM_REQUIRE(x1->data && out->data && params->data && start->data && end->data, KM_ERR_INVALID_ARGUMENT,
+               "km_matmul_f32: null data pointer");
+    KM_REQUIRE(n == 0 || (x2->data && rhs->data), KM_ERR_INVALID_ARGUMENT, "km_matmul_f32: null data pointer");
+    a.m = m;
+    a.n = n;
+    a.k = k;
+    a.row_blocks = ceil_div(m, KM_BLOCK_SIZE);
+    a.x1 = make_view<const float>(x1, a.batch);
+    a.x2 = make_view<const float>(x2, a.batch);
+    a.rhs = make_view<const float>(rhs, a.batch);
+    a.params = make_view<const float>(params, a.batch);
+    a.start = make_view<const int>(start, a.batch);
+    a.end = make_view<const int>(end, a.batch);
+    a.out = make_view<float>(out, a.batch);
+    a.rhs_vec_ok = rows_vectorizable(a.rhs, a.batch) ? 1 : 0;
+    a.out_vec_ok = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (kernel_type) {
+    case KM_KERNEL_RBF: return dispatch_matmul<KM_KERNEL_RBF>(a, s);
+    case KM_KERNEL_SPECTRAL: return dispatch_matmul<KM_KERNEL_SPECTRAL>(a, s);
+    default: return dispatch_matmul<KM_KERNEL_LOCALLY_PERIODIC>(a, s);
+    }
+}

@@ -1,0 +1,303 @@
+"""The native ops of the hot path, with the call signatures of the reference's per-op modules.
+
+Each function is what ``load_native(<op>, defines).call`` is in the reference
+(``native/<op>/<op>.cpp``), with the kernel type as a runtime argument instead of a
+``-DKM_KERNEL_*`` define.  PyTorch is used for device memory and the current stream only;
+all arithmetic runs in ``libkm_b200.so`` through its C ABI (``include/km_b200.h``).
+
+Conventions shared with the reference: fp32 CUDA tensors, int32 ranges and indices; arbitrary
+leading batch dims shared by all arguments (expanded / stride-0 views are used as they are,
+never materialised); gradients are produced for ``params`` only.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Sequence
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import KM_MAX_BATCH_DIMS, KERNEL_TYPES, KmBatch, KmView, check, lib
+
+BLOCK_SIZE = 128
+NUM_PARAMS = {"rbf": 2, "spectral": 3, "locally_periodic": 4}
+
+
+def _kernel_id(kernel_type: str) -> int:
+    try:
+        return KERNEL_TYPES[kernel_type]
+    except KeyError:
+        raise ValueError(f"Unknown kernel type: {kernel_type}") from None
+
+
+def _check_cuda(x: Tensor) -> None:
+    # native/common/entrypoint.h:3-5
+    if not isinstance(x, Tensor) or not x.is_cuda:
+        raise RuntimeError("x must be a CUDA tensor")
+
+
+def _check_f32(x: Tensor) -> None:
+    _check_cuda(x)
+    if x.dtype != torch.float32:
+        raise RuntimeError("x must be float32")
+
+
+def _check_i32(x: Tensor) -> None:
+    # native/common/entrypoint.h:7-14
+    _check_cuda(x)
+    if x.dtype != torch.int32:
+        raise RuntimeError("x must be int32")
+
+
+def _same_device(*tensors: Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors[1:]:
+        if t.device != dev:
+            raise RuntimeError("all tensors must be on the same CUDA device")
+    return dev
+
+
+def _common_batch(tensors_nb: Sequence[tuple[Tensor, int]]) -> tuple[int, ...]:
+    shapes = []
+    for t, nb in tensors_nb:
+        if t.dim() < nb:
+            raise RuntimeError(f"tensor of rank {t.dim()} needs at least {nb} trailing dims")
+        shapes.append(t.shape[: t.dim() - nb])
+    try:
+        return tuple(torch.broadcast_shapes(*shapes))
+    except RuntimeError as exc:
+        raise RuntimeError(f"batch dimensions do not broadcast: {[tuple(s) for s in shapes]}") from exc
+
+
+def _expand(t: Tensor, batch: tuple[int, ...], nb: int) -> Tensor:
+    core = t.shape[t.dim() - nb :]
+    t = t.expand(*batch, *core)
+    if len(batch) > KM_MAX_BATCH_DIMS:
+        # more batch dims than the ABI carries: flatten them (copies only if not collapsible)
+        t = t.reshape(-1, *core)
+    return t
+
+
+def _km_batch(batch: tuple[int, ...]) -> KmBatch:
+    if len(batch) > KM_MAX_BATCH_DIMS:
+        n = 1
+        for s in batch:
+            n *= s
+        batch = (n,)
+    b = KmBatch()
+    b.ndim = len(batch)
+    for d, s in enumerate(batch):
+        b.size[d] = s
+    return b
+
+
+def _view(t: Tensor, nb: int) -> KmView:
+    v = KmView()
+    v.data = t.data_ptr()
+    st = t.stride()
+    nbatch = t.dim() - nb
+    for d in range(nbatch):
+        v.batch_stride[d] = st[d]
+    for d in range(nb):
+        v.stride[d] = st[nbatch + d]
+    return v
+
+
+def _stream(dev: torch.device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+
+def _prep(kernel_type: str, x1, x2, params, start, end, extra: Sequence[tuple[Tensor, int]] = ()):
+    """Common validation / broadcasting.  Returns (kid, device, batch shape, expanded tensors)."""
+    kid = _kernel_id(kernel_type)
+    for t in (x1, x2, params):
+        _check_f32(t)
+    for t in (start, end):
+        _check_i32(t)
+    for t, _ in extra:
+        _check_f32(t)
+    dev = _same_device(x1, x2, params, start, end, *(t for t, _ in extra))
+    P = NUM_PARAMS[kernel_type]
+    if params.shape[-1] != P:
+        raise RuntimeError(f"params must have {P} entries in the last dim for kernel '{kernel_type}', got {params.shape[-1]}")
+    m, n = x1.shape[-1], x2.shape[-1]
+    R = -(-m // BLOCK_SIZE)
+    if start.shape[-1] != R or end.shape[-1] != R:
+        raise RuntimeError(f"start/end must have ceil(m/{BLOCK_SIZE}) = {R} entries, got {start.shape[-1]} and {end.shape[-1]}")
+    pairs = [(x1, 1), (x2, 1), (params, 1), (start, 1), (end, 1), *extra]
+    batch = _common_batch(pairs)
+    expanded = [_expand(t, batch, nb) for t, nb in pairs]
+    return kid, dev, batch, m, n, expanded
+
+
+def _out_batch(batch: tuple[int, ...]) -> tuple[int, ...]:
+    return batch
+
+
+def matmul(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor, start: Tensor, end: Tensor) -> Tensor:
+    """``K(x1, x2; params)[masked by ranges] @ rhs`` -> ``(*batch, m, k)``.
+
+    Reference: ``matmul.call(x1, x2, rhs, params, start, end)`` (native/matmul/matmul.cpp:6-17).
+    """
+    kid, dev, batch, m, n, (x1e, x2e, pe, se, ee, re) = _prep(kernel_type, x1, x2, params, start, end, [(rhs, 2)])
+    if rhs.shape[-2] != n:
+        raise RuntimeError(f"rhs must have n = {n} rows, got {rhs.shape[-2]}")
+    k = rhs.shape[-1]
+    out = torch.empty(*batch, m, k, device=dev, dtype=torch.float32)
+    oute = out.reshape(-1, m, k) if len(batch) > KM_MAX_BATCH_DIMS else out
+    with torch.cuda.device(dev):
+        check(lib.km_matmul_f32(
+            kid, _km_batch(batch), m, n, k, _view(x1e, 1), _view(x2e, 1), _view(re, 2), _view(pe, 1),
+            _view(se, 1), _view(ee, 1), _view(oute, 2), _stream(dev)))
+    return out
+
+
+def _grad_call(fn, kernel_type, x1, x2, left, right, params, start, end, swap: bool) -> Tensor:
+    kid, dev, batch, m, n, (x1e, x2e, pe, se, ee, le, rte) = _prep(
+        kernel_type, x1, x2, params, start, end, [(left, 2), (right, 2)])
+    if left.shape[-2] != m or right.shape[-2] != n or left.shape[-1] != right.shape[-1]:
+        raise RuntimeError(f"left must be (.., {m}, k) and right (.., {n}, k); got {tuple(left.shape)} and {tuple(right.shape)}")
+    k = left.shape[-1]
+    P = NUM_PARAMS[kernel_type]
+    grad = torch.empty(*batch, P, device=dev, dtype=torch.float32)
+    grade = grad.reshape(-1, P) if len(batch) > KM_MAX_BATCH_DIMS else grad
+    kb = _km_batch(batch)
+    ws_bytes = lib.km_grad_workspace_bytes(kid, kb, m)
+    ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
+    a, b = (_view(rte, 2), _view(le, 2)) if swap else (_view(le, 2), _view(rte, 2))
+    with torch.cuda.device(dev):
+        if swap:  # matmul_bwd argument order: rhs ... out_grad
+            check(fn(kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), a, _view(pe, 1), _view(se, 1), _view(ee, 1),
+                     b, _view(grade, 1), ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
+        else:
+            check(fn(kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), a, b, _view(pe, 1), _view(se, 1), _view(ee, 1),
+                     _view(grade, 1), ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
+    return grad
+
+
+def matmul_bwd(kernel_type: str, x1, x2, rhs, params, start, end, out_grad) -> Tensor:
+    """Gradient of ``sum(out_grad * matmul(...))`` wrt ``params`` -> ``(*batch, P)``.
+
+    Reference: ``matmul_bwd.call(x1, x2, rhs, params, start, end, out_grad)``
+    (native/matmul_bwd/matmul_bwd.cpp:6-19).
+    """
+    return _grad_call(lib.km_matmul_bwd_f32, kernel_type, x1, x2, out_grad, rhs, params, start, end, swap=True)
+
+
+def bilinear_derivative(kernel_type: str, x1, x2, left_vecs, right_vecs, params, start, end) -> Tensor:
+    """Gradient of ``sum_c left[:, c]^T K right[:, c]`` wrt ``params`` -> ``(*batch, P)``.
+
+    Reference: ``bilinear_derivative.call(x1, x2, left_vecs, right_vecs, params, start, end)``
+    (native/bilinear_derivative/bilinear_derivative.cpp:6-21).
+    """
+    return _grad_call(lib.km_bilinear_derivative_f32, kernel_type, x1, x2, left_vecs, right_vecs, params, start, end, swap=False)
+
+
+def dense(kernel_type: str, x1, x2, params, start, end) -> Tensor:
+    """Masked dense ``K`` -> ``(*batch, m, n)``.  Reference: ``dense.call`` (native/dense/dense.cpp:6-17)."""
+    kid, dev, batch, m, n, (x1e, x2e, pe, se, ee) = _prep(kernel_type, x1, x2, params, start, end)
+    out = torch.empty(*batch, m, n, device=dev, dtype=torch.float32)
+    oute = out.reshape(-1, m, n) if len(batch) > KM_MAX_BATCH_DIMS else out
+    with torch.cuda.device(dev):
+        check(lib.km_dense_f32(kid, _km_batch(batch), m, n, _view(x1e, 1), _view(x2e, 1), _view(pe, 1),
+                               _view(se, 1), _view(ee, 1), _view(oute, 2), _stream(dev)))
+    return out
+
+
+def dense_bwd(kernel_type: str, x1, x2, params, start, end, out_grad) -> Tensor:
+    """Gradient of ``sum(out_grad * dense(...))`` wrt ``params``.  Reference: ``dense_bwd.call``
+    (native/dense_bwd/dense_bwd.cpp:6-17)."""
+    kid, dev, batch, m, n, (x1e, x2e, pe, se, ee, ge) = _prep(kernel_type, x1, x2, params, start, end, [(out_grad, 2)])
+    if out_grad.shape[-2:] != (m, n):
+        raise RuntimeError(f"out_grad must be (.., {m}, {n}), got {tuple(out_grad.shape)}")
+    P = NUM_PARAMS[kernel_type]
+    grad = torch.empty(*batch, P, device=dev, dtype=torch.float32)
+    grade = grad.reshape(-1, P) if len(batch) > KM_MAX_BATCH_DIMS else grad
+    kb = _km_batch(batch)
+    ws_bytes = lib.km_grad_workspace_bytes(kid, kb, m)
+    ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
+    with torch.cuda.device(dev):
+        check(lib.km_dense_bwd_f32(kid, kb, m, n, _view(x1e, 1), _view(x2e, 1), _view(pe, 1), _view(se, 1),
+                                   _view(ee, 1), _view(ge, 2), _view(grade, 1), ctypes.c_void_p(ws.data_ptr()),
+                                   ws_bytes, _stream(dev)))
+    return grad
+
+
+def _index_prep(batch: tuple[int, ...], batch_indices, row_index, col_index, dev):
+    batch_indices = tuple(batch_indices)
+    if len(batch_indices) != len(batch):
+        raise RuntimeError(f"expected {len(batch)} batch index tensors, got {len(batch_indices)}")
+    for t in (*batch_indices, row_index, col_index):
+        _check_i32(t)
+        if t.device != dev:
+            raise RuntimeError("all tensors must be on the same CUDA device")
+    shape = tuple(torch.broadcast_shapes(row_index.shape, col_index.shape, *(b.shape for b in batch_indices)))
+    flat = [t.expand(shape).contiguous().reshape(-1) for t in (*batch_indices, row_index, col_index)]
+    return shape, flat[:-2], flat[-2], flat[-1]
+
+
+def _bidx_array(bidx: Sequence[Tensor], batch: tuple[int, ...]):
+    arr = (ctypes.c_void_p * KM_MAX_BATCH_DIMS)()
+    for d, t in enumerate(bidx):
+        arr[d] = t.data_ptr()
+    return arr
+
+
+def index(kernel_type: str, x1, x2, params, start, end, batch_indices, row_index, col_index) -> Tensor:
+    """``K[batch_indices..., row_index, col_index]`` (0 outside the band) with the shape of the
+    index tensors.  Reference: ``index.call`` (native/index/index.cpp:6-24)."""
+    kid, dev, batch, m, n, (x1e, x2e, pe, se, ee) = _prep(kernel_type, x1, x2, params, start, end)
+    if len(batch) > KM_MAX_BATCH_DIMS:
+        raise RuntimeError(f"index supports at most {KM_MAX_BATCH_DIMS} batch dims")
+    shape, bidx, row, col = _index_prep(batch, batch_indices, row_index, col_index, dev)
+    L = row.numel()
+    out = torch.empty(L, device=dev, dtype=torch.float32)
+    with torch.cuda.device(dev):
+        check(lib.km_index_f32(kid, _km_batch(batch), m, n, L, _view(x1e, 1), _view(x2e, 1), _view(pe, 1),
+                               _view(se, 1), _view(ee, 1), _bidx_array(bidx, batch), ctypes.c_void_p(row.data_ptr()),
+                               ctypes.c_void_p(col.data_ptr()), ctypes.c_void_p(out.data_ptr()), _stream(dev)))
+    return out.reshape(shape)
+
+
+def index_bwd(kernel_type: str, x1, x2, params, start, end, batch_indices, row_index, col_index, out_grad) -> Tensor:
+    """Gradient of ``sum(out_grad * index(...))`` wrt ``params`` -> ``(*batch, P)``.
+    Reference: ``index_bwd.call`` (native/index_bwd/index_bwd.cpp:6-27)."""
+    kid, dev, batch, m, n, (x1e, x2e, pe, se, ee) = _prep(kernel_type, x1, x2, params, start, end)
+    if len(batch) > KM_MAX_BATCH_DIMS:
+        raise RuntimeError(f"index_bwd supports at most {KM_MAX_BATCH_DIMS} batch dims")
+    shape, bidx, row, col = _index_prep(batch, batch_indices, row_index, col_index, dev)
+    _check_f32(out_grad)
+    og = out_grad.expand(shape).contiguous().reshape(-1)
+    L = row.numel()
+    P = NUM_PARAMS[kernel_type]
+    grad = torch.empty(*batch, P, device=dev, dtype=torch.float32)
+    kb = _km_batch(batch)
+    ws_bytes = lib.km_index_bwd_workspace_bytes(kid, kb)
+    ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
+    with torch.cuda.device(dev):
+        check(lib.km_index_bwd_f32(kid, kb, m, n, L, _view(x1e, 1), _view(x2e, 1), _view(pe, 1), _view(se, 1),
+                                   _view(ee, 1), _bidx_array(bidx, batch), ctypes.c_void_p(row.data_ptr()),
+                                   ctypes.c_void_p(col.data_ptr()), ctypes.c_void_p(og.data_ptr()), _view(grad, 1),
+                                   ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
+    return grad
+
+
+def count_entries(m: int, n: int, start: Tensor, end: Tensor) -> Tensor:
+    """Visited kernel entries ``sum rows(r) * (end - start)`` as a 0-dim int64 device tensor."""
+    _check_i32(start)
+    _check_i32(end)
+    dev = _same_device(start, end)
+    batch = _common_batch([(start, 1), (end, 1)])
+    se, ee = _expand(start, batch, 1), _expand(end, batch, 1)
+    out = torch.empty((), device=dev, dtype=torch.int64)
+    with torch.cuda.device(dev):
+        check(lib.km_count_entries(_km_batch(batch), m, n, _view(se, 1), _view(ee, 1),
+                                   ctypes.c_void_p(out.data_ptr()), _stream(dev)))
+    return out
+
+
+__all__ = [
+    "matmul", "matmul_bwd", "bilinear_derivative", "dense", "dense_bwd", "index", "index_bwd",
+    "count_entries", "BLOCK_SIZE", "NUM_PARAMS",
+]
