@@ -1,0 +1,481 @@
+"""Benchmark of the kernel-matmul hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+Workload at the default settings: the spectral-mixture configuration (16 components sharing
+x and rhs, m = n = 65536 sorted U[0, 500], l ~ LogUniform[0.5, 5], f ~ U[0, 2], cutoff 4 l,
+rhs 65536 x 16; seeded synthetic inputs, ``kernel_matmul_b200/workloads.py``).  One step is one
+pass of the hot path over that batch: the forward product ``K . rhs`` and the hyper-parameter
+gradients ``matmul_bwd`` of all 16 components.  The metric is kernel entries x rhs columns per
+second: a step processes ``2 * E * k`` units (E visited entries, once forward and once in the
+gradient).
+
+Printed keys (one JSON line, rank 0):
+  value      whole-job units/s with inputs resident in HBM, CUDA-event time per step summed over
+             K steps, L2 flushed between steps, max over ranks;
+  e2e        the same metric through the public ops with HOST (pinned) buffers: every step
+             copies x, rhs, params and out_grad to the device, builds the band on the device,
+             runs forward + gradient and copies out and grad back;
+  roofline   the dominant kernel against the FP32-pipe peak measured live with the library's
+             FFMA calibration kernel (FMA-equivalent TFLOP/s = 2 x FP32-pipe instructions);
+  cpu_baseline  the dense PyTorch formulation (materialise K, mask by ranges, matmul, autograd)
+             in fp32 on all host cores, on a bounded sample of the same workload.
+
+With N > 1 (torchrun) every rank runs its own 16 components of the same shape (seeded by rank):
+independent work, no data-path collective, weak scaling.
+
+``--impl reference`` times only the CPU dense formulation (the reference has no CPU kernel of
+its own for this path; the dense formulation is what its tests define as the expected result).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "kernel_entries_x_rhs_cols_per_s"
+UNIT = "entry-cols/s"
+
+# Algorithmic per-entry instruction budget of the FMA path (FP32-pipe instructions, SFU ops):
+# generation + contraction.  Forward: k FFMA per entry; gradient: k FFMA for the coefficient
+# <left_i, right_j> plus one FFMA per parameter.
+GEN_FWD = {"rbf": (3, 1), "spectral": (5, 2), "locally_periodic": (6, 2)}
+GEN_BWD = {"rbf": (4, 1), "spectral": (8, 3), "locally_periodic": (11, 3)}
+NPARAMS = {"rbf": 2, "spectral": 3, "locally_periodic": 4}
+
+
+def fp32_instr_fwd(kt: str, k: int) -> int:
+    return GEN_FWD[kt][0] + k
+
+
+def fp32_instr_bwd(kt: str, k: int) -> int:
+    return GEN_BWD[kt][0] + k + NPARAMS[kt]
+
+
+# ------------------------------------------------------------------------------------ helpers
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device_index: int):
+        self.proc = None
+        self.path = None
+        try:
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            if not uuid.startswith("GPU-"):
+                uuid = "GPU-" + uuid
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=self.out, stderr=subprocess.DEVNULL)
+        except Exception:  # noqa: BLE001 - no nvidia-smi: report empty clocks
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:  # noqa: BLE001
+            self.proc.kill()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        busy = [s for s in sm if s > 0.5 * max(sm)] if sm else []
+        return {
+            "sm_mhz": statistics.median(busy) if busy else None,
+            "sm_max_mhz": max(mx) if mx else None,
+            "reasons": sorted(reasons),
+            "samples": len(sm),
+        }
+
+
+def cuda_ms(fn, stream=None) -> float:
+    a = torch.cuda.Event(enable_timing=True)
+    b = torch.cuda.Event(enable_timing=True)
+    a.record()
+    fn()
+    b.record()
+    b.synchronize()
+    return a.elapsed_time(b)
+
+
+# ----------------------------------------------------------------------------------- workload
+
+
+def make_workload(name: str, rank: int):
+    from kernel_matmul_b200 import workloads
+
+    if name == "spectral_mixture":
+        w = workloads.spectral_mixture()
+    elif name == "spectral_mixture_small":
+        w = workloads.spectral_mixture(n=8192, components=4, k=16, span=62.5)
+    else:
+        raise SystemExit(f"unknown workload {name}")
+    if rank > 0:
+        # every rank gets its own components of the same distribution (weak scaling)
+        g = torch.Generator().manual_seed(1000 + rank)
+        B = w.params.shape[0]
+        ell = torch.exp(torch.rand(B, generator=g) * math.log(10.0) + math.log(0.5))
+        f = torch.rand(B, generator=g) * 2
+        w.params = torch.stack([ell, f, torch.ones(B)], dim=-1)
+        w.cutoffs = [4.0 * float(v) for v in ell]
+        w.extra["out_grad"] = torch.randn(w.extra["out_grad"].shape, generator=g)
+    return w
+
+
+# -------------------------------------------------------------------------------- CPU baseline
+
+
+def cpu_dense_sample(w, seconds: float = 12.0, max_seconds: float = 30.0) -> dict:
+    """Dense formulation (oracle/dense_reference.py) in fp32 on all host cores: forward slab
+    product + autograd gradient for row-block slabs of the workload, drawn round-robin over the
+    components, until ``seconds`` of work are done.  Returns units/s."""
+    from oracle import dense_reference as D
+    from oracle import oracle as O
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    x = w.x
+    n = w.n
+    k = w.rhs.shape[-1]
+    B = w.params.shape[0]
+    R = -(-n // 128)
+    bands = [O.make_ranges(c, x) for c in w.cutoffs]
+    units = 0
+    entries = 0
+    slabs = 0
+    t0 = time.perf_counter()
+    group = 8  # row blocks per slab
+    order = [(b, r0) for p in range(16) for r0 in range(p * group, R, group * 16) for b in range(B)]
+    for b, r0 in order:
+        start, end = bands[b if len(bands) > 1 else 0]
+        r1 = min(r0 + group, R)
+        c0 = int(start[r0:r1].min())
+        c1 = min(int(end[r0:r1].max()), n)
+        rows = slice(r0 * 128, min(r1 * 128, n))
+        p = w.params[b].clone().requires_grad_(True)
+        K = D.kernel_matrix(w.kernel_type, x[rows], x[c0:c1], p)
+        mask = D.band_mask(start[r0:r1] - c0, end[r0:r1] - c0, K.shape[0], c1 - c0)
+        Km = torch.where(mask, K, torch.zeros((), dtype=K.dtype))
+        out = Km @ w.rhs[c0:c1]
+        out.backward(gradient=w.extra["out_grad"][b, rows])
+        e = int(mask.sum())
+        entries += e
+        units += 2 * e * k
+        slabs += 1
+        el = time.perf_counter() - t0
+        if el >= seconds or el >= max_seconds:
+            break
+    el = time.perf_counter() - t0
+    return {
+        "value": units / el,
+        "unit": UNIT,
+        "cores": cores,
+        "kind": "port",
+        "sample": f"{slabs} slabs of {group} row blocks ({entries} entries, fwd + autograd bwd, fp32) in {el:.1f} s",
+        "seconds": el,
+    }
+
+
+# --------------------------------------------------------------------------------------- main
+
+
+def run_reference(args, rank: int, world: int) -> None:
+    if rank != 0:
+        return
+    w = make_workload(args.workload, 0)
+    per_step = max(2.0, min(10.0, 60.0 / max(1, args.steps + args.warmup)))
+    for _ in range(args.warmup):
+        cpu_dense_sample(w, seconds=per_step / 4, max_seconds=per_step)
+    vals, secs = [], []
+    base = None
+    for _ in range(args.steps):
+        base = cpu_dense_sample(w, seconds=per_step, max_seconds=2 * per_step)
+        vals.append(base["value"])
+        secs.append(base["seconds"])
+    value = statistics.mean(vals)
+    base["value"] = value
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(secs),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name, "what": "dense PyTorch formulation on host cores, bounded sample per step"},
+        "cpu_baseline": base,
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def reference_cuda_timing(w, dev, xb, rhs, params, start, end, og) -> dict | None:
+    """Times the reference's own CUDA kernels (compiled unmodified into oracle/_ref) on the same
+    inputs, when those modules are present.  Informational: the generic-SIMT bar on this GPU."""
+    import importlib.util
+
+    out = {}
+    try:
+        k = rhs.shape[-1]
+        for op, modname in (("fwd", f"km_ref_matmul_{w.kernel_type}_k{k}"), ("bwd", f"km_ref_matmul_bwd_{w.kernel_type}")):
+            path = os.path.join(ROOT, "oracle", "_ref", modname, modname + ".so")
+            if not os.path.exists(path):
+                return None
+            spec = importlib.util.spec_from_file_location(modname, path)
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            fn = (lambda m=mod: m.call(xb, xb, rhs, params, start, end)) if op == "fwd" else (
+                lambda m=mod: m.call(xb, xb, rhs, params, start, end, og))
+            fn()
+            torch.cuda.synchronize()
+            # the reference launches on the legacy default stream: time with full device syncs
+            ts = []
+            for _ in range(3):
+                torch.cuda.synchronize()
+                t0 = time.perf_counter()
+                fn()
+                torch.cuda.synchronize()
+                ts.append(1e3 * (time.perf_counter() - t0))
+            out[f"{op}_ms"] = min(ts)
+        return out
+    except Exception as exc:  # noqa: BLE001 - informational only
+        return {"error": str(exc)[:200]}
+
+
+def run_ours(args, rank: int, world: int, local: int) -> None:
+    import kernel_matmul_b200 as km  # raises if libkm_b200.so is missing: no fallback
+    from kernel_matmul_b200 import ops, ranges, workloads
+    from kernel_matmul_b200._lib import check, lib
+    import ctypes
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    w = make_workload(args.workload, rank)
+    kt = w.kernel_type
+    n, k = w.n, w.rhs.shape[-1]
+    B = w.params.shape[0]
+
+    # ---- resident inputs
+    x = w.x.to(dev)
+    xb = x.expand(B, -1)
+    rhs = w.rhs.to(dev).expand(B, -1, -1)
+    params = w.params.to(dev)
+    og = w.extra["out_grad"].to(dev)
+    start, end = workloads.band(w, x)
+    E = int(ops.count_entries(n, n, start, end))
+    units_per_step = 2 * E * k
+
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB of L2
+
+    def step():
+        out = ops.matmul(kt, xb, xb, rhs, params, start, end)
+        g = ops.matmul_bwd(kt, xb, xb, rhs, params, start, end, og)
+        return out, g
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize()
+
+    # ---- live FP32 peak (FFMA calibration kernel of the library)
+    flops = ctypes.c_double()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+    def probe():
+        check(lib.km_probe_fp32_peak(20000, None, ctypes.byref(flops), stream))
+
+    probe()
+    fp32_peak = max(flops.value / (cuda_ms(probe) * 1e-3) for _ in range(3)) / 1e12
+
+    # ---- timed region
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.barrier()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    wall0 = time.perf_counter()
+    step_ms, fwd_ms, bwd_ms = [], [], []
+    for _ in range(args.steps):
+        flush.fill_(1)
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        ops.matmul(kt, xb, xb, rhs, params, start, end)
+        e1.record()
+        ops.matmul_bwd(kt, xb, xb, rhs, params, start, end, og)
+        e2.record()
+        e2.synchronize()
+        fwd_ms.append(e0.elapsed_time(e1))
+        bwd_ms.append(e1.elapsed_time(e2))
+        step_ms.append(e0.elapsed_time(e2))
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    wall = time.perf_counter() - wall0
+    total_ms = sum(step_ms)
+
+    # ---- end to end with host buffers (pinned), copies inside the timed region
+    hx = w.x.pin_memory()
+    hrhs = w.rhs.contiguous().pin_memory()
+    hp = w.params.contiguous().pin_memory()
+    hog = w.extra["out_grad"].contiguous().pin_memory()
+    hout = torch.empty(B, n, k).pin_memory()
+    hgrad = torch.empty(B, w.params.shape[-1]).pin_memory()
+    h2d = sum(t.numel() * t.element_size() for t in (hx, hrhs, hp, hog))
+    d2h = sum(t.numel() * t.element_size() for t in (hout, hgrad))
+
+    def e2e_step():
+        dx = hx.to(dev, non_blocking=True)
+        drhs = hrhs.to(dev, non_blocking=True).expand(B, -1, -1)
+        dp = hp.to(dev, non_blocking=True)
+        dog = hog.to(dev, non_blocking=True)
+        st, en = workloads.band(w, dx)
+        dxb = dx.expand(B, -1)
+        out = ops.matmul(kt, dxb, dxb, drhs, dp, st, en)
+        g = ops.matmul_bwd(kt, dxb, dxb, drhs, dp, st, en, dog)
+        hout.copy_(out, non_blocking=True)
+        hgrad.copy_(g, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_ms = []
+    for _ in range(args.steps):
+        flush.fill_(1)
+        e2e_ms.append(cuda_ms(e2e_step))
+    clocks = sampler.stop()
+    e2e_total = sum(e2e_ms)
+
+    # ---- max over ranks
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_total], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_total = float(t[0]), float(t[1])
+        u = torch.tensor([float(units_per_step)], device=dev, dtype=torch.float64)
+        dist.all_reduce(u, op=dist.ReduceOp.SUM)
+        units_all = float(u[0])
+    else:
+        units_all = float(units_per_step)
+
+    if rank == 0:
+        ms_per_step = total_ms / args.steps
+        value = units_all / (ms_per_step * 1e-3)
+        e2e_value = units_all / (e2e_total / args.steps * 1e-3)
+        fwd = statistics.mean(fwd_ms)
+        bwd = statistics.mean(bwd_ms)
+        kernels = {
+            "matmul_fma_kernel": {"ms": fwd, "fp32_instr_per_entry": fp32_instr_fwd(kt, k), "sfu_per_entry": GEN_FWD[kt][1]},
+            "grad_band_kernel": {"ms": bwd, "fp32_instr_per_entry": fp32_instr_bwd(kt, k), "sfu_per_entry": GEN_BWD[kt][1]},
+        }
+        traffic = None
+        tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
+        dom = max(kernels, key=lambda kname: kernels[kname]["ms"])
+        if os.path.exists(tpath):
+            traffic = json.load(open(tpath)).get(args.workload, {}).get(dom)
+        for kname, kd in kernels.items():
+            kd["achieved_tflops"] = 2.0 * E * kd["fp32_instr_per_entry"] / (kd["ms"] * 1e-3) / 1e12
+            kd["frac_fp32"] = kd["achieved_tflops"] / fp32_peak
+            sm_clk = (clocks["sm_mhz"] or 1965.0) * 1e6
+            kd["frac_sfu"] = E * kd["sfu_per_entry"] / (kd["ms"] * 1e-3) / (148 * 16 * sm_clk)
+        d = kernels[dom]
+        peaks = {}
+        ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
+        if os.path.exists(ppath):
+            peaks = json.load(open(ppath))
+        hbm_bytes = 4 * (n * k + B * n * k * 2 + n + 2 * B * (n // 128))
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {
+                "workload": w.name, "ops": "matmul fwd + matmul_bwd", "entries_per_rank": E, "rhs_cols": k,
+                "units_per_step": units_all, "l2": "flushed between steps (256 MB write)",
+                "per_rank": "own 16 components, no collective",
+            },
+            "roofline": {
+                "bound": "fp32", "kernel": dom, "achieved": d["achieved_tflops"], "peak": fp32_peak,
+                "unit": "TFLOP/s", "frac": d["frac_fp32"], "traffic": traffic,
+                "peak_source": "measured live: km_probe_fp32_peak (FFMA issue rate of all SMs); achieved = 2 x "
+                               "algorithmic FP32-pipe instructions per launch / CUDA-event time",
+                "hbm": {"algorithmic_bytes_per_step": hbm_bytes,
+                        "frac_of_measured_hbm": (hbm_bytes / (ms_per_step * 1e-3)) / (peaks.get("hbm_gbs", 6650.0) * 1e9)},
+                "kernels": kernels,
+            },
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "ms_per_step": e2e_total / args.steps},
+            "gpu_launches": 3 * args.steps,
+            "clocks": clocks,
+            "wall_s": wall,
+        }
+        if not args.no_cpu and world == 1:
+            line["cpu_baseline"] = cpu_dense_sample(w)
+        ref_cuda = reference_cuda_timing(w, dev, xb, rhs, params, start, end, og)
+        if ref_cuda is not None:
+            line["reference_cuda_kernels_same_gpu"] = ref_cuda
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="spectral_mixture")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    rank, world, local = dist_env()
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local)
+
+
+if __name__ == "__main__":
+    main()

@@ -119,6 +119,23 @@ __device__ __forceinline__ float sin_approx(float x) {
     return y;
 }
 
+// Packed FP32 pairs (Blackwell fma.rn.f32x2): one instruction issues two FMAs, which halves
+// the issue slots of the contraction loops and leaves them to the SFU / load instructions.
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pack2(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float &lo, float &hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
 // Kernel functions.
 //
 // User parameters theta are mapped to device constants once per CTA (the reference launches
@@ -308,6 +325,22 @@ __device__ __forceinline__ void load_staged_row(const float *rs, int j, float (&
     } else {
 #pragma unroll
         for (int c = 0; c < KB; c++) rv[c] = rs[j * KB + c];
+    }
+}
+
+// Same read as packed pairs: rv2[c] = (row[2c], row[2c + 1]).  KB even.
+template <int KB>
+__device__ __forceinline__ void load_staged_row2(const float *rs, int j, f32x2 (&rv2)[KB / 2]) {
+    if constexpr (KB % 4 == 0) {
+#pragma unroll
+        for (int c4 = 0; c4 < KB / 4; c4++) {
+            const ulonglong2 v = *reinterpret_cast<const ulonglong2 *>(rs + j * KB + c4 * 4);
+            rv2[c4 * 2 + 0] = v.x;
+            rv2[c4 * 2 + 1] = v.y;
+        }
+    } else {
+        static_assert(KB == 2, "packed rows need KB = 2 or a multiple of 4");
+        rv2[0] = *reinterpret_cast<const f32x2 *>(rs + j * 2);
     }
 }
 

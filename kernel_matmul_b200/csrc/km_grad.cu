@@ -79,13 +79,20 @@ __global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN)
     for (int64_t k0 = 0; k0 < a.k; k0 += KB) {
         // left values of this thread's rows for this block of columns (zero for masked rows /
         // columns, which makes their coefficients vanish)
+        constexpr bool PACKED = (KB % 2 == 0);
+        constexpr int KB2 = PACKED ? KB / 2 : 1;
         float lv[RPT][KB];
+        f32x2 lv2[RPT][KB2];
 #pragma unroll
         for (int i = 0; i < RPT; i++) {
             const int64_t row = row_base + 32 * i;
 #pragma unroll
             for (int c = 0; c < KB; c++)
                 lv[i][c] = (row < a.m && k0 + c < a.k) ? left[row * a.left.s0 + (k0 + c) * a.left.s1] : 0.0f;
+            if constexpr (PACKED) {
+#pragma unroll
+                for (int c = 0; c < KB2; c++) lv2[i][c] = pack2(lv[i][2 * c], lv[i][2 * c + 1]);
+            }
         }
         const bool vec = (KB % 4 == 0) && a.right_vec_ok && (k0 + KB <= a.k);
 
@@ -115,24 +122,29 @@ __global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN)
 #pragma unroll 2
             for (int j = wn; j < cnt; j += WN) {
                 const float xj = xs[j];
-                float rv[KB];
-                load_staged_row<KB>(rs, j, rv);
+                if constexpr (PACKED) {
+                    // even / odd columns accumulate in the two halves of one packed register
+                    f32x2 rv2[KB2];
+                    load_staged_row2<KB>(rs, j, rv2);
 #pragma unroll
-                for (int i = 0; i < RPT; i++) {
-                    float coeff = 0.0f;
-                    if constexpr (KB >= 8) {
-                        float c1 = 0.0f;
+                    for (int i = 0; i < RPT; i++) {
+                        f32x2 c2 = 0ull;
 #pragma unroll
-                        for (int c = 0; c < KB; c += 2) {
-                            coeff = fmaf(lv[i][c], rv[c], coeff);
-                            c1 = fmaf(lv[i][c + 1], rv[c + 1], c1);
-                        }
-                        coeff += c1;
-                    } else {
+                        for (int c = 0; c < KB2; c++) c2 = fma2(lv2[i][c], rv2[c], c2);
+                        float ce, co;
+                        unpack2(c2, ce, co);
+                        fn.accumulate(x1r[i] - xj, ce + co, sums);
+                    }
+                } else {
+                    float rv[KB];
+                    load_staged_row<KB>(rs, j, rv);
+#pragma unroll
+                    for (int i = 0; i < RPT; i++) {
+                        float coeff = 0.0f;
 #pragma unroll
                         for (int c = 0; c < KB; c++) coeff = fmaf(lv[i][c], rv[c], coeff);
+                        fn.accumulate(x1r[i] - xj, coeff, sums);
                     }
-                    fn.accumulate(x1r[i] - xj, coeff, sums);
                 }
             }
             __syncthreads();

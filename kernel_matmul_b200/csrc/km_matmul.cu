@@ -29,7 +29,7 @@ struct MatmulArgs {
 };
 
 template <int KT, int KB, int RPT, int WN>
-__global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN)
+__global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN, 512 / (32 * (128 / (32 * RPT)) * WN))
     matmul_fma_kernel(const MatmulArgs<float> a) {
     constexpr int WM = 128 / (32 * RPT);
     constexpr int THREADS = 32 * WM * WN;
@@ -74,11 +74,18 @@ __global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN)
         x1r[i] = row < a.m ? x1[row * a.x1.s0] : 0.0f;
     }
 
+    // accumulators: packed pairs (fma.rn.f32x2) whenever the rhs block has an even width
+    constexpr bool PACKED = (KB % 2 == 0);
+    constexpr int KB2 = PACKED ? KB / 2 : 1;
     float acc[RPT][KB];
+    f32x2 acc2[RPT][KB2];
 #pragma unroll
-    for (int i = 0; i < RPT; i++)
+    for (int i = 0; i < RPT; i++) {
 #pragma unroll
         for (int c = 0; c < KB; c++) acc[i][c] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < KB2; c++) acc2[i][c] = 0ull;
+    }
 
     const bool full_kb = (k0 + KB <= a.k);
     const bool vec = (KB % 4 == 0) && a.rhs_vec_ok && full_kb;
@@ -111,16 +118,35 @@ __global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN)
 #pragma unroll 2
         for (int j = wn; j < cnt; j += WN) {
             const float xj = xs[j];
-            float rv[KB];
-            load_staged_row<KB>(rs, j, rv);
+            if constexpr (PACKED) {
+                f32x2 rv2[KB2];
+                load_staged_row2<KB>(rs, j, rv2);
 #pragma unroll
-            for (int i = 0; i < RPT; i++) {
-                const float kv = fn.unscaled(x1r[i] - xj);
+                for (int i = 0; i < RPT; i++) {
+                    const float kv = fn.unscaled(x1r[i] - xj);
+                    const f32x2 kk = pack2(kv, kv);
 #pragma unroll
-                for (int c = 0; c < KB; c++) acc[i][c] = fmaf(kv, rv[c], acc[i][c]);
+                    for (int c = 0; c < KB2; c++) acc2[i][c] = fma2(kk, rv2[c], acc2[i][c]);
+                }
+            } else {
+                float rv[KB];
+                load_staged_row<KB>(rs, j, rv);
+#pragma unroll
+                for (int i = 0; i < RPT; i++) {
+                    const float kv = fn.unscaled(x1r[i] - xj);
+#pragma unroll
+                    for (int c = 0; c < KB; c++) acc[i][c] = fmaf(kv, rv[c], acc[i][c]);
+                }
             }
         }
         __syncthreads();
+    }
+
+    if constexpr (PACKED) {
+#pragma unroll
+        for (int i = 0; i < RPT; i++)
+#pragma unroll
+            for (int c = 0; c < KB2; c++) unpack2(acc2[i][c], acc[i][2 * c], acc[i][2 * c + 1]);
     }
 
     // combine the WN column-interleaved partial sums, scale, store

@@ -114,14 +114,14 @@ def rel_err(actual: torch.Tensor, expected: torch.Tensor, dim=None) -> float:
 
 
 GRAD_RTOL = 1e-5
-GRAD_COND_TOL = 1e-7
+GRAD_COND_TOL = 1e-6
 
 
 def assert_grad_close(actual: torch.Tensor, expected: torch.Tensor, term_scale: torch.Tensor) -> None:
     """Gradient parity criterion.  Every element must satisfy
 
         |actual - expected| <= 1e-5 * |expected|          (relative to the result)
-     or |actual - expected| <= 1e-7 * sum_i |t_i|          (for sums whose terms cancel)
+     or |actual - expected| <= 1e-6 * sum_i |t_i|          (for sums whose terms cancel)
 
     where the t_i are the terms of the sum the gradient consists of and sum |t_i| is computed by
     the fp64 oracle (``absolute=True``).  The second bound is about one fp32 rounding unit of

@@ -136,3 +136,54 @@ def test_index_oracle_matches_dense(O):
     c = torch.randint(0, 500, (5, 40), dtype=torch.int32)
     v = O.index("locally_periodic", ex.x1, ex.x2, ex.params, ex.start, ex.end, (b,), r, c)
     assert torch.equal(v, K[b.long(), r.long(), c.long()])
+
+
+CUDA_GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "cuda_golden.npz")
+
+
+@pytest.mark.parametrize("kt", KERNEL_TYPES)
+def test_oracle_matches_reference_cuda_golden(O, kt):
+    """The fp64 oracle vs the fp32 outputs of the reference's own CUDA kernels (compiled
+    unmodified, run on a B200; tests/golden/make_cuda_golden.py).  The reference computes in
+    fp32, so agreement is to fp32 accuracy: 1e-5 relative for values, and for gradients 1e-4
+    relative or 1e-5 of the sum of term magnitudes (its own tests accept 2e-3)."""
+    g = np.load(CUDA_GOLDEN)
+    t = lambda name: torch.from_numpy(g[f"{kt}_{name}"])  # noqa: E731
+    x1, x2, params, start, end = t("x1"), t("x2"), t("params"), t("start"), t("end")
+
+    def close(actual, ref):
+        return float((actual - ref.double()).abs().max() / ref.double().abs().max())
+
+    def grad_close(actual, ref, scale):
+        err = (actual - ref.double()).abs()
+        return bool(((err <= 1e-4 * actual.abs()) | (err <= 1e-5 * scale)).all())
+
+    assert close(O.matmul(kt, x1, x2, t("rhs"), params, start, end), t("ref_matmul")) <= 1e-5
+    a = O.matmul_bwd(kt, x1, x2, t("rhs"), params, start, end, t("og"))
+    s = O.matmul_bwd(kt, x1, x2, t("rhs"), params, start, end, t("og"), absolute=True)
+    assert grad_close(a, t("ref_matmul_bwd"), s)
+    a = O.bilinear_derivative(kt, x1, x2, t("left"), t("right"), params, start, end)
+    s = O.bilinear_derivative(kt, x1, x2, t("left"), t("right"), params, start, end, absolute=True)
+    assert grad_close(a, t("ref_bilinear"), s)
+    x1d, x2d = x1[:, :160].contiguous(), x2[:, :150].contiguous()
+    dstart, dend = t("dstart"), t("dend")
+    K = O.dense(kt, x1d, x2d, params, dstart, dend)
+    Kref = t("ref_dense")
+    assert close(K, Kref) <= 1e-5
+    assert torch.equal(K == 0, Kref == 0)
+    a = O.dense_bwd(kt, x1d, x2d, params, dstart, dend, t("dg"))
+    s = O.dense_bwd(kt, x1d, x2d, params, dstart, dend, t("dg"), absolute=True)
+    assert grad_close(a, t("ref_dense_bwd"), s)
+    sstart, send = t("sstart"), t("send")
+    v = O.index(kt, x1, x1, params, sstart, send, (t("bidx"),), t("row"), t("col"))
+    vref = t("ref_index")
+    assert close(v, vref) <= 1e-5
+    assert torch.equal(v == 0, vref == 0)  # band membership of every lookup
+    a = O.index_bwd(kt, x1, x1, params, sstart, send, (t("bidx"),), t("row"), t("col"), t("ig"))
+    s = O.index_bwd(kt, x1, x1, params, sstart, send, (t("bidx"),), t("row"), t("col"), t("ig"), absolute=True)
+    assert grad_close(a, t("ref_index_bwd"), s)
+    # the band the GPU box computed with the reference's ranges.cpp equals the oracle's
+    rs, re = O.make_ranges(2.0, x1, x2)
+    assert torch.equal(rs, start) and torch.equal(re, end)
+    rs, re = O.make_ranges(2.0, x1)
+    assert torch.equal(rs, sstart) and torch.equal(re, send)
