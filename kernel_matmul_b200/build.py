@@ -4,7 +4,8 @@ One fixed build: no per-configuration JIT and no autotuning (the reference compi
 extension per op and define set at run time, kernel_matmul/compile.py:49-125).  The library is
 built in-tree next to this file; it has no dependency on PyTorch or Python.
 
-Usage:  python -m kernel_matmul_b200.build [--force] [--verbose]
+Usage:  python kernel_matmul_b200/build.py [--force] [--verbose]
+(run as a script: importing the package itself requires the built library)
 """
 from __future__ import annotations
 
