@@ -113,6 +113,41 @@ KM_API int km_matmul_bwd_f32(int kernel_type, const km_batch *batch, int64_t m, 
                       size_t workspace_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------
+ * km_bilinear_derivative_f32 for callers that cannot hand over a workspace.  It has no
+ * counterpart in the reference (whose ops allocate their temporaries through ATen).
+ *
+ * Some hosts may not allocate device memory at the point where they need this gradient: an
+ * application that has given all of HBM to its own pool has nothing left for cudaMalloc to
+ * return, and a latency-critical loop may forbid allocation calls because they can serialise
+ * the device.  For them the per-row-block partial sums go to a fixed array compiled into the
+ * library instead of a caller buffer.  Same arguments (minus the workspace), same results,
+ * bit for bit, as km_bilinear_derivative_f32; pass left = out_grad and right = rhs for the
+ * matmul_bwd gradient.  The call itself allocates nothing and frees nothing.
+ *
+ * Limits and rules
+ *  - batch count x ceil(m / 128) must not exceed KM_STATIC_GRAD_UNITS (262144 records, 4 MiB);
+ *    larger problems are refused with KM_ERR_UNSUPPORTED and a message, nothing is launched.
+ *  - The array exists once per device and is shared by every call on that device.  Nothing in
+ *    it has to be cleared (each call writes every record it later reads), but two calls whose
+ *    kernels may run at the same time (different streams, different host threads) race on
+ *    it: serialise them.  It occupies its 4 MiB on every GPU that loads the library, until
+ *    the process exits.
+ *  - The first call on each device looks up the array's device address
+ *    (cudaGetSymbolAddress, with that device current) and keeps it.  Make that first call
+ *    before starting any stream capture on that device.  Device ordinals up to
+ *    KM_STATIC_MAX_DEVICES - 1.
+ * ------------------------------------------------------------------------------------- */
+#define KM_STATIC_GRAD_UNITS 262144
+#define KM_STATIC_MAX_DEVICES 64
+
+KM_API int km_bilinear_derivative_static_f32(int kernel_type, const km_batch *batch, int64_t m,
+                                             int64_t n, int64_t k, const km_view *x1,
+                                             const km_view *x2, const km_view *left,
+                                             const km_view *right, const km_view *params,
+                                             const km_view *start, const km_view *end,
+                                             const km_view *grad, void *stream);
+
+/* ---------------------------------------------------------------------------------------
  * Masked dense K: out (B.., m, n), exact zeros outside the band; every element written (no
  * separate zero fill).  Replaces dense.call(x1, x2, params, start, end)
  * (native/dense/dense.cpp:6-17, native/dense/dense.cu:73-98).

@@ -37,7 +37,7 @@ class KmError(RuntimeError):
 def _load() -> ctypes.CDLL:
     if not os.path.exists(LIB_PATH):
         raise ImportError(
-            f"{LIB_PATH} not found: build it with `python -m kernel_matmul_b200.build` "
+            f"{LIB_PATH} not found: build it with `python kernel_matmul_b200/build.py` "
             "(nvcc, sm_100a). There is no CPU or PyTorch fallback."
         )
     lib = ctypes.CDLL(LIB_PATH)
@@ -57,6 +57,8 @@ def _load() -> ctypes.CDLL:
     lib.km_bilinear_derivative_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, wp, vp, sz, vp]
     lib.km_matmul_bwd_f32.restype = ctypes.c_int
     lib.km_matmul_bwd_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, wp, vp, sz, vp]
+    lib.km_bilinear_derivative_static_f32.restype = ctypes.c_int
+    lib.km_bilinear_derivative_static_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, wp, vp]
     lib.km_dense_f32.restype = ctypes.c_int
     lib.km_dense_f32.argtypes = [ctypes.c_int, bp, i64, i64, wp, wp, wp, wp, wp, wp, vp]
     lib.km_dense_bwd_f32.restype = ctypes.c_int
@@ -85,7 +87,7 @@ lib = _load()
 
 EXPORTED = [
     "km_last_error", "km_version", "km_num_params", "km_matmul_f32", "km_grad_workspace_bytes",
-    "km_bilinear_derivative_f32", "km_matmul_bwd_f32", "km_dense_f32", "km_dense_bwd_f32",
+    "km_bilinear_derivative_f32", "km_bilinear_derivative_static_f32", "km_matmul_bwd_f32", "km_dense_f32", "km_dense_bwd_f32",
     "km_index_f32", "km_index_bwd_workspace_bytes", "km_index_bwd_f32", "km_make_ranges_f32",
     "km_make_ranges_symmetric_f32", "km_transpose_ranges_i32", "km_count_entries",
     "km_probe_fp32_peak",

@@ -13,6 +13,8 @@
 // reduced warp-shuffle -> shared memory -> one partial per (batch, row block) in the
 // workspace; a second small kernel adds the partials of a batch in a fixed order in fp64 and
 // applies the chain rule theta <- p, so results are deterministic.
+#include <mutex>
+
 #include "km_common.cuh"
 
 namespace km {
@@ -313,7 +315,61 @@ static int grad_entry(const char *name, int kernel_type, const km_batch *batch, 
     return launch_grad_finish(kernel_type, a.batch, a.row_blocks, a.partials, false, a.params, a.grad, s);
 }
 
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant: the partial sums live in a fixed array inside the library image.
+// ---------------------------------------------------------------------------------------
+
+// One record of KM_MAX_PARAMS floats per (batch, row block).  Lives in every CUDA context
+// that loads the library, for the lifetime of that context.
+static __device__ __align__(256) float g_static_partials[KM_STATIC_GRAD_UNITS * KM_MAX_PARAMS];
+
+static std::mutex g_static_mutex;
+static void *g_static_ptr[KM_STATIC_MAX_DEVICES] = {nullptr};
+
+// Device address of g_static_partials on the current device.  In host code the array's name is
+// only a handle for the runtime, not an address a kernel could use, so it is translated with
+// cudaGetSymbolAddress once per device (with that device current) and remembered.
+static int static_partials_address(void **out) {
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return cuda_fail(err, "km_bilinear_derivative_static_f32: cudaGetDevice");
+    KM_REQUIRE(dev >= 0 && dev < KM_STATIC_MAX_DEVICES, KM_ERR_UNSUPPORTED,
+               "km_bilinear_derivative_static_f32: device ordinal %d not below %d", dev, KM_STATIC_MAX_DEVICES);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_ptr[dev] == nullptr) {
+        void *p = nullptr;
+        err = cudaGetSymbolAddress(&p, g_static_partials);
+        if (err != cudaSuccess) return cuda_fail(err, "km_bilinear_derivative_static_f32: cudaGetSymbolAddress");
+        KM_REQUIRE(p != nullptr, KM_ERR_CUDA, "km_bilinear_derivative_static_f32: null symbol address");
+        g_static_ptr[dev] = p;
+    }
+    *out = g_static_ptr[dev];
+    return KM_OK;
+}
+
 }  // namespace km
+
+extern "C" int km_bilinear_derivative_static_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
+                                                 int64_t k, const km_view *x1, const km_view *x2,
+                                                 const km_view *left, const km_view *right,
+                                                 const km_view *params, const km_view *start,
+                                                 const km_view *end, const km_view *grad, void *stream) {
+    using namespace km;
+    KM_REQUIRE(batch != nullptr && m >= 0, KM_ERR_INVALID_ARGUMENT, "km_bilinear_derivative_static_f32: bad arguments");
+    Batch b;
+    int rc = make_batch(batch, &b);
+    if (rc != KM_OK) return rc;
+    const int64_t units = b.count * ceil_div(m, KM_BLOCK_SIZE);
+    KM_REQUIRE(units <= (int64_t)KM_STATIC_GRAD_UNITS, KM_ERR_UNSUPPORTED,
+               "km_bilinear_derivative_static_f32: batch count x row blocks = %lld exceeds the built-in scratch of "
+               "%d records; use km_bilinear_derivative_f32 with a caller-provided workspace",
+               (long long)units, KM_STATIC_GRAD_UNITS);
+    void *scratch = nullptr;
+    rc = static_partials_address(&scratch);
+    if (rc != KM_OK) return rc;
+    return grad_entry("km_bilinear_derivative_static_f32", kernel_type, batch, m, n, k, x1, x2, left, right, params,
+                      start, end, grad, scratch, sizeof(float) * KM_STATIC_GRAD_UNITS * KM_MAX_PARAMS, stream);
+}
 
 extern "C" size_t km_grad_workspace_bytes(int kernel_type, const km_batch *batch, int64_t m) {
     (void)kernel_type;
