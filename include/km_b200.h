@@ -88,6 +88,25 @@ KM_API int km_matmul_f32(int kernel_type, const km_batch *batch, int64_t m, int6
                   const km_view *out, void *stream);
 
 /* ---------------------------------------------------------------------------------------
+ * The same product for a window of row blocks, optionally summed over the batch:
+ *   rows [row_block_begin * 128, (row_block_begin + row_block_count) * 128) (clipped to m) only;
+ *   out row 0 is row row_block_begin * 128, i.e. out is (B.., rows_in_window, k);
+ *   sum_batches != 0: out (rows_in_window, k) = sum_b K_b . rhs_b, accumulated in registers
+ *   inside one CTA per row block -- no (B.., m, k) intermediate.  out's batch strides are ignored.
+ * row_block_count < 0 means "to the last row block".
+ * The window is how the product is sharded by rows over GPUs: every rank holds x, rhs and the
+ * bands in full and computes its own row blocks (there is no dependence between row blocks).
+ * The batch sum is the product with the reference's SumKernel operator
+ * (kernel_matmul/gpytorch/sum.py:16-24: the batched operator summed over its batch dim), which
+ * the reference evaluates as B separate products followed by a sum.
+ * ------------------------------------------------------------------------------------- */
+KM_API int km_matmul_rows_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
+                              int64_t k, const km_view *x1, const km_view *x2,
+                              const km_view *rhs, const km_view *params, const km_view *start,
+                              const km_view *end, const km_view *out, int64_t row_block_begin,
+                              int64_t row_block_count, int32_t sum_batches, void *stream);
+
+/* ---------------------------------------------------------------------------------------
  * grad[b, q] = d/d theta_q  sum_{i, j in band, c} left[b,i,c] * kappa(x1[b,i], x2[b,j]) * right[b,j,c]
  * Replaces bilinear_derivative.call(x1, x2, left, right, params, start, end)
  * (native/bilinear_derivative/bilinear_derivative.cpp:6-21, .cu:138-183) and, with

@@ -19,7 +19,8 @@ template <typename T>
 struct MatmulArgs {
     Batch batch;
     int64_t m, n, k;
-    int64_t row_blocks;  // ceil(m / 128)
+    int64_t row_blocks;  // row blocks computed by this launch
+    int64_t rb_begin;    // first row block of the window; out row 0 is row rb_begin * 128
     int k_blocks;        // ceil(k / KB)
     View<const float> x1, x2, rhs, params;
     View<const int> start, end;
@@ -28,67 +29,19 @@ struct MatmulArgs {
     int out_vec_ok;  // out rows may be stored 16 bytes at a time
 };
 
-template <int KT, int KB, int RPT, int WN>
-__global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN, 512 / (32 * (128 / (32 * RPT)) * WN))
-    matmul_fma_kernel(const MatmulArgs<float> a) {
+// Walks the band [band_lo, band_hi) of one row block and one batch and adds
+// kappa(x1r[i], x2[j]) * rhs[j, k0 + c] (times `kscale` if SCALED) to the accumulators.
+template <int KT, int KB, int RPT, int WN, bool SCALED>
+__device__ __forceinline__ void band_walk(const MatmulArgs<float> &a, const KernelFn<KT> &fn, const float *x2,
+                                          const float *rhs, const float (&x1r)[RPT], const int band_lo,
+                                          const int band_hi, const int64_t k0, const bool vec, float *smem,
+                                          const int tid, const int wn, const float kscale,
+                                          float (&acc)[RPT][KB], f32x2 (&acc2)[RPT][(KB % 2 == 0) ? KB / 2 : 1]) {
     constexpr int WM = 128 / (32 * RPT);
     constexpr int THREADS = 32 * WM * WN;
     constexpr int STAGE_FLOATS = TILE_N * KB + TILE_N;  // rhs tile then x2 tile
-
-    extern __shared__ __align__(16) float smem[];
-
-    const int tid = threadIdx.x;
-    const int lane = tid & 31;
-    const int warp = tid >> 5;
-    const int wm = warp % WM;
-    const int wn = warp / WM;
-
-    // work item: batch fastest so that CTAs resident together share rhs / x2 tiles in L2
-    int64_t item = blockIdx.x;
-    const int64_t b = item % a.batch.count;
-    item /= a.batch.count;
-    const int64_t r = item % a.row_blocks;
-    const int kb = (int)(item / a.row_blocks);
-    const int64_t k0 = (int64_t)kb * KB;
-
-    const BatchIndex bi = decompose(a.batch, b);
-    const float *x1 = batch_ptr(a.x1, bi);
-    const float *x2 = batch_ptr(a.x2, bi);
-    const float *rhs = batch_ptr(a.rhs, bi);
-    const float *theta = batch_ptr(a.params, bi);
-    float *out = batch_ptr(a.out, bi);
-
-    KernelFn<KT> fn;
-    fn.init(theta, a.params.s0);
-
-    const int n = (int)a.n;
-    const int band_lo = clamp_int(batch_ptr(a.start, bi)[r * a.start.s0], 0, n);
-    const int band_hi = max(band_lo, min(batch_ptr(a.end, bi)[r * a.end.s0], n));
-
-    // rows of this thread
-    float x1r[RPT];
-    const int64_t row_base = r * KM_BLOCK_SIZE + wm * (32 * RPT) + lane;
-#pragma unroll
-    for (int i = 0; i < RPT; i++) {
-        const int64_t row = row_base + 32 * i;
-        x1r[i] = row < a.m ? x1[row * a.x1.s0] : 0.0f;
-    }
-
-    // accumulators: packed pairs (fma.rn.f32x2) whenever the rhs block has an even width
     constexpr bool PACKED = (KB % 2 == 0);
     constexpr int KB2 = PACKED ? KB / 2 : 1;
-    float acc[RPT][KB];
-    f32x2 acc2[RPT][KB2];
-#pragma unroll
-    for (int i = 0; i < RPT; i++) {
-#pragma unroll
-        for (int c = 0; c < KB; c++) acc[i][c] = 0.0f;
-#pragma unroll
-        for (int c = 0; c < KB2; c++) acc2[i][c] = 0ull;
-    }
-
-    const bool full_kb = (k0 + KB <= a.k);
-    const bool vec = (KB % 4 == 0) && a.rhs_vec_ok && full_kb;
 
     auto stage_tile = [&](int buf, int n0) {
         float *rs = smem + buf * STAGE_FLOATS;
@@ -123,7 +76,8 @@ __global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN, 512 / (32 * (128
                 load_staged_row2<KB>(rs, j, rv2);
 #pragma unroll
                 for (int i = 0; i < RPT; i++) {
-                    const float kv = fn.unscaled(x1r[i] - xj);
+                    float kv = fn.unscaled(x1r[i] - xj);
+                    if (SCALED) kv *= kscale;
                     const f32x2 kk = pack2(kv, kv);
 #pragma unroll
                     for (int c = 0; c < KB2; c++) acc2[i][c] = fma2(kk, rv2[c], acc2[i][c]);
@@ -133,7 +87,8 @@ __global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN, 512 / (32 * (128
                 load_staged_row<KB>(rs, j, rv);
 #pragma unroll
                 for (int i = 0; i < RPT; i++) {
-                    const float kv = fn.unscaled(x1r[i] - xj);
+                    float kv = fn.unscaled(x1r[i] - xj);
+                    if (SCALED) kv *= kscale;
 #pragma unroll
                     for (int c = 0; c < KB; c++) acc[i][c] = fmaf(kv, rv[c], acc[i][c]);
                 }
@@ -141,19 +96,22 @@ __global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN, 512 / (32 * (128
         }
         __syncthreads();
     }
+}
 
-    if constexpr (PACKED) {
-#pragma unroll
-        for (int i = 0; i < RPT; i++)
-#pragma unroll
-            for (int c = 0; c < KB2; c++) unpack2(acc2[i][c], acc[i][2 * c], acc[i][2 * c + 1]);
-    }
-
-    // combine the WN column-interleaved partial sums, scale, store
-    const float scale = fn.scale;
+// Combines the WN column-interleaved partial sums of a CTA through shared memory, applies
+// `scale` and stores the 128 x KB output tile (rows relative to out_row0).
+template <int KB, int RPT, int WN>
+__device__ __forceinline__ void store_tile(const MatmulArgs<float> &a, float *out, const int64_t r,
+                                           const int64_t out_row0, const int64_t k0, const float scale,
+                                           float *smem, const int tid, float (&acc)[RPT][KB]) {
+    constexpr int WM = 128 / (32 * RPT);
+    constexpr int THREADS = 32 * WM * WN;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int wm = warp % WM;
+    const int wn = warp / WM;
     if constexpr (WN > 1) {
-        // red[wn][row_local][KB]
-        float *red = smem;
+        float *red = smem;  // red[wn][row_local][KB]
 #pragma unroll
         for (int i = 0; i < RPT; i++) {
             const int row_local = wm * (32 * RPT) + lane + 32 * i;
@@ -168,35 +126,166 @@ __global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN, 512 / (32 * (128
                 float s = 0.0f;
 #pragma unroll
                 for (int w = 0; w < WN; w++) s += red[(w * 128 + row_local) * KB + c];
-                out[row * a.out.s0 + (k0 + c) * a.out.s1] = s * scale;
+                out[(row - out_row0) * a.out.s0 + (k0 + c) * a.out.s1] = s * scale;
             }
         }
     } else {
 #pragma unroll
         for (int i = 0; i < RPT; i++) {
-            const int64_t row = row_base + 32 * i;
+            const int64_t row = r * KM_BLOCK_SIZE + wm * (32 * RPT) + lane + 32 * i;
             if (row < a.m) {
 #pragma unroll
                 for (int c = 0; c < KB; c++)
-                    if (k0 + c < a.k) out[row * a.out.s0 + (k0 + c) * a.out.s1] = acc[i][c] * scale;
+                    if (k0 + c < a.k) out[(row - out_row0) * a.out.s0 + (k0 + c) * a.out.s1] = acc[i][c] * scale;
             }
         }
     }
 }
 
+// One CTA per (batch, row block, block of KB rhs columns).
+//
+// 3 CTAs of 128 threads per SM: up to 168 registers per thread.  With the register file capped
+// for a 4th CTA (128 registers) the compiler can no longer keep the operands of two columns in
+// flight and the kernel is 10 % slower despite the extra warps.
 template <int KT, int KB, int RPT, int WN>
+__global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN, 384 / (32 * (128 / (32 * RPT)) * WN))
+    matmul_fma_kernel(const MatmulArgs<float> a) {
+    constexpr int WM = 128 / (32 * RPT);
+    extern __shared__ __align__(16) float smem[];
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int wm = warp % WM;
+    const int wn = warp / WM;
+
+    // work item: batch fastest so that CTAs resident together share rhs / x2 tiles in L2
+    int64_t item = blockIdx.x;
+    const int64_t b = item % a.batch.count;
+    item /= a.batch.count;
+    const int64_t r = a.rb_begin + item % a.row_blocks;
+    const int kb = (int)(item / a.row_blocks);
+    const int64_t k0 = (int64_t)kb * KB;
+
+    const BatchIndex bi = decompose(a.batch, b);
+    const float *x1 = batch_ptr(a.x1, bi);
+    const float *x2 = batch_ptr(a.x2, bi);
+    const float *rhs = batch_ptr(a.rhs, bi);
+    float *out = batch_ptr(a.out, bi);
+
+    KernelFn<KT> fn;
+    fn.init(batch_ptr(a.params, bi), a.params.s0);
+
+    const int n = (int)a.n;
+    const int band_lo = clamp_int(batch_ptr(a.start, bi)[r * a.start.s0], 0, n);
+    const int band_hi = max(band_lo, min(batch_ptr(a.end, bi)[r * a.end.s0], n));
+
+    float x1r[RPT];
+    const int64_t row_base = r * KM_BLOCK_SIZE + wm * (32 * RPT) + lane;
+#pragma unroll
+    for (int i = 0; i < RPT; i++) {
+        const int64_t row = row_base + 32 * i;
+        x1r[i] = row < a.m ? x1[row * a.x1.s0] : 0.0f;
+    }
+
+    // accumulators: packed pairs (fma.rn.f32x2) whenever the rhs block has an even width
+    constexpr bool PACKED = (KB % 2 == 0);
+    constexpr int KB2 = PACKED ? KB / 2 : 1;
+    float acc[RPT][KB];
+    f32x2 acc2[RPT][KB2];
+#pragma unroll
+    for (int i = 0; i < RPT; i++) {
+#pragma unroll
+        for (int c = 0; c < KB; c++) acc[i][c] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < KB2; c++) acc2[i][c] = 0ull;
+    }
+
+    const bool vec = (KB % 4 == 0) && a.rhs_vec_ok && (k0 + KB <= a.k);
+    band_walk<KT, KB, RPT, WN, false>(a, fn, x2, rhs, x1r, band_lo, band_hi, k0, vec, smem, tid, wn, 1.0f, acc, acc2);
+
+    if constexpr (PACKED) {
+#pragma unroll
+        for (int i = 0; i < RPT; i++)
+#pragma unroll
+            for (int c = 0; c < KB2; c++) unpack2(acc2[i][c], acc[i][2 * c], acc[i][2 * c + 1]);
+    }
+    store_tile<KB, RPT, WN>(a, out, r, a.rb_begin * KM_BLOCK_SIZE, k0, fn.scale, smem, tid, acc);
+}
+
+// One CTA per (row block, block of KB rhs columns): adds the products of ALL batches
+// (components of a sum kernel) in registers; each batch's output scale goes into its kernel
+// values.  out has no batch dimension.
+template <int KT, int KB, int RPT, int WN>
+__global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN, 384 / (32 * (128 / (32 * RPT)) * WN))
+    matmul_sum_fma_kernel(const MatmulArgs<float> a) {
+    constexpr int WM = 128 / (32 * RPT);
+    extern __shared__ __align__(16) float smem[];
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int wm = warp % WM;
+    const int wn = warp / WM;
+
+    const int64_t item = blockIdx.x;
+    const int64_t r = a.rb_begin + item % a.row_blocks;
+    const int64_t k0 = (item / a.row_blocks) * KB;
+    const int n = (int)a.n;
+    const int64_t row_base = r * KM_BLOCK_SIZE + wm * (32 * RPT) + lane;
+
+    constexpr bool PACKED = (KB % 2 == 0);
+    constexpr int KB2 = PACKED ? KB / 2 : 1;
+    float acc[RPT][KB];
+    f32x2 acc2[RPT][KB2];
+#pragma unroll
+    for (int i = 0; i < RPT; i++) {
+#pragma unroll
+        for (int c = 0; c < KB; c++) acc[i][c] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < KB2; c++) acc2[i][c] = 0ull;
+    }
+    const bool vec = (KB % 4 == 0) && a.rhs_vec_ok && (k0 + KB <= a.k);
+
+    for (int64_t b = 0; b < a.batch.count; b++) {
+        const BatchIndex bi = decompose(a.batch, b);
+        const float *x1 = batch_ptr(a.x1, bi);
+        KernelFn<KT> fn;
+        fn.init(batch_ptr(a.params, bi), a.params.s0);
+        const int band_lo = clamp_int(batch_ptr(a.start, bi)[r * a.start.s0], 0, n);
+        const int band_hi = max(band_lo, min(batch_ptr(a.end, bi)[r * a.end.s0], n));
+        float x1r[RPT];
+#pragma unroll
+        for (int i = 0; i < RPT; i++) {
+            const int64_t row = row_base + 32 * i;
+            x1r[i] = row < a.m ? x1[row * a.x1.s0] : 0.0f;
+        }
+        band_walk<KT, KB, RPT, WN, true>(a, fn, batch_ptr(a.x2, bi), batch_ptr(a.rhs, bi), x1r, band_lo, band_hi, k0,
+                                         vec, smem, tid, wn, fn.scale, acc, acc2);
+    }
+
+    if constexpr (PACKED) {
+#pragma unroll
+        for (int i = 0; i < RPT; i++)
+#pragma unroll
+            for (int c = 0; c < KB2; c++) unpack2(acc2[i][c], acc[i][2 * c], acc[i][2 * c + 1]);
+    }
+    store_tile<KB, RPT, WN>(a, a.out.data, r, a.rb_begin * KM_BLOCK_SIZE, k0, 1.0f, smem, tid, acc);
+}
+
+template <int KT, int KB, int RPT, int WN, bool SUM>
 static int launch_matmul(const MatmulArgs<float> &a, cudaStream_t stream) {
     constexpr int WM = 128 / (32 * RPT);
     constexpr int THREADS = 32 * WM * WN;
     constexpr size_t stage_bytes = 2 * (TILE_N * KB + TILE_N) * sizeof(float);
     constexpr size_t red_bytes = WN > 1 ? (size_t)WN * 128 * KB * sizeof(float) : 0;
     constexpr size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
-    auto kernel = matmul_fma_kernel<KT, KB, RPT, WN>;
+    auto kernel = SUM ? matmul_sum_fma_kernel<KT, KB, RPT, WN> : matmul_fma_kernel<KT, KB, RPT, WN>;
     if (smem > 48 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(matmul)");
     }
-    const int64_t items = a.batch.count * a.row_blocks * a.k_blocks;
+    const int64_t items = (SUM ? 1 : a.batch.count) * a.row_blocks * a.k_blocks;
     if (items > 0x7fffffffLL) {
         set_error("km_matmul_f32: too many work items (%lld)", (long long)items);
         return KM_ERR_UNSUPPORTED;
@@ -206,42 +295,48 @@ static int launch_matmul(const MatmulArgs<float> &a, cudaStream_t stream) {
     return KM_OK;
 }
 
-template <int KT>
+template <int KT, bool SUM>
 static int dispatch_matmul(MatmulArgs<float> &a, cudaStream_t stream) {
     const int64_t k = a.k;
     auto with_kb = [&](int kb) { a.k_blocks = (int)ceil_div(k, kb); };
-    if (k <= 1) { with_kb(1); return launch_matmul<KT, 1, 4, 4>(a, stream); }
-    if (k <= 2) { with_kb(2); return launch_matmul<KT, 2, 4, 4>(a, stream); }
-    if (k <= 4) { with_kb(4); return launch_matmul<KT, 4, 4, 4>(a, stream); }
-    if (k <= 8) { with_kb(8); return launch_matmul<KT, 8, 4, 4>(a, stream); }
-    if (k <= 16) { with_kb(16); return launch_matmul<KT, 16, 4, 4>(a, stream); }
+    if (k <= 1) { with_kb(1); return launch_matmul<KT, 1, 4, 4, SUM>(a, stream); }
+    if (k <= 2) { with_kb(2); return launch_matmul<KT, 2, 4, 4, SUM>(a, stream); }
+    if (k <= 4) { with_kb(4); return launch_matmul<KT, 4, 4, 4, SUM>(a, stream); }
+    if (k <= 8) { with_kb(8); return launch_matmul<KT, 8, 4, 4, SUM>(a, stream); }
+    if (k <= 16) { with_kb(16); return launch_matmul<KT, 16, 4, 4, SUM>(a, stream); }
     with_kb(32);
-    return launch_matmul<KT, 32, 2, 2>(a, stream);
+    return launch_matmul<KT, 32, 2, 2, SUM>(a, stream);
 }
 
-}  // namespace km
-
-extern "C" int km_matmul_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
-                             const km_view *x1, const km_view *x2, const km_view *rhs,
-                             const km_view *params, const km_view *start, const km_view *end,
-                             const km_view *out, void *stream) {
-    using namespace km;
-    KM_REQUIRE(valid_kernel_type(kernel_type), KM_ERR_INVALID_ARGUMENT, "km_matmul_f32: unknown kernel type %d", kernel_type);
-    KM_REQUIRE(batch && x1 && x2 && rhs && params && start && end && out, KM_ERR_INVALID_ARGUMENT,
-               "km_matmul_f32: null argument");
+static int matmul_entry(const char *name, int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
+                        const km_view *x1, const km_view *x2, const km_view *rhs, const km_view *params,
+                        const km_view *start, const km_view *end, const km_view *out, int64_t rb_begin,
+                        int64_t rb_count, bool sum_batches, void *stream) {
+    KM_REQUIRE(valid_kernel_type(kernel_type), KM_ERR_INVALID_ARGUMENT, "%s: unknown kernel type %d", name, kernel_type);
+    KM_REQUIRE(batch && x1 && x2 && rhs && params && start && end && out, KM_ERR_INVALID_ARGUMENT, "%s: null argument", name);
     KM_REQUIRE(m >= 0 && n >= 0 && k >= 0 && n <= 0x7fffffffLL && m <= 0x7fffffffLL * 64, KM_ERR_INVALID_ARGUMENT,
-               "km_matmul_f32: bad sizes m=%lld n=%lld k=%lld", (long long)m, (long long)n, (long long)k);
+               "%s: bad sizes m=%lld n=%lld k=%lld", name, (long long)m, (long long)n, (long long)k);
     MatmulArgs<float> a;
     int rc = make_batch(batch, &a.batch);
     if (rc != KM_OK) return rc;
-    if (a.batch.count == 0 || m == 0 || k == 0) return KM_OK;
+    const int64_t total_blocks = ceil_div(m, KM_BLOCK_SIZE);
+    if (rb_count < 0) rb_count = total_blocks - rb_begin;
+    KM_REQUIRE(rb_begin >= 0 && rb_count >= 0 && rb_begin + rb_count <= total_blocks, KM_ERR_INVALID_ARGUMENT,
+               "%s: row-block window [%lld, %lld) outside [0, %lld)", name, (long long)rb_begin,
+               (long long)(rb_begin + rb_count), (long long)total_blocks);
+    if (a.batch.count == 0 || rb_count == 0 || k == 0) {
+        KM_REQUIRE(!(sum_batches && a.batch.count == 0 && rb_count > 0 && k > 0), KM_ERR_INVALID_ARGUMENT,
+                   "%s: summing over an empty batch is not supported", name);
+        return KM_OK;
+    }
     KM_REQUIRE(x1->data && out->data && params->data && start->data && end->data, KM_ERR_INVALID_ARGUMENT,
-               "km_matmul_f32: null data pointer");
-    KM_REQUIRE(n == 0 || (x2->data && rhs->data), KM_ERR_INVALID_ARGUMENT, "km_matmul_f32: null data pointer");
+               "%s: null data pointer", name);
+    KM_REQUIRE(n == 0 || (x2->data && rhs->data), KM_ERR_INVALID_ARGUMENT, "%s: null data pointer", name);
     a.m = m;
     a.n = n;
     a.k = k;
-    a.row_blocks = ceil_div(m, KM_BLOCK_SIZE);
+    a.row_blocks = rb_count;
+    a.rb_begin = rb_begin;
     a.x1 = make_view<const float>(x1, a.batch);
     a.x2 = make_view<const float>(x2, a.batch);
     a.rhs = make_view<const float>(rhs, a.batch);
@@ -252,9 +347,35 @@ extern "C" int km_matmul_f32(int kernel_type, const km_batch *batch, int64_t m, 
     a.rhs_vec_ok = rows_vectorizable(a.rhs, a.batch) ? 1 : 0;
     a.out_vec_ok = 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    switch (kernel_type) {
-    case KM_KERNEL_RBF: return dispatch_matmul<KM_KERNEL_RBF>(a, s);
-    case KM_KERNEL_SPECTRAL: return dispatch_matmul<KM_KERNEL_SPECTRAL>(a, s);
-    default: return dispatch_matmul<KM_KERNEL_LOCALLY_PERIODIC>(a, s);
+    if (sum_batches) {
+        switch (kernel_type) {
+        case KM_KERNEL_RBF: return dispatch_matmul<KM_KERNEL_RBF, true>(a, s);
+        case KM_KERNEL_SPECTRAL: return dispatch_matmul<KM_KERNEL_SPECTRAL, true>(a, s);
+        default: return dispatch_matmul<KM_KERNEL_LOCALLY_PERIODIC, true>(a, s);
+        }
     }
+    switch (kernel_type) {
+    case KM_KERNEL_RBF: return dispatch_matmul<KM_KERNEL_RBF, false>(a, s);
+    case KM_KERNEL_SPECTRAL: return dispatch_matmul<KM_KERNEL_SPECTRAL, false>(a, s);
+    default: return dispatch_matmul<KM_KERNEL_LOCALLY_PERIODIC, false>(a, s);
+    }
+}
+
+}  // namespace km
+
+extern "C" int km_matmul_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
+                             const km_view *x1, const km_view *x2, const km_view *rhs,
+                             const km_view *params, const km_view *start, const km_view *end,
+                             const km_view *out, void *stream) {
+    return km::matmul_entry("km_matmul_f32", kernel_type, batch, m, n, k, x1, x2, rhs, params, start, end, out, 0, -1,
+                            false, stream);
+}
+
+extern "C" int km_matmul_rows_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
+                                  const km_view *x1, const km_view *x2, const km_view *rhs,
+                                  const km_view *params, const km_view *start, const km_view *end,
+                                  const km_view *out, int64_t row_block_begin, int64_t row_block_count,
+                                  int32_t sum_batches, void *stream) {
+    return km::matmul_entry("km_matmul_rows_f32", kernel_type, batch, m, n, k, x1, x2, rhs, params, start, end, out,
+                            row_block_begin, row_block_count, sum_batches != 0, stream);
 }

@@ -153,6 +153,42 @@ def matmul(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor
     return out
 
 
+def matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor, start: Tensor, end: Tensor,
+                *, row_block_begin: int = 0, row_block_count: int | None = None, sum_batches: bool = False,
+                out: Tensor | None = None) -> Tensor:
+    """``matmul`` restricted to the row blocks ``[row_block_begin, row_block_begin + row_block_count)``
+    and, with ``sum_batches``, summed over all batch dims inside the kernel.
+
+    Returns ``(*batch, rows, k)`` or, with ``sum_batches``, ``(rows, k)``, where ``rows`` is the
+    number of rows of ``x1`` inside the window.  ``out`` may be passed to receive the result
+    (e.g. a rank's slice of an all-gather buffer).
+    """
+    kid, dev, batch, m, n, (x1e, x2e, pe, se, ee, re) = _prep(kernel_type, x1, x2, params, start, end, [(rhs, 2)])
+    if rhs.shape[-2] != n:
+        raise RuntimeError(f"rhs must have n = {n} rows, got {rhs.shape[-2]}")
+    k = rhs.shape[-1]
+    R = -(-m // BLOCK_SIZE)
+    if row_block_count is None:
+        row_block_count = R - row_block_begin
+    if row_block_begin < 0 or row_block_count < 0 or row_block_begin + row_block_count > R:
+        raise RuntimeError(f"row-block window [{row_block_begin}, {row_block_begin + row_block_count}) outside [0, {R})")
+    rows = max(0, min(m, (row_block_begin + row_block_count) * BLOCK_SIZE) - row_block_begin * BLOCK_SIZE)
+    shape = (rows, k) if sum_batches else (*batch, rows, k)
+    if out is None:
+        out = torch.empty(shape, device=dev, dtype=torch.float32)
+    elif tuple(out.shape) != shape or out.dtype != torch.float32 or out.device != dev:
+        raise RuntimeError(f"out must be a float32 tensor of shape {shape} on {dev}")
+    if sum_batches and len(batch) == 0:
+        sum_batches = False  # a single kernel: nothing to sum
+    oute = out.reshape(-1, rows, k) if (len(batch) > KM_MAX_BATCH_DIMS and not sum_batches) else out
+    with torch.cuda.device(dev):
+        check(lib.km_matmul_rows_f32(
+            kid, _km_batch(batch), m, n, k, _view(x1e, 1), _view(x2e, 1), _view(re, 2), _view(pe, 1),
+            _view(se, 1), _view(ee, 1), _view(oute, 2), row_block_begin, row_block_count,
+            1 if sum_batches else 0, _stream(dev)))
+    return out
+
+
 def _grad_call(fn, kernel_type, x1, x2, left, right, params, start, end, swap: bool) -> Tensor:
     kid, dev, batch, m, n, (x1e, x2e, pe, se, ee, le, rte) = _prep(
         kernel_type, x1, x2, params, start, end, [(left, 2), (right, 2)])
@@ -298,6 +334,6 @@ def count_entries(m: int, n: int, start: Tensor, end: Tensor) -> Tensor:
 
 
 __all__ = [
-    "matmul", "matmul_bwd", "bilinear_derivative", "dense", "dense_bwd", "index", "index_bwd",
+    "matmul", "matmul_rows", "matmul_bwd", "bilinear_derivative", "dense", "dense_bwd", "index", "index_bwd",
     "count_entries", "BLOCK_SIZE", "NUM_PARAMS",
 ]
