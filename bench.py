@@ -461,6 +461,141 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
         dist.destroy_process_group()
 
 
+def run_cg(args, rank: int, world: int, local: int) -> None:
+    """Config-5 style workload: (K + sigma^2 I) V = Y by CG, K the sum of 64 spectral components
+    (shared band), rows sharded over the ranks, one NCCL all-gather per iteration.  One step =
+    one CG iteration (sharded product + all-gather + replicated vector updates); total work is
+    fixed, so scaling is strong."""
+    import ctypes
+
+    import kernel_matmul_b200  # noqa: F401
+    from kernel_matmul_b200 import ops, workloads
+    from kernel_matmul_b200._lib import check, lib
+    from kernel_matmul_b200.cg import ShardedOperator, conjugate_gradient
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    w = workloads.cg_sum_kernel() if args.workload == "cg_sum" else workloads.cg_sum_kernel(n=1 << 17, components=8, span=625.0)
+    kt, n, k, B = w.kernel_type, w.n, w.rhs.shape[-1], w.params.shape[0]
+    x = w.x.to(dev)
+    params = w.params.to(dev)
+    y = w.rhs.to(dev)
+    start, end = workloads.band(w, x)
+    E = int(ops.count_entries(n, n, start, end))  # over all components
+    units = float(E) * k
+    op = ShardedOperator.from_kernel(kt, x, params, start[0], end[0], w.extra["sigma2"])
+
+    flops = ctypes.c_double()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+    def probe():
+        check(lib.km_probe_fp32_peak(20000, None, ctypes.byref(flops), stream))
+
+    probe()
+    fp32_peak = max(flops.value / (cuda_ms(probe) * 1e-3) for _ in range(3)) / 1e12
+    sm_clock = fp32_peak * 1e12 / (148 * 128 * 2)
+
+    # state of a running solve: a few iterations are warm-up, then K timed iterations
+    state = {"x": torch.zeros_like(y), "r": y.clone(), "p": y.clone()}
+    state["rs"] = (state["r"] * state["r"]).sum(0)
+    tiny = torch.finfo(torch.float32).tiny
+    mv_ms = []
+
+    def iteration(timed: bool):
+        p, r, xs = state["p"], state["r"], state["x"]
+        if timed:
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+        Ap = op.apply(p)
+        if timed:
+            e1.record()
+        alpha = state["rs"] / (p * Ap).sum(0).clamp_min(tiny)
+        xs.addcmul_(p, alpha)
+        r.addcmul_(Ap, -alpha)
+        rs_new = (r * r).sum(0)
+        p.mul_(rs_new / state["rs"].clamp_min(tiny)).add_(r)
+        state["rs"] = rs_new
+        if timed:
+            return e0, e1
+        return None
+
+    for _ in range(max(args.warmup, 3)):
+        iteration(False)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    t0 = torch.cuda.Event(enable_timing=True)
+    t1 = torch.cuda.Event(enable_timing=True)
+    t0.record()
+    evs = [iteration(True) for _ in range(args.steps)]
+    t1.record()
+    t1.synchronize()
+    total_ms = t0.elapsed_time(t1)
+    apply_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    clocks = sampler.stop()
+
+    # end to end: host y in, solution out, full solve of `iters` iterations
+    iters = int(w.extra["iterations"]) if args.workload == "cg_sum" and world > 1 else min(int(w.extra["iterations"]), 10)
+    hy = w.rhs.contiguous().pin_memory()
+    hx = w.x.pin_memory()
+    hp = w.params.contiguous().pin_memory()
+    hsol = torch.empty(n, k).pin_memory()
+
+    def solve_e2e():
+        dx = hx.to(dev, non_blocking=True)
+        dp = hp.to(dev, non_blocking=True)
+        dy = hy.to(dev, non_blocking=True)
+        st, en = workloads.band(w, dx)
+        o = ShardedOperator.from_kernel(kt, dx, dp, st[0], en[0], w.extra["sigma2"])
+        res = conjugate_gradient(o, dy, iterations=iters)
+        hsol.copy_(res.solution, non_blocking=True)
+
+    e2e_ms = cuda_ms(solve_e2e)
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_ms, apply_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_ms, apply_ms = (float(v) for v in t)
+    if rank == 0:
+        ms_per_step = total_ms / args.steps
+        fp32_instr, sfu = fp32_instr_fwd(kt, k), GEN_FWD[kt][1]
+        e_rank = E / world  # row windows are equal
+        t_apply = apply_ms * 1e-3
+        frac_fp32 = 2.0 * e_rank * fp32_instr / t_apply / 1e12 / fp32_peak
+        sfu_peak = 148 * 16 * sm_clock
+        frac_sfu = e_rank * sfu / t_apply / sfu_peak
+        bound = "sfu" if sfu / 16 > fp32_instr / 128 else "fp32"
+        line = {
+            "metric": METRIC, "value": units / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": w.name, "ops": "CG iteration: batch-summed banded product (rows sharded) + all-gather + vector updates",
+                       "entries_per_matvec": E, "rhs_cols": k, "components": B, "sigma2": w.extra["sigma2"],
+                       "l2": "operands (134 MB vectors) exceed L2", "collective": "all_gather_into_tensor per iteration" if world > 1 else "none"},
+            "roofline": {
+                "bound": bound, "kernel": "matmul_sum_fma_kernel",
+                "achieved": (e_rank * sfu / t_apply / 1e12) if bound == "sfu" else 2.0 * e_rank * fp32_instr / t_apply / 1e12,
+                "peak": sfu_peak / 1e12 if bound == "sfu" else fp32_peak,
+                "unit": "T sfu-op/s" if bound == "sfu" else "TFLOP/s",
+                "frac": frac_sfu if bound == "sfu" else frac_fp32, "traffic": None,
+                "frac_fp32": frac_fp32, "frac_sfu": frac_sfu, "apply_ms_incl_allgather": apply_ms,
+                "peak_source": "SFU peak = 148 SMs x 16 ops/clk x SM clock implied by the live FFMA probe",
+            },
+            "e2e": {"value": units * iters / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": (hy.numel() + hx.numel() + hp.numel()) * 4 // iters,
+                    "d2h_bytes_per_step": hsol.numel() * 4 // iters, "solve_ms": e2e_ms, "iterations": iters},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -472,7 +607,13 @@ def main() -> None:
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.impl == "reference":
+        if args.workload.startswith("cg_sum"):
+            if rank == 0:
+                print(json.dumps({"impl": "reference", "unavailable": "CPU leg implemented for the default workload only"}))
+            return
         run_reference(args, rank, world)
+    elif args.workload.startswith("cg_sum"):
+        run_cg(args, rank, world, local)
     else:
         run_ours(args, rank, world, local)
 

@@ -88,6 +88,27 @@ KM_API int km_matmul_f32(int kernel_type, const km_batch *batch, int64_t m, int6
                   const km_view *out, void *stream);
 
 /* ---------------------------------------------------------------------------------------
+ * The same product on the tensor cores (tcgen05.mma, fp32 accumulators in tensor memory), for
+ * right-hand sides wide enough to make the contraction a dense GEMM.  Same arguments and
+ * result as km_matmul_f32 (to fp32 accuracy: 3xTF32 split operands), plus a workspace of
+ * km_matmul_tc_workspace_bytes(...) bytes, 256-byte aligned, contents irrelevant on entry: a
+ * pre-pass writes the rhs there as hi / lo TF32 tile images in the tensor core's shared-memory
+ * layout, preceded by a 4-byte status word (0 = ok, non-zero = a bounded wait inside the
+ * kernel gave up and the output is invalid; read it with km_workspace_status, which
+ * synchronises the stream).  Replaces the same reference call as km_matmul_f32.
+ * ------------------------------------------------------------------------------------- */
+KM_API size_t km_matmul_tc_workspace_bytes(const km_batch *batch, int64_t n, int64_t k,
+                                           const km_view *rhs);
+
+KM_API int km_matmul_tc_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
+                            int64_t k, const km_view *x1, const km_view *x2, const km_view *rhs,
+                            const km_view *params, const km_view *start, const km_view *end,
+                            const km_view *out, void *workspace, size_t workspace_bytes,
+                            void *stream);
+
+KM_API int km_workspace_status(const void *workspace, int32_t *status_out, void *stream);
+
+/* ---------------------------------------------------------------------------------------
  * The same product for a window of row blocks, optionally summed over the batch:
  *   rows [row_block_begin * 128, (row_block_begin + row_block_count) * 128) (clipped to m) only;
  *   out row 0 is row row_block_begin * 128, i.e. out is (B.., rows_in_window, k);

@@ -135,22 +135,54 @@ def _out_batch(batch: tuple[int, ...]) -> tuple[int, ...]:
     return batch
 
 
-def matmul(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor, start: Tensor, end: Tensor) -> Tensor:
+#: rhs widths from which ``matmul`` runs the contraction on the tensor cores (tcgen05) instead
+#: of the FMA pipe
+TENSOR_CORE_MIN_K = 64
+
+
+def matmul(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor, start: Tensor, end: Tensor,
+           *, path: str = "auto") -> Tensor:
     """``K(x1, x2; params)[masked by ranges] @ rhs`` -> ``(*batch, m, k)``.
 
     Reference: ``matmul.call(x1, x2, rhs, params, start, end)`` (native/matmul/matmul.cpp:6-17).
+    ``path``: ``"fma"`` (FP32 pipe), ``"tc"`` (tensor cores, 3xTF32) or ``"auto"`` (tensor cores
+    from ``TENSOR_CORE_MIN_K`` rhs columns).
     """
     kid, dev, batch, m, n, (x1e, x2e, pe, se, ee, re) = _prep(kernel_type, x1, x2, params, start, end, [(rhs, 2)])
     if rhs.shape[-2] != n:
         raise RuntimeError(f"rhs must have n = {n} rows, got {rhs.shape[-2]}")
     k = rhs.shape[-1]
+    if path not in ("auto", "fma", "tc"):
+        raise ValueError(f"unknown path {path!r}")
     out = torch.empty(*batch, m, k, device=dev, dtype=torch.float32)
     oute = out.reshape(-1, m, k) if len(batch) > KM_MAX_BATCH_DIMS else out
+    if path == "tc" or (path == "auto" and k >= TENSOR_CORE_MIN_K):
+        kb = _km_batch(batch)
+        rv = _view(re, 2)
+        ws_bytes = lib.km_matmul_tc_workspace_bytes(kb, n, k, rv)
+        ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
+        with torch.cuda.device(dev):
+            check(lib.km_matmul_tc_f32(
+                kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), rv, _view(pe, 1), _view(se, 1), _view(ee, 1),
+                _view(oute, 2), ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
+        out._km_workspace = ws  # keeps the status word reachable for tc_status()
+        return out
     with torch.cuda.device(dev):
         check(lib.km_matmul_f32(
             kid, _km_batch(batch), m, n, k, _view(x1e, 1), _view(x2e, 1), _view(re, 2), _view(pe, 1),
             _view(se, 1), _view(ee, 1), _view(oute, 2), _stream(dev)))
     return out
+
+
+def tc_status(out: Tensor) -> int:
+    """Status word of the tensor-core product that produced ``out`` (synchronises): 0 = ok."""
+    ws = getattr(out, "_km_workspace", None)
+    if ws is None:
+        return 0
+    status = ctypes.c_int32(-1)
+    with torch.cuda.device(ws.device):
+        check(lib.km_workspace_status(ctypes.c_void_p(ws.data_ptr()), ctypes.byref(status), _stream(ws.device)))
+    return int(status.value)
 
 
 def matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor, start: Tensor, end: Tensor,
@@ -334,6 +366,6 @@ def count_entries(m: int, n: int, start: Tensor, end: Tensor) -> Tensor:
 
 
 __all__ = [
-    "matmul", "matmul_rows", "matmul_bwd", "bilinear_derivative", "dense", "dense_bwd", "index", "index_bwd",
+    "matmul", "matmul_rows", "tc_status", "matmul_bwd", "bilinear_derivative", "dense", "dense_bwd", "index", "index_bwd",
     "count_entries", "BLOCK_SIZE", "NUM_PARAMS",
 ]
