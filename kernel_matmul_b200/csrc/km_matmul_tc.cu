@@ -18,9 +18,9 @@
 // dropped lo*lo term and the truncation of lo are ~2^-21 relative.  The tensor core adds into
 // its fp32 accumulator with truncation, a bias that grows with the number of accumulations
 // (measured: 1.5e-5 relative after 750 MMAs), so a tensor-memory accumulator only ever holds
-// ONE 32-column tile: the small cross terms are issued first, the four hi*hi MMAs last, and
-// the finished tile is added to fp32 registers (round-to-nearest) while the next tiles are
-// generated -- two accumulators in tensor memory alternate.
+// a group of TC_PROMO tiles (16 hi*hi MMAs, bias < 1e-6): within a tile the small cross terms
+// are issued first and the hi*hi MMAs last, and a finished group is added to fp32 registers
+// (round-to-nearest) while the next groups are generated -- two accumulators alternate.
 //
 // Every wait on an mbarrier is bounded; a wait that gives up records a code in the status word
 // of the workspace and the CTA leaves through the normal exit (tensor memory released).
@@ -29,9 +29,12 @@
 namespace km {
 
 constexpr int TC_BK = 32;             // band columns (GEMM K) per stage
-constexpr int TC_STAGES = 2;
+constexpr int TC_STAGES = 3;           // A (and rhs-lo) stages
+constexpr int TC_B_STAGES = 5;         // raw rhs tiles in flight / in use
+constexpr int TC_B_AHEAD = TC_B_STAGES - TC_STAGES;  // prefetch distance in tiles
+constexpr int TC_PROMO = 4;           // tiles accumulated in tensor memory before promotion to registers
 constexpr int TC_STATUS_BYTES = 256;  // status word + padding in front of the images
-constexpr unsigned TC_WAIT_POLLS = 400000;
+constexpr unsigned TC_WAIT_POLLS = 1u << 18;  // each poll may block for a short, system-defined time
 
 struct TcArgs {
     Batch batch;
@@ -44,7 +47,7 @@ struct TcArgs {
     View<const float> x1, x2, params;
     View<const int> start, end;
     View<float> out;
-    const float *images;         // [slot][k block][tile][hi|lo][chunk][c][4]
+    const float *images;         // [slot][k block][tile][chunk][c][4]
     int64_t image_slot_stride;   // floats between batch slots (0: rhs shared by all batches)
     int *status;
 };
@@ -59,6 +62,9 @@ __device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 // Bounded wait for the phase with the given parity.  false = gave up.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
     const uint32_t addr = smem_u32(bar);
@@ -67,11 +73,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
         asm volatile(
             "{\n\t"
             ".reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t"
             "}"
             : "=r"(done)
-            : "r"(addr), "r"(parity), "r"(2000u)
+            : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
     }
@@ -128,18 +134,31 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
     for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
 }
 
+// 16 / 32 consecutive columns of this thread's lane; the wait is issued by the caller
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
 
 // ------------------------------------------------------------------------- rhs images pre-pass
 
-// Writes, for every (slot, k block, 32-column tile), the hi and lo parts of the rhs tile in the
-// K-major core-matrix layout: part[chunk = jj / 4][c][jj % 4], c the column inside the k block.
-// Rows past n and columns past k are zero.  Also clears the status word.
+// Writes, for every (slot, k block, 32-column tile), the rhs tile transposed into the K-major
+// core-matrix layout: image[chunk = jj / 4][c][jj % 4], c the column inside the k block (the
+// tensor core reads the TF32 bits of these words as the "hi" operand; the "lo" operand is
+// derived from them in shared memory by the product kernel).  Rows past n and columns past k
+// are zero.  Also clears the status word.
 __global__ void __launch_bounds__(256) tc_rhs_images_kernel(Batch batch, int64_t slots, int64_t n, int64_t k,
                                                             int64_t tiles, int k_blocks, int n_pad,
                                                             View<const float> rhs, float *images, int *status) {
     if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
-    const int64_t per_tile = 2LL * TC_BK * n_pad;
+    const int64_t per_tile = (int64_t)TC_BK * n_pad;
     const int64_t total = slots * k_blocks * tiles * (int64_t)TC_BK * n_pad;
     for (int64_t idx = blockIdx.x * 256LL + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * 256) {
         // idx -> (slot, kb, tile, jj, c) with c fastest: coalesced reads of rhs rows
@@ -159,41 +178,58 @@ __global__ void __launch_bounds__(256) tc_rhs_images_kernel(Batch batch, int64_t
             const BatchIndex bi = decompose(batch, slot);
             v = batch_ptr(rhs, bi)[j * rhs.s0 + col * rhs.s1];
         }
-        const float hi = tf32_hi(v);
         float *img = images + ((slot * k_blocks + kb) * tiles + tile) * per_tile;
-        const int64_t off = (int64_t)(jj >> 2) * (n_pad * 4) + c * 4 + (jj & 3);
-        img[off] = hi;
-        img[(int64_t)TC_BK * n_pad + off] = v - hi;
+        img[(int64_t)(jj >> 2) * (n_pad * 4) + c * 4 + (jj & 3)] = v;
     }
 }
 
 // ----------------------------------------------------------------------------------- kernel
 
-// N = GEMM N (rhs columns per CTA, 16 .. 128); G threads per row: 128 * G threads, thread
-// (row = tid % 128, g = tid / 128) generates the columns [g * 32 / G, (g + 1) * 32 / G) of
-// every tile and owns the output columns [g * N / G, (g + 1) * N / G) of its row.
+// N = GEMM N (rhs columns per CTA, 64 or 128).  128 * G generator threads + one MMA warp.
+//
+// Generator thread (row = tid % 128, g = tid / 128) produces the columns
+// [g * 32 / G, (g + 1) * 32 / G) of its row in every A tile, derives its share of the rhs "lo"
+// tile, and owns the output columns [g * N / G, (g + 1) * N / G) of its row in registers.  The
+// MMA warp (one lane) fetches rhs tiles ahead of time and issues the MMAs.  The two sides meet
+// only through mbarriers -- there is no CTA-wide barrier inside the band loop:
+//   bar_full[bs]   raw rhs tile landed (bulk copy transaction count)   MMA warp -> generators
+//   bar_ready[s]   A tile and rhs-lo tile of stage s written           generators -> MMA warp
+//   bar_empty[s]   MMAs that read stage s are done (tcgen05.commit)     tensor core -> everyone
+//   bar_acc[ai]    a group of tiles is complete in accumulator ai      tensor core -> generators
+//   bar_free[ai]   accumulator ai has been added to the registers      generators -> MMA warp
 template <int KT, int N, int G>
-__global__ void __launch_bounds__(128 * G) matmul_tc_kernel(const TcArgs a) {
+__global__ void __launch_bounds__(128 * G + 32) matmul_tc_kernel(const TcArgs a) {
+    constexpr int GEN_THREADS = 128 * G;
+    constexpr int GEN_WARPS = 4 * G;
     constexpr int A_PART = 128 * TC_BK;  // floats per hi / lo part of an A stage
-    constexpr int STAGE_FLOATS = 2 * A_PART + 2 * TC_BK * N;
-    constexpr int NPT = N / G;  // accumulator columns per thread
-    static_assert(NPT % 8 == 0, "columns per thread must be a multiple of 8");
+    constexpr int B_TILE = TC_BK * N;    // floats per rhs tile image
+    constexpr int NPT = N / G;           // accumulator columns per thread
+    constexpr int CPT = TC_BK / 4 / G;   // 4-column chunks generated per thread and tile
+    static_assert(NPT % 16 == 0, "columns per thread must be a multiple of 16");
+    static_assert((B_TILE / 4) % GEN_THREADS == 0, "rhs tile must split evenly over the threads");
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[TC_STAGES];   // rhs images landed
-    __shared__ __align__(8) uint64_t bar_empty[TC_STAGES];  // MMAs of the stage are done
+    __shared__ __align__(8) uint64_t bar_full[TC_B_STAGES];
+    __shared__ __align__(8) uint64_t bar_ready[TC_STAGES];
+    __shared__ __align__(8) uint64_t bar_empty[TC_STAGES];
+    __shared__ __align__(8) uint64_t bar_acc[2];
+    __shared__ __align__(8) uint64_t bar_free[2];
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int abort_flag;
-    __shared__ __align__(16) float xs[2][TC_BK];
+    __shared__ int fail_flag;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const bool is_mma_warp = warp == GEN_WARPS;
     const int row_local = tid & 127;
-    const int g = tid >> 7;
+    const int g = (tid >> 7) % G;
 
-    float *stage_base = reinterpret_cast<float *>(smem_raw);
-    auto a_hi = [&](int s) { return stage_base + s * STAGE_FLOATS; };
-    auto a_lo = [&](int s) { return stage_base + s * STAGE_FLOATS + A_PART; };
-    auto b_img = [&](int s) { return stage_base + s * STAGE_FLOATS + 2 * A_PART; };
+    // shared memory: [A hi | A lo | rhs lo] x TC_STAGES, then TC_B_STAGES raw rhs tiles
+    float *smem_f = reinterpret_cast<float *>(smem_raw);
+    constexpr int STAGE_FLOATS = 2 * A_PART + B_TILE;
+    auto a_hi = [&](int s) { return smem_f + s * STAGE_FLOATS; };
+    auto a_lo = [&](int s) { return smem_f + s * STAGE_FLOATS + A_PART; };
+    auto b_lo = [&](int s) { return smem_f + s * STAGE_FLOATS + 2 * A_PART; };
+    auto b_raw = [&](int bs) { return smem_f + TC_STAGES * STAGE_FLOATS + bs * B_TILE; };
 
     // work item
     int64_t item = blockIdx.x;
@@ -215,160 +251,252 @@ __global__ void __launch_bounds__(128 * G) matmul_tc_kernel(const TcArgs a) {
     const int tile_lo = band_lo / TC_BK;
     const int tile_hi = (band_hi + TC_BK - 1) / TC_BK;  // exclusive
     const int tiles = band_hi > band_lo ? tile_hi - tile_lo : 0;
-
-    const int64_t row = r * KM_BLOCK_SIZE + row_local;
-    const float x1v = row < a.m ? x1[row * a.x1.s0] : 0.0f;
     const float *images = a.images + (a.image_slot_stride ? b * a.image_slot_stride : 0) +
-                          (int64_t)kb * a.tiles * (2LL * TC_BK * N);
+                          (int64_t)kb * a.tiles * (int64_t)B_TILE;
 
     if (tid == 0) {
 #pragma unroll
+        for (int s = 0; s < TC_B_STAGES; s++) mbar_init(&bar_full[s], 1);
+#pragma unroll
         for (int s = 0; s < TC_STAGES; s++) {
-            mbar_init(&bar_full[s], 1);
+            mbar_init(&bar_ready[s], GEN_WARPS);
             mbar_init(&bar_empty[s], 1);
         }
-        abort_flag = 0;
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            mbar_init(&bar_acc[i], 1);
+            mbar_init(&bar_free[i], GEN_WARPS);
+        }
+        fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 0) tmem_alloc(&tmem_base_slot, (unsigned)a.tmem_cols);
-    // x2 values of the first tile
-    if (tiles > 0 && tid < TC_BK) {
-        const int j = tile_lo * TC_BK + tid;
-        xs[0][tid] = j < n ? x2[(int64_t)j * a.x2.s0] : 0.0f;
-    }
+    if (is_mma_warp) tmem_alloc(&tmem_base_slot, (unsigned)a.tmem_cols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    // this thread's window of an accumulator: its lane quarter, its column share
-    const uint32_t tmem_mine = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(g * NPT);
 
     // instruction descriptor: D fp32, A / B tf32, both K-major, M = 128, N
     constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
-    constexpr uint32_t img_bytes = 2u * TC_BK * N * sizeof(float);
+    constexpr uint32_t img_bytes = B_TILE * sizeof(float);
     bool failed = false;
 
     float acc[NPT];
 #pragma unroll
     for (int c = 0; c < NPT; c++) acc[c] = 0.0f;
 
-    // adds the finished tile held by accumulator `s` to the registers
-    auto collect = [&](int s) {
-        tc_fence_after();
-#pragma unroll
-        for (int c0 = 0; c0 < NPT; c0 += 8) {
-            float v[8];
-            tmem_ld8(tmem_mine + (uint32_t)(s * N + c0), v);
-#pragma unroll
-            for (int u = 0; u < 8; u++) acc[c0 + u] += v[u];
-        }
-        tc_fence_before();
-    };
-
-    for (int t = 0; t < tiles; t++) {
-        const int s = t % TC_STAGES;
-        const int use = t / TC_STAGES;
-        const int jt = tile_lo + t;
-        // the MMAs of the tile that used this stage (and this accumulator) before must be done
-        if (use > 0 && !mbar_wait(&bar_empty[s], (unsigned)((use - 1) & 1))) failed = true;
-        if (__syncthreads_or(failed ? 1 : 0)) {
-            failed = true;
-            break;
-        }
-        if (use > 0) collect(s);
-        if (tid == 0) {
-            mbar_expect_tx(&bar_full[s], img_bytes);
-            bulk_copy_g2s(b_img(s), images + (int64_t)jt * (2LL * TC_BK * N), img_bytes, &bar_full[s]);
-        }
-        // prefetch the x2 values of the next tile (visible after this tile's barrier)
-        if (t + 1 < tiles && tid < TC_BK) {
-            const int j = (jt + 1) * TC_BK + tid;
-            xs[(t + 1) & 1][tid] = j < n ? x2[(int64_t)j * a.x2.s0] : 0.0f;
-        }
-
-        // generate the A tile: this thread's row, its share of the 32 columns, 4 at a time
-        const int j0 = jt * TC_BK;
-        const bool partial = (j0 < band_lo) || (j0 + TC_BK > band_hi);
-        float *ah = a_hi(s), *al = a_lo(s);
-        const float *xt = xs[t & 1];
-#pragma unroll
-        for (int q = 0; q < TC_BK / 4 / G; q++) {
-            const int chunk = g * (TC_BK / 4 / G) + q;
-            const float4 xq = *reinterpret_cast<const float4 *>(xt + chunk * 4);
-            float kv[4] = {fn.unscaled(x1v - xq.x), fn.unscaled(x1v - xq.y), fn.unscaled(x1v - xq.z),
-                           fn.unscaled(x1v - xq.w)};
-            if (partial) {
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int j = j0 + chunk * 4 + u;
-                    if (j < band_lo || j >= band_hi) kv[u] = 0.0f;
-                }
-            }
-            float lo[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++) lo[u] = kv[u] - tf32_hi(kv[u]);
-            // [chunk][row][16 bytes]: the tensor core reads only the TF32 bits of kv as "hi"
-            *reinterpret_cast<float4 *>(ah + (chunk * 128 + row_local) * 4) = make_float4(kv[0], kv[1], kv[2], kv[3]);
-            *reinterpret_cast<float4 *>(al + (chunk * 128 + row_local) * 4) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-        }
-        fence_async_smem();
-        __syncthreads();
-
-        if (tid == 0) {
-            if (!mbar_wait(&bar_full[s], (unsigned)(use & 1))) {
-                abort_flag = 1;
-            } else {
+    if (is_mma_warp) {
+        // ------------------------------------------------------------ rhs fetch + MMA issue
+        if (lane == 0) {
+            auto fetch_rhs = [&](int t) {
+                const int bs = t % TC_B_STAGES;
+                mbar_expect_tx(&bar_full[bs], img_bytes);
+                bulk_copy_g2s(b_raw(bs), images + (int64_t)(tile_lo + t) * B_TILE, img_bytes, &bar_full[bs]);
+            };
+            for (int t = 0; t < min(tiles, TC_B_AHEAD); t++) fetch_rhs(t);
+            // Shared-memory descriptors: built once; per tile only the 14-bit start-address field
+            // moves (by whole stages), per K step by two core-matrix columns.  This thread is the
+            // only one issuing MMAs, so its instruction count per tile is on the critical path.
+            constexpr uint32_t lbo_a = 128 * 16, lbo_b = N * 16, sbo = 128;
+            constexpr uint64_t stage_step = (uint64_t)(STAGE_FLOATS * 4) >> 4;
+            constexpr uint64_t braw_step = (uint64_t)(B_TILE * 4) >> 4;
+            constexpr uint64_t ks_a = (uint64_t)(2 * lbo_a) >> 4, ks_b = (uint64_t)(2 * lbo_b) >> 4;
+            const uint64_t d_ah0 = smem_desc(smem_u32(a_hi(0)), lbo_a, sbo);
+            const uint64_t d_al0 = smem_desc(smem_u32(a_lo(0)), lbo_a, sbo);
+            const uint64_t d_bl0 = smem_desc(smem_u32(b_lo(0)), lbo_b, sbo);
+            const uint64_t d_br0 = smem_desc(smem_u32(b_raw(0)), lbo_b, sbo);
+            int s = 0, use = 0, bs = 0, in_grp = 0, grp = 0;  // ring counters of tile t
+            for (int t = 0; t < tiles; t++) {
+                const int ai = grp & 1;
+                const bool grp_first = in_grp == 0;
+                const bool grp_last = in_grp == TC_PROMO - 1 || t == tiles - 1;
+                // stage s (and the raw-rhs buffer of tile t - TC_STAGES) is free once its MMAs are done
+                if (use > 0 && !mbar_wait(&bar_empty[s], (unsigned)((use - 1) & 1))) failed = true;
+                if (!failed && t + TC_B_AHEAD < tiles) fetch_rhs(t + TC_B_AHEAD);
+                // the accumulator must have been collected by every generator warp
+                if (!failed && grp_first && grp >= 2 && !mbar_wait(&bar_free[ai], (unsigned)(((grp >> 1) - 1) & 1))) failed = true;
+                if (!failed && !mbar_wait(&bar_ready[s], (unsigned)(use & 1))) failed = true;
+                if (failed) break;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(s * N);
-                const uint32_t ah_addr = smem_u32(ah), al_addr = smem_u32(al);
-                const uint32_t bh_addr = smem_u32(b_img(s)), bl_addr = bh_addr + TC_BK * N * 4;
-                constexpr uint32_t lbo_a = 128 * 16, lbo_b = N * 16, sbo = 128;
+                const uint32_t d_tmem = tmem_base + (uint32_t)(ai * N);
+                const uint64_t dah = d_ah0 + s * stage_step, dal = d_al0 + s * stage_step;
+                const uint64_t dbl = d_bl0 + s * stage_step, dbh = d_br0 + bs * braw_step;
                 // cross terms first (tiny accumulator, truncation irrelevant), hi * hi last
 #pragma unroll
                 for (int ks = 0; ks < TC_BK / 8; ks++) {
-                    const uint64_t dah = smem_desc(ah_addr + ks * 2 * lbo_a, lbo_a, sbo);
-                    const uint64_t dal = smem_desc(al_addr + ks * 2 * lbo_a, lbo_a, sbo);
-                    const uint64_t dbh = smem_desc(bh_addr + ks * 2 * lbo_b, lbo_b, sbo);
-                    const uint64_t dbl = smem_desc(bl_addr + ks * 2 * lbo_b, lbo_b, sbo);
-                    mma_tf32(d_tmem, dah, dbl, idesc, ks > 0 ? 1u : 0u);
-                    mma_tf32(d_tmem, dal, dbh, idesc, 1u);
+                    mma_tf32(d_tmem, dah + ks * ks_a, dbl + ks * ks_b, idesc, (ks > 0 || !grp_first) ? 1u : 0u);
+                    mma_tf32(d_tmem, dal + ks * ks_a, dbh + ks * ks_b, idesc, 1u);
                 }
 #pragma unroll
-                for (int ks = 0; ks < TC_BK / 8; ks++) {
-                    const uint64_t dah = smem_desc(ah_addr + ks * 2 * lbo_a, lbo_a, sbo);
-                    const uint64_t dbh = smem_desc(bh_addr + ks * 2 * lbo_b, lbo_b, sbo);
-                    mma_tf32(d_tmem, dah, dbh, idesc, 1u);
-                }
+                for (int ks = 0; ks < TC_BK / 8; ks++) mma_tf32(d_tmem, dah + ks * ks_a, dbh + ks * ks_b, idesc, 1u);
                 mma_commit(&bar_empty[s]);
+                if (grp_last) mma_commit(&bar_acc[ai]);
+                // advance the ring counters
+                if (++s == TC_STAGES) {
+                    s = 0;
+                    use++;
+                }
+                if (++bs == TC_B_STAGES) bs = 0;
+                if (++in_grp == TC_PROMO) {
+                    in_grp = 0;
+                    grp++;
+                }
+            }
+            if (failed) atomicExch(&fail_flag, 1);
+        }
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------- generators
+        const int64_t row = r * KM_BLOCK_SIZE + row_local;
+        const float x1v = row < a.m ? x1[row * a.x1.s0] : 0.0f;
+        const uint32_t tmem_mine = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(g * NPT);
+
+        auto collect = [&](int ai) {
+            tc_fence_after();
+            uint32_t v[NPT / 16][16];
+#pragma unroll
+            for (int q = 0; q < NPT / 16; q++) tmem_ld16_nowait(tmem_mine + (uint32_t)(ai * N + q * 16), v[q]);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < NPT / 16; q++)
+#pragma unroll
+                for (int u = 0; u < 16; u++) acc[q * 16 + u] += __uint_as_float(v[q][u]);
+            tc_fence_before();
+        };
+        // x2 values of this thread's columns, fetched one tile ahead
+        auto load_x2 = [&](int jt, float (&xv)[CPT][4]) {
+#pragma unroll
+            for (int q = 0; q < CPT; q++)
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const int j = jt * TC_BK + (g * CPT + q) * 4 + u;
+                    xv[q][u] = j < n ? __ldg(x2 + (int64_t)j * a.x2.s0) : 0.0f;
+                }
+        };
+        float xnext[CPT][4];
+        if (tiles > 0) load_x2(tile_lo, xnext);
+
+        for (int t = 0; t < tiles; t++) {
+            const int s = t % TC_STAGES, use = t / TC_STAGES, bs = t % TC_B_STAGES;
+            const int jt = tile_lo + t;
+            const int grp = t / TC_PROMO, ai = grp & 1;
+            float xv[CPT][4];
+#pragma unroll
+            for (int q = 0; q < CPT; q++)
+#pragma unroll
+                for (int u = 0; u < 4; u++) xv[q][u] = xnext[q][u];
+            if (t + 1 < tiles) load_x2(jt + 1, xnext);
+
+            // an accumulator that is about to be reused is first added to the registers
+            if ((t % TC_PROMO) == 0 && grp >= 2) {
+                if (!mbar_wait(&bar_acc[ai], (unsigned)((grp / 2 - 1) & 1))) {
+                    failed = true;
+                    break;
+                }
+                collect(ai);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&bar_free[ai]);
+            }
+            // stage s must have been read by the MMAs of tile t - TC_STAGES
+            if (use > 0 && !mbar_wait(&bar_empty[s], (unsigned)((use - 1) & 1))) {
+                failed = true;
+                break;
+            }
+            // kernel entries: this thread's row, its share of the 32 columns, 4 at a time
+            const int j0 = jt * TC_BK;
+            const bool partial = (j0 < band_lo) || (j0 + TC_BK > band_hi);
+            float *ah = a_hi(s), *al = a_lo(s);
+#pragma unroll
+            for (int q = 0; q < CPT; q++) {
+                const int chunk = g * CPT + q;
+                float kv[4], lo[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) kv[u] = fn.unscaled(x1v - xv[q][u]);
+                if (partial) {
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        const int j = j0 + chunk * 4 + u;
+                        if (j < band_lo || j >= band_hi) kv[u] = 0.0f;
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; u++) lo[u] = kv[u] - tf32_hi(kv[u]);
+                // [chunk][row][16 bytes]: the tensor core reads only the TF32 bits of kv as "hi"
+                *reinterpret_cast<float4 *>(ah + (chunk * 128 + row_local) * 4) = make_float4(kv[0], kv[1], kv[2], kv[3]);
+                *reinterpret_cast<float4 *>(al + (chunk * 128 + row_local) * 4) = make_float4(lo[0], lo[1], lo[2], lo[3]);
+            }
+            // lo part of the rhs tile (the raw tile itself serves as hi)
+            if (!mbar_wait(&bar_full[bs], (unsigned)((t / TC_B_STAGES) & 1))) {
+                failed = true;
+                break;
+            }
+            {
+                const float4 *raw = reinterpret_cast<const float4 *>(b_raw(bs));
+                float4 *lo4 = reinterpret_cast<float4 *>(b_lo(s));
+#pragma unroll
+                for (int q = 0; q < B_TILE / 4 / GEN_THREADS; q++) {
+                    const float4 v = raw[q * GEN_THREADS + tid];
+                    lo4[q * GEN_THREADS + tid] =
+                        make_float4(v.x - tf32_hi(v.x), v.y - tf32_hi(v.y), v.z - tf32_hi(v.z), v.w - tf32_hi(v.w));
+                }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_ready[s]);
+        }
+
+        // drain: the last two groups still sit in tensor memory
+        const int groups = (tiles + TC_PROMO - 1) / TC_PROMO;
+        for (int grp = max(0, groups - 2); grp < groups && !failed; grp++) {
+            if (!mbar_wait(&bar_acc[grp & 1], (unsigned)((grp / 2) & 1))) {
+                failed = true;
+                break;
+            }
+            collect(grp & 1);
+        }
+        if (failed) atomicExch(&fail_flag, 1);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (fail_flag) {
+        if (tid == 0) atomicExch(a.status, 1);
+    } else if (!is_mma_warp) {
+        // Output.  Each thread holds NPT consecutive columns of one row; a warp transposes its
+        // 32 x NPT block through shared memory (the stages are idle now) so that every store
+        // instruction writes whole 128-byte row segments.
+        const float scale = fn.scale;
+        const int64_t row0 = r * KM_BLOCK_SIZE + (warp & 3) * 32;  // first row of this warp
+        const int64_t out_row0 = row0 - a.rb_begin * KM_BLOCK_SIZE;
+        const int64_t col0 = (int64_t)kb * N + g * NPT;
+        constexpr int PITCH = NPT + 4;  // floats; keeps float4 alignment, staggers banks
+        float *tile = smem_f + warp * (32 * PITCH);
+#pragma unroll
+        for (int c = 0; c < NPT; c += 4)
+            *reinterpret_cast<float4 *>(tile + lane * PITCH + c) =
+                make_float4(acc[c] * scale, acc[c + 1] * scale, acc[c + 2] * scale, acc[c + 3] * scale);
+        __syncwarp();
+        const bool vec_ok = a.out.s1 == 1 && (a.out.s0 % 4 == 0) && (col0 + NPT <= a.k) &&
+                            ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+        constexpr int V = NPT / 4;          // float4 per row
+        constexpr int ROWS_PER_IT = 32 / V;  // rows written per store instruction
+        if (vec_ok) {
+#pragma unroll
+            for (int it = 0; it < 32 / ROWS_PER_IT; it++) {
+                const int rr = it * ROWS_PER_IT + lane / V, cc = (lane % V) * 4;
+                if (row0 + rr < a.m)
+                    *reinterpret_cast<float4 *>(out + (out_row0 + rr) * a.out.s0 + col0 + cc) =
+                        *reinterpret_cast<const float4 *>(tile + rr * PITCH + cc);
+            }
+        } else {
+            for (int rr = 0; rr < 32; rr++) {
+                if (row0 + rr >= a.m) break;
+                for (int cc = lane; cc < NPT; cc += 32)
+                    if (col0 + cc < a.k) out[(out_row0 + rr) * a.out.s0 + (col0 + cc) * a.out.s1] = tile[rr * PITCH + cc];
             }
         }
     }
-
-    // drain: the last tiles still sit in tensor memory
-    for (int t = max(0, tiles - TC_STAGES); t < tiles && !failed; t++) {
-        if (!mbar_wait(&bar_empty[t % TC_STAGES], (unsigned)((t / TC_STAGES) & 1))) failed = true;
-        if (__syncthreads_or((failed || abort_flag) ? 1 : 0)) {
-            failed = true;
-            break;
-        }
-        collect(t % TC_STAGES);
-    }
-    if (__syncthreads_or((failed || abort_flag) ? 1 : 0)) failed = true;
-
-    if (failed) {
-        if (tid == 0) atomicExch(a.status, 1);
-    } else if (row < a.m) {
-        const float scale = fn.scale;
-        const int64_t out_row = row - a.rb_begin * KM_BLOCK_SIZE;
-        const int64_t col0 = (int64_t)kb * N + g * NPT;
-#pragma unroll
-        for (int c = 0; c < NPT; c++) {
-            if (col0 + c < a.k) out[out_row * a.out.s0 + (col0 + c) * a.out.s1] = acc[c] * scale;
-        }
-    }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0) tmem_free(tmem_base, (unsigned)a.tmem_cols);
+    if (is_mma_warp) tmem_free(tmem_base, (unsigned)a.tmem_cols);
 }
 
 static int64_t tc_slots(const Batch &b, const View<const float> &rhs) {
@@ -377,7 +505,7 @@ static int64_t tc_slots(const Batch &b, const View<const float> &rhs) {
     return shared ? 1 : b.count;
 }
 
-static int tc_n_pad(int64_t k) { return k <= 16 ? 16 : (k <= 32 ? 32 : (k <= 64 ? 64 : 128)); }
+static int tc_n_pad(int64_t k) { return k <= 64 ? 64 : 128; }
 
 template <int KT, int N, int G>
 static int launch_tc_n(const TcArgs &a, cudaStream_t s) {
@@ -386,23 +514,19 @@ static int launch_tc_n(const TcArgs &a, cudaStream_t s) {
         set_error("km_matmul_tc_f32: too many work items (%lld)", (long long)items);
         return KM_ERR_UNSUPPORTED;
     }
-    constexpr size_t smem = (size_t)TC_STAGES * (2 * 128 * TC_BK + 2 * TC_BK * N) * sizeof(float);
+    constexpr size_t smem = ((size_t)TC_STAGES * (2 * 128 * TC_BK + TC_BK * N) + (size_t)TC_B_STAGES * TC_BK * N) * sizeof(float);
     auto kernel = matmul_tc_kernel<KT, N, G>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(matmul_tc)");
-    kernel<<<(unsigned)items, 128 * G, smem, s>>>(a);
+    kernel<<<(unsigned)items, 128 * G + 32, smem, s>>>(a);
     KM_CHECK_LAUNCH("km_matmul_tc_f32 launch");
     return KM_OK;
 }
 
 template <int KT>
 static int launch_tc(const TcArgs &a, cudaStream_t s) {
-    switch (a.n_pad) {
-    case 16: return launch_tc_n<KT, 16, 1>(a, s);
-    case 32: return launch_tc_n<KT, 32, 1>(a, s);
-    case 64: return launch_tc_n<KT, 64, 2>(a, s);
-    default: return launch_tc_n<KT, 128, 2>(a, s);
-    }
+    if (a.n_pad == 64) return launch_tc_n<KT, 64, 2>(a, s);
+    return launch_tc_n<KT, 128, 4>(a, s);
 }
 
 }  // namespace km
@@ -415,7 +539,7 @@ extern "C" size_t km_matmul_tc_workspace_bytes(const km_batch *batch, int64_t n,
     const int n_pad = tc_n_pad(k);
     const int64_t k_blocks = ceil_div(k, n_pad);
     const int64_t tiles = ceil_div(n, TC_BK);
-    return (size_t)TC_STATUS_BYTES + (size_t)(tc_slots(b, rv) * k_blocks * tiles) * (2 * TC_BK * n_pad) * sizeof(float);
+    return (size_t)TC_STATUS_BYTES + (size_t)(tc_slots(b, rv) * k_blocks * tiles) * (TC_BK * n_pad) * sizeof(float);
 }
 
 extern "C" int km_matmul_tc_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
@@ -460,7 +584,7 @@ extern "C" int km_matmul_tc_f32(int kernel_type, const km_batch *batch, int64_t 
     a.status = static_cast<int *>(workspace);
     float *images = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + TC_STATUS_BYTES);
     a.images = images;
-    a.image_slot_stride = slots > 1 ? (int64_t)a.k_blocks * a.tiles * (2LL * TC_BK * a.n_pad) : 0;
+    a.image_slot_stride = slots > 1 ? (int64_t)a.k_blocks * a.tiles * ((int64_t)TC_BK * a.n_pad) : 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
 
     const int64_t total = slots * a.k_blocks * a.tiles * (int64_t)TC_BK * a.n_pad;
