@@ -596,6 +596,115 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
         dist.destroy_process_group()
 
 
+def run_single_op(args, local: int) -> None:
+    """The other benchmark configurations, one op each, on one GPU (inputs resident in HBM, CUDA
+    events, L2 flushed between steps).  Workloads:
+      rbf_small                  config 1: RBF forward, n = 4096, k = 1 (launch-latency bound)
+      locally_periodic_bilinear  config 3: bilinear_derivative, batch 4, n = 262144, k = 32
+      rbf_unbanded               config 4: unbanded RBF forward, n = 131072, k = 128 (tensor cores)
+      rbf_unbanded_index         config 4: 2^24 random (row, col) gathers
+    """
+    import ctypes
+
+    import kernel_matmul_b200  # noqa: F401
+    from kernel_matmul_b200 import ops, ranges, workloads
+    from kernel_matmul_b200._lib import check, lib
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    name = args.workload
+    peaks = {}
+    ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(ppath):
+        peaks = json.load(open(ppath))
+    flops = ctypes.c_double()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+    def probe():
+        check(lib.km_probe_fp32_peak(20000, None, ctypes.byref(flops), stream))
+
+    probe()
+    fp32_peak = max(flops.value / (cuda_ms(probe) * 1e-3) for _ in range(3)) / 1e12
+    sm_clock = fp32_peak * 1e12 / (148 * 128 * 2)
+
+    if name == "rbf_small":
+        w = workloads.rbf_small()
+        x = w.x.to(dev)
+        start, end = workloads.band(w, x)
+        rhs, params = w.rhs.to(dev), w.params.to(dev)
+        E, k, kt = int(ops.count_entries(w.n, w.n, start, end)), 1, "rbf"
+        fn = lambda: ops.matmul(kt, x, x, rhs, params, start, end)  # noqa: E731
+        model = {"bound": "launch latency", "fp32_instr": fp32_instr_fwd(kt, k), "sfu": GEN_FWD[kt][1]}
+        units, kernel = E * k, "matmul_fma_kernel"
+    elif name == "locally_periodic_bilinear":
+        w = workloads.locally_periodic_bilinear()
+        B = w.params.shape[0]
+        x = w.x.to(dev)
+        start, end = workloads.band(w, x)
+        xb = x.expand(B, -1)
+        lhs, rhs, params = w.extra["lhs"].to(dev), w.rhs.to(dev), w.params.to(dev)
+        kt, k = "locally_periodic", w.rhs.shape[-1]
+        E = int(ops.count_entries(w.n, w.n, start, end))
+        fn = lambda: ops.bilinear_derivative(kt, xb, xb, lhs, rhs, params, start, end)  # noqa: E731
+        model = {"bound": "fp32", "fp32_instr": fp32_instr_bwd(kt, k), "sfu": GEN_BWD[kt][1]}
+        units, kernel = E * k, "grad_band_kernel"
+    elif name == "rbf_unbanded":
+        w = workloads.rbf_unbanded(lookups=16)
+        x = w.x.to(dev)
+        start, end = ranges.make_ranges(None, x)
+        rhs, params = w.rhs.to(dev), w.params.to(dev)
+        kt, k, E = "rbf", w.rhs.shape[-1], w.n * w.n
+        fn = lambda: ops.matmul(kt, x, x, rhs, params, start, end)  # noqa: E731
+        model = {"bound": "tensor", "tensor_flops": 3 * 2.0 * E * k, "fp32_instr": 3 + 2, "sfu": 1}
+        units, kernel = E * k, "matmul_tc_kernel"
+    elif name == "rbf_unbanded_index":
+        w = workloads.rbf_unbanded()
+        x = w.x.to(dev)
+        start, end = ranges.make_ranges(None, x)
+        params = w.params.to(dev)
+        row, col = w.extra["row"].to(dev), w.extra["col"].to(dev)
+        L = row.numel()
+        fn = lambda: ops.index("rbf", x, x, params, start, end, (), row, col)  # noqa: E731
+        model = {"bound": "hbm", "bytes": 12 * L}
+        units, kernel, E, k, kt = L, "index_kernel", L, 1, "rbf"
+    else:
+        raise SystemExit(f"unknown workload {name}")
+
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        fn()
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    ms = []
+    for _ in range(args.steps):
+        flush.fill_(1)
+        ms.append(cuda_ms(fn))
+    clocks = sampler.stop()
+    t = statistics.mean(ms) * 1e-3
+    roof = {"bound": model["bound"], "kernel": kernel, "traffic": None}
+    if model["bound"] == "tensor":
+        # peak: the measured dense bf16 rate halved (TF32 runs at half the bf16 rate)
+        tf32_peak = peaks.get("bf16_tflops", 1590.0) / 2
+        roof.update(achieved=model["tensor_flops"] / t / 1e12, peak=tf32_peak, unit="TFLOP/s",
+                    peak_source="MEASURED_PEAKS.json bf16_tflops / 2 (TF32 rate); achieved counts the 3 TF32 MMAs per product")
+    elif model["bound"] == "hbm":
+        roof.update(achieved=model["bytes"] / t / 1e9, peak=peaks.get("hbm_gbs", 6650.0), unit="GB/s",
+                    peak_source="MEASURED_PEAKS.json hbm_gbs; algorithmic bytes = row + col + out per lookup")
+    else:
+        roof.update(achieved=2.0 * E * model["fp32_instr"] / t / 1e12, peak=fp32_peak, unit="TFLOP/s",
+                    peak_source="live FFMA probe", frac_sfu=E * model["sfu"] / t / (148 * 16 * sm_clock))
+    roof["frac"] = roof["achieved"] / roof["peak"]
+    print(json.dumps({
+        "metric": METRIC if name != "rbf_unbanded_index" else "gathered_kernel_entries_per_s",
+        "value": units / t, "unit": UNIT if name != "rbf_unbanded_index" else "entries/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": w.name if name != "rbf_unbanded_index" else w.name + "_index", "entries": E, "rhs_cols": k,
+                   "l2": "flushed between steps (256 MB write)"},
+        "roofline": roof, "gpu_launches": args.steps, "clocks": clocks,
+    }), flush=True)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -607,13 +716,16 @@ def main() -> None:
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.impl == "reference":
-        if args.workload.startswith("cg_sum"):
+        if args.workload != "spectral_mixture" and args.workload != "spectral_mixture_small":
             if rank == 0:
                 print(json.dumps({"impl": "reference", "unavailable": "CPU leg implemented for the default workload only"}))
             return
         run_reference(args, rank, world)
     elif args.workload.startswith("cg_sum"):
         run_cg(args, rank, world, local)
+    elif args.workload in ("rbf_small", "locally_periodic_bilinear", "rbf_unbanded", "rbf_unbanded_index"):
+        if rank == 0:
+            run_single_op(args, local)
     else:
         run_ours(args, rank, world, local)
 
