@@ -114,6 +114,8 @@ KM_API int km_workspace_status(const void *workspace, int32_t *status_out, void 
  *   out row 0 is row row_block_begin * 128, i.e. out is (B.., rows_in_window, k);
  *   sum_batches != 0: out (rows_in_window, k) = sum_b K_b . rhs_b, accumulated in registers
  *   inside one CTA per row block -- no (B.., m, k) intermediate.  out's batch strides are ignored.
+ *   Spectral components that share x1, x2, rhs and the band (batch stride 0) and have one
+ *   common lengthscale are summed with the Gaussian envelope evaluated once per entry.
  * row_block_count < 0 means "to the last row block".
  * The window is how the product is sharded by rows over GPUs: every rank holds x, rhs and the
  * bands in full and computes its own row blocks (there is no dependence between row blocks).

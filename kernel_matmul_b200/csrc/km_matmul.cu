@@ -27,6 +27,7 @@ struct MatmulArgs {
     View<float> out;
     int rhs_vec_ok;  // rhs rows may be copied 16 bytes at a time
     int out_vec_ok;  // out rows may be stored 16 bytes at a time
+    int sum_shared_ok;  // batch sum: x1, x2, rhs, start, end are one copy shared by all batches
 };
 
 // Walks the band [band_lo, band_hi) of one row block and one batch and adds
@@ -213,6 +214,86 @@ __global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN, 384 / (32 * (128
     store_tile<KB, RPT, WN>(a, out, r, a.rb_begin * KM_BLOCK_SIZE, k0, fn.scale, smem, tid, acc);
 }
 
+constexpr int SUM_MAX_SHARED = 1024;  // components whose (frequency, scale) fit the shared table
+
+// Band walk for a SUM of spectral components that share inputs, band and lengthscale:
+//   sum_b s_b exp(-tau^2 / 2 l^2) cos(2 pi f_b tau) = exp(-tau^2 / 2 l^2) * sum_b s_b cos(w_b tau).
+// The envelope is evaluated once per entry, the component loop costs one SFU cosine and two
+// FP32 operations per component, and the k contraction FMAs happen once per entry instead of
+// once per entry and component.  `comp` holds (w_b, s_b) in shared memory.
+template <int KB, int RPT, int WN>
+__device__ __forceinline__ void band_walk_shared_envelope(
+    const MatmulArgs<float> &a, const float c0, const float2 *comp, const int ncomp, const float *x2,
+    const float *rhs, const float (&x1r)[RPT], const int band_lo, const int band_hi, const int64_t k0, const bool vec,
+    float *smem, const int tid, const int wn, float (&acc)[RPT][KB], f32x2 (&acc2)[RPT][(KB % 2 == 0) ? KB / 2 : 1]) {
+    constexpr int WM = 128 / (32 * RPT);
+    constexpr int THREADS = 32 * WM * WN;
+    constexpr int STAGE_FLOATS = TILE_N * KB + TILE_N;
+    constexpr bool PACKED = (KB % 2 == 0);
+    constexpr int KB2 = PACKED ? KB / 2 : 1;
+
+    auto stage_tile = [&](int buf, int n0) {
+        float *rs = smem + buf * STAGE_FLOATS;
+        stage_band_tile<KB, THREADS>(rs, rs + TILE_N * KB, x2, a.x2.s0, rhs, a.rhs.s0, a.rhs.s1, k0, a.k, n0,
+                                     min(TILE_N, band_hi - n0), vec, tid);
+    };
+    const int tiles = (band_hi - band_lo + TILE_N - 1) / TILE_N;
+    if (tiles > 0) {
+        stage_tile(0, band_lo);
+        cp_async_commit();
+    }
+    for (int t = 0; t < tiles; t++) {
+        const int n0 = band_lo + t * TILE_N;
+        if (t + 1 < tiles) {
+            stage_tile((t + 1) & 1, n0 + TILE_N);
+            cp_async_commit();
+            cp_async_wait<1>();
+        } else {
+            cp_async_wait<0>();
+        }
+        __syncthreads();
+        const float *rs = smem + (t & 1) * STAGE_FLOATS;
+        const float *xs = rs + TILE_N * KB;
+        const int cnt = min(TILE_N, band_hi - n0);
+        for (int j = wn; j < cnt; j += WN) {
+            const float xj = xs[j];
+            float tau[RPT], g[RPT];
+#pragma unroll
+            for (int i = 0; i < RPT; i++) {
+                tau[i] = x1r[i] - xj;
+                g[i] = 0.0f;
+            }
+#pragma unroll 4
+            for (int b = 0; b < ncomp; b++) {
+                const float2 ws = comp[b];
+#pragma unroll
+                for (int i = 0; i < RPT; i++) g[i] = fmaf(ws.y, cos_approx(ws.x * tau[i]), g[i]);
+            }
+            if constexpr (PACKED) {
+                f32x2 rv2[KB2];
+                load_staged_row2<KB>(rs, j, rv2);
+#pragma unroll
+                for (int i = 0; i < RPT; i++) {
+                    const float kv = g[i] * ex2_approx(c0 * tau[i] * tau[i]);
+                    const f32x2 kk = pack2(kv, kv);
+#pragma unroll
+                    for (int c = 0; c < KB2; c++) acc2[i][c] = fma2(kk, rv2[c], acc2[i][c]);
+                }
+            } else {
+                float rv[KB];
+                load_staged_row<KB>(rs, j, rv);
+#pragma unroll
+                for (int i = 0; i < RPT; i++) {
+                    const float kv = g[i] * ex2_approx(c0 * tau[i] * tau[i]);
+#pragma unroll
+                    for (int c = 0; c < KB; c++) acc[i][c] = fmaf(kv, rv[c], acc[i][c]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+}
+
 // One CTA per (row block, block of KB rhs columns): adds the products of ALL batches
 // (components of a sum kernel) in registers; each batch's output scale goes into its kernel
 // values.  out has no batch dimension.
@@ -247,7 +328,39 @@ __global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN, 384 / (32 * (128
     }
     const bool vec = (KB % 4 == 0) && a.rhs_vec_ok && (k0 + KB <= a.k);
 
-    for (int64_t b = 0; b < a.batch.count; b++) {
+    // Spectral components that share everything but frequency and scale take the
+    // shared-envelope walk.  Sharing of the inputs is known on the host; equality of the
+    // lengthscales is checked here (one value per component).
+    bool shared_envelope = false;
+    if constexpr (KT == KM_KERNEL_SPECTRAL) {
+        constexpr int STAGE_BYTES_TOTAL = 2 * (TILE_N * KB + TILE_N) * (int)sizeof(float);
+        float2 *comp = reinterpret_cast<float2 *>(reinterpret_cast<unsigned char *>(smem) + STAGE_BYTES_TOTAL);
+        if (a.sum_shared_ok && a.batch.count <= SUM_MAX_SHARED) {
+            const float ell0 = a.params.data[0];
+            int same = 1;
+            for (int64_t b = tid; b < a.batch.count; b += blockDim.x) {
+                const float *th = batch_ptr(a.params, decompose(a.batch, b));
+                same &= (th[0] == ell0) ? 1 : 0;
+                comp[b] = make_float2(2.0f * KM_PI_F * th[a.params.s0], th[2 * a.params.s0]);
+            }
+            shared_envelope = __syncthreads_and(same) != 0;
+            if (shared_envelope) {
+                const int band_lo = clamp_int(a.start.data[r * a.start.s0], 0, n);
+                const int band_hi = max(band_lo, min(a.end.data[r * a.end.s0], n));
+                float x1r[RPT];
+#pragma unroll
+                for (int i = 0; i < RPT; i++) {
+                    const int64_t row = row_base + 32 * i;
+                    x1r[i] = row < a.m ? a.x1.data[row * a.x1.s0] : 0.0f;
+                }
+                const float c0 = -(0.5f / (ell0 * ell0)) * KM_LOG2E_F;
+                band_walk_shared_envelope<KB, RPT, WN>(a, c0, comp, (int)a.batch.count, a.x2.data, a.rhs.data, x1r,
+                                                       band_lo, band_hi, k0, vec, smem, tid, wn, acc, acc2);
+            }
+        }
+    }
+
+    for (int64_t b = 0; b < (shared_envelope ? 0 : a.batch.count); b++) {
         const BatchIndex bi = decompose(a.batch, b);
         const float *x1 = batch_ptr(a.x1, bi);
         KernelFn<KT> fn;
@@ -279,7 +392,9 @@ static int launch_matmul(const MatmulArgs<float> &a, cudaStream_t stream) {
     constexpr int THREADS = 32 * WM * WN;
     constexpr size_t stage_bytes = 2 * (TILE_N * KB + TILE_N) * sizeof(float);
     constexpr size_t red_bytes = WN > 1 ? (size_t)WN * 128 * KB * sizeof(float) : 0;
-    constexpr size_t smem = stage_bytes > red_bytes ? stage_bytes : red_bytes;
+    // (the batch-sum kernel keeps a table of SUM_MAX_SHARED (frequency, scale) pairs behind the stages)
+    constexpr size_t table_bytes = SUM ? SUM_MAX_SHARED * sizeof(float2) : 0;
+    constexpr size_t smem = (stage_bytes + table_bytes > red_bytes) ? stage_bytes + table_bytes : red_bytes;
     auto kernel = SUM ? matmul_sum_fma_kernel<KT, KB, RPT, WN> : matmul_fma_kernel<KT, KB, RPT, WN>;
     if (smem > 48 * 1024) {
         cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -346,6 +461,9 @@ static int matmul_entry(const char *name, int kernel_type, const km_batch *batch
     a.out = make_view<float>(out, a.batch);
     a.rhs_vec_ok = rows_vectorizable(a.rhs, a.batch) ? 1 : 0;
     a.out_vec_ok = 0;
+    a.sum_shared_ok = 1;
+    for (int d = 0; d < a.batch.ndim; d++)
+        if (a.batch.size[d] > 1 && (a.x1.bs[d] || a.x2.bs[d] || a.rhs.bs[d] || a.start.bs[d] || a.end.bs[d])) a.sum_shared_ok = 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (sum_batches) {
         switch (kernel_type) {

@@ -23,6 +23,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
+# where the reference project is mounted (read-only); override with KM_REFERENCE_DIR
+REFERENCE_DIR = os.environ.get("KM_REFERENCE_DIR", "/root/reference")
 
 KERNEL_DEFINE = {
     "rbf": "KERNEL_RBF",
@@ -124,7 +126,7 @@ def build_one(reference: str, name: str, op: str, defines: dict) -> str:
 
 def main() -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=REFERENCE_DIR)
     ap.add_argument("--only", default=None, help="substring filter on module names")
     ap.add_argument("-j", type=int, default=4)
     args = ap.parse_args()

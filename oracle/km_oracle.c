@@ -207,7 +207,7 @@ void kmo_matmul(int kt, int64_t B, int m, int n, int k, int block,
  * (tests/native/test_matmul_bwd.py:26-27, tests/native/test_bilinear_derivative.py:35-40).
  * out: (B, P) doubles.  absolute != 0 returns the sum of the MAGNITUDES of the terms instead
  * (the scale that bounds the rounding error of any finite-precision evaluation of the sum;
- * used by the tests to judge results whose terms cancel).
+ * used by the tests to assess results whose terms cancel).
  */
 void kmo_bilinear_derivative(int kt, int64_t B, int m, int n, int k, int block,
                              const float *x1, int64_t x1_bs, const float *x2, int64_t x2_bs,

@@ -65,3 +65,29 @@ def test_cg_solve_matches_dense_fp64():
     v = torch.randn(n, k)
     Av = op.apply(v.cuda())
     assert rel_err(Av, K @ v.double() + 0.1 * v.double()) <= 1e-5
+
+
+@pytest.mark.parametrize("k", [1, 8, 11])
+@pytest.mark.parametrize("shared_lengthscale", [True, False])
+def test_spectral_mixture_sum_shared_envelope(k, shared_lengthscale):
+    """Sum over spectral components sharing x, band and rhs: with one common lengthscale the
+    kernel evaluates the envelope once per entry (shared-envelope walk), otherwise it adds the
+    components one by one; both against the oracle."""
+    from kernel_matmul_b200 import ops
+    from oracle import oracle as O
+
+    B, n = 37, 900
+    x = torch.sort(torch.rand(n) * 15)[0]
+    ell = torch.full((B,), 0.7) if shared_lengthscale else 0.5 + torch.rand(B)
+    params = torch.stack([ell, torch.rand(B) * 1.5, torch.randn(B)], dim=-1)  # signed scales
+    start, end = O.make_ranges(2.8, x)
+    rhs = torch.randn(n, k)
+    ref = O.matmul("spectral", x.expand(B, n), x.expand(B, n), rhs.expand(B, n, k), params,
+                   start.expand(B, -1), end.expand(B, -1)).sum(0)
+    xd = x.cuda().expand(B, n)
+    out = ops.matmul_rows("spectral", xd, xd, rhs.cuda().expand(B, n, k), params.cuda(),
+                          start.cuda().expand(B, -1), end.cuda().expand(B, -1), sum_batches=True)
+    # the components cancel partly (signed scales): compare against the sum of magnitudes
+    scale = O.matmul("spectral", x.expand(B, n), x.expand(B, n), rhs.expand(B, n, k), params,
+                     start.expand(B, -1), end.expand(B, -1)).abs().sum(0).max()
+    assert float((out.cpu().double() - ref).abs().max() / scale) <= 1e-5
