@@ -562,7 +562,11 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
         total_ms, e2e_ms, apply_ms = (float(v) for v in t)
     if rank == 0:
         ms_per_step = total_ms / args.steps
-        fp32_instr, sfu = fp32_instr_fwd(kt, k), GEN_FWD[kt][1]
+        # All components share inputs, band and lengthscale, so the kernel takes its
+        # shared-envelope walk: per (row, column) one exp and the k FMAs, per component one SFU
+        # cosine and two FP32 operations (phase multiply, scaled accumulate).
+        fp32_instr = 2 + (3 + k) / B
+        sfu = (B + 1) / B
         e_rank = E / world  # row windows are equal
         t_apply = apply_ms * 1e-3
         frac_fp32 = 2.0 * e_rank * fp32_instr / t_apply / 1e12 / fp32_peak
