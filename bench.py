@@ -21,8 +21,9 @@ Printed keys (one JSON line, rank 0):
   cpu_baseline  the dense PyTorch formulation (materialise K, mask by ranges, matmul, autograd)
              in fp32 on all host cores, on a bounded sample of the same workload.
 
-With N > 1 (torchrun) every rank runs its own 16 components of the same shape (seeded by rank):
-independent work, no data-path collective, weak scaling.
+With N > 1 (torchrun) every rank runs its own batch of 16 components with the same seeded
+parameters (the same work per GPU at every N): independent work, no data-path collective, weak
+scaling.
 
 ``--impl reference`` times only the CPU dense formulation (the reference has no CPU kernel of
 its own for this path; the dense formulation is what its tests define as the expected result).
@@ -152,15 +153,6 @@ def make_workload(name: str, rank: int):
         w = workloads.spectral_mixture(n=8192, components=4, k=16, span=62.5)
     else:
         raise SystemExit(f"unknown workload {name}")
-    if rank > 0:
-        # every rank gets its own components of the same distribution (weak scaling)
-        g = torch.Generator().manual_seed(1000 + rank)
-        B = w.params.shape[0]
-        ell = torch.exp(torch.rand(B, generator=g) * math.log(10.0) + math.log(0.5))
-        f = torch.rand(B, generator=g) * 2
-        w.params = torch.stack([ell, f, torch.ones(B)], dim=-1)
-        w.cutoffs = [4.0 * float(v) for v in ell]
-        w.extra["out_grad"] = torch.randn(w.extra["out_grad"].shape, generator=g)
     return w
 
 
@@ -433,7 +425,7 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
             "config": {
                 "workload": w.name, "ops": "matmul fwd + matmul_bwd", "entries_per_rank": E, "rhs_cols": k,
                 "units_per_step": units_all, "l2": "flushed between steps (256 MB write)",
-                "per_rank": "own 16 components, no collective",
+                "per_rank": "own batch of 16 components (same seeded parameters on every rank), no collective",
             },
             "roofline": {
                 "bound": "fp32", "kernel": dom, "achieved": d["achieved_tflops"], "peak": fp32_peak,
