@@ -155,6 +155,33 @@ KM_API int km_matmul_bwd_f32(int kernel_type, const km_batch *batch, int64_t m, 
                       size_t workspace_bytes, void *stream);
 
 /* ---------------------------------------------------------------------------------------
+ * The same gradients with the coefficients <left[i, :], right[j, :]> computed on the tensor
+ * cores (tcgen05.mma, 3xTF32 = fp32-level accuracy) while the threads evaluate the factors of
+ * d kappa / d p: the FP32 pipe no longer pays k FMAs per entry.  At most 32 columns (k <= 32;
+ * KM_ERR_UNSUPPORTED beyond -- use the entry points above).  Replaces the same reference calls
+ * as km_bilinear_derivative_f32 / km_matmul_bwd_f32.
+ * workspace: km_grad_tc_workspace_bytes(...) bytes of device memory, 256-byte aligned: a 4-byte
+ * status word (0 = ok, non-zero = a bounded wait inside the kernel gave up and the gradient is
+ * invalid; read it with km_workspace_status), the per-row-block partial sums, and the hi / lo
+ * TF32 images of `right` written by a pre-pass.
+ * ------------------------------------------------------------------------------------- */
+KM_API size_t km_grad_tc_workspace_bytes(const km_batch *batch, int64_t m, int64_t n, int64_t k,
+                                         const km_view *right);
+
+KM_API int km_bilinear_derivative_tc_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
+                                         int64_t k, const km_view *x1, const km_view *x2,
+                                         const km_view *left, const km_view *right,
+                                         const km_view *params, const km_view *start,
+                                         const km_view *end, const km_view *grad, void *workspace,
+                                         size_t workspace_bytes, void *stream);
+
+KM_API int km_matmul_bwd_tc_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
+                                int64_t k, const km_view *x1, const km_view *x2, const km_view *rhs,
+                                const km_view *params, const km_view *start, const km_view *end,
+                                const km_view *out_grad, const km_view *grad, void *workspace,
+                                size_t workspace_bytes, void *stream);
+
+/* ---------------------------------------------------------------------------------------
  * km_bilinear_derivative_f32 for callers that cannot hand over a workspace.  It has no
  * counterpart in the reference (whose ops allocate their temporaries through ATen).
  *

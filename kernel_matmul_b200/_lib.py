@@ -65,6 +65,12 @@ def _load() -> ctypes.CDLL:
     lib.km_bilinear_derivative_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, wp, vp, sz, vp]
     lib.km_matmul_bwd_f32.restype = ctypes.c_int
     lib.km_matmul_bwd_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, wp, vp, sz, vp]
+    lib.km_grad_tc_workspace_bytes.restype = sz
+    lib.km_grad_tc_workspace_bytes.argtypes = [bp, i64, i64, i64, wp]
+    lib.km_bilinear_derivative_tc_f32.restype = ctypes.c_int
+    lib.km_bilinear_derivative_tc_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, wp, vp, sz, vp]
+    lib.km_matmul_bwd_tc_f32.restype = ctypes.c_int
+    lib.km_matmul_bwd_tc_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, wp, vp, sz, vp]
     lib.km_bilinear_derivative_static_f32.restype = ctypes.c_int
     lib.km_bilinear_derivative_static_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, wp, vp]
     lib.km_dense_f32.restype = ctypes.c_int
@@ -95,7 +101,8 @@ lib = _load()
 
 EXPORTED = [
     "km_last_error", "km_version", "km_num_params", "km_matmul_f32", "km_matmul_rows_f32", "km_matmul_tc_workspace_bytes", "km_matmul_tc_f32",
-    "km_workspace_status", "km_grad_workspace_bytes",
+    "km_workspace_status", "km_grad_workspace_bytes", "km_grad_tc_workspace_bytes", "km_bilinear_derivative_tc_f32",
+    "km_matmul_bwd_tc_f32",
     "km_bilinear_derivative_f32", "km_bilinear_derivative_static_f32", "km_matmul_bwd_f32", "km_dense_f32", "km_dense_bwd_f32",
     "km_index_f32", "km_index_bwd_workspace_bytes", "km_index_bwd_f32", "km_make_ranges_f32",
     "km_make_ranges_symmetric_f32", "km_transpose_ranges_i32", "km_count_entries",

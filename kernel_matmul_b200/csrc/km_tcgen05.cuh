@@ -1,0 +1,179 @@
+// tcgen05 / tensor-memory / mbarrier / bulk-copy PTX wrappers shared by the tensor-core kernels
+// (km_matmul_tc.cu, km_matmul_tcn.cu, km_grad_tc.cu).  sm_100a only.
+#pragma once
+
+#include "km_common.cuh"
+
+namespace km {
+
+constexpr int TC_STATUS_BYTES = 256;  // status word + padding in front of the workspace payload
+
+// Arguments of the tensor-core products (filled by km_matmul_tc_f32).
+struct TcArgs {
+    Batch batch;
+    int64_t m, n, k;
+    int64_t row_blocks, rb_begin;
+    int k_blocks;  // blocks of n_pad rhs columns
+    int n_pad;     // GEMM N per block: multiple of 16, <= 256
+    int tmem_cols; // power of two >= max(32, n_pad)
+    int64_t tiles; // ceil(n / TC_BK)
+    View<const float> x1, x2, params;
+    View<const int> start, end;
+    View<float> out;
+    const float *images;         // [slot][k block][tile][chunk][c][4]
+    int64_t image_slot_stride;   // floats between batch slots (0: rhs shared by all batches)
+    int *status;
+};
+
+// Number of distinct rhs images: 1 when every batch shares one rhs (all batch strides 0).
+inline int64_t tc_slots(const Batch &b, const View<const float> &rhs) {
+    bool shared = true;
+    for (int d = 0; d < b.ndim; d++) shared = shared && (rhs.bs[d] == 0 || b.size[d] == 1);
+    return shared ? 1 : b.count;
+}
+
+// Narrow right-hand sides (k <= TCN_MAX_K): kernel-matrix tiles handed to the tensor core
+// through tensor memory (km_matmul_tcn.cu).  `a` carries everything but the images.
+constexpr int TCN_MAX_K = 16;
+size_t tcn_workspace_bytes(const Batch &b, int64_t n, const View<const float> &rhs);
+int tcn_matmul(int kernel_type, TcArgs a, const View<const float> &rhs, void *workspace, cudaStream_t stream);
+
+constexpr unsigned TC_WAIT_POLLS = 1u << 18;  // each poll may block for a short, system-defined time
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Bounded wait for the phase with the given parity.  false = gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
+    const uint32_t addr = smem_u32(bar);
+    for (unsigned poll = 0; poll < TC_WAIT_POLLS; poll++) {
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+// The same wait with a warp-uniform outcome (all 32 lanes must call it): false if any lane gave
+// up, so that a warp leaves its loop as a whole and .aligned instructions stay warp-wide.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, unsigned parity) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+}
+__device__ __forceinline__ void bulk_copy_g2s(void *dst, const void *src, unsigned bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t *smem_dst, unsigned cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_free(uint32_t taddr, unsigned cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+
+// K-major, no swizzle: core matrices of 8 rows x 16 bytes stored as 128 contiguous bytes;
+// `lbo` = bytes between core matrices adjacent in K, `sbo` = bytes between 8-row groups.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
+    return (uint64_t)((addr >> 4) & 0x3fffu) | ((uint64_t)((lbo >> 4) & 0x3fffu) << 16) |
+           ((uint64_t)((sbo >> 4) & 0x3fffu) << 32) | (1ull << 46);
+}
+// D (fp32, tensor memory) (+)= A (smem, tf32) . B (smem, tf32); M = 128, N from idesc, K = 8.
+__device__ __forceinline__ void mma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void mma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr)
+                 : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// 16 / 32 consecutive columns of this thread's lane; the wait is issued by the caller
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
+
+// D (fp32, tensor memory) (+)= A (tensor memory, tf32: row i in lane i, one K value per 32-bit
+// column) . B (smem, tf32); M = 128, N from idesc, K = 8.
+__device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                            uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+
+// registers -> 16 consecutive tensor-memory columns of this thread's lane
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        :
+        : "r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// 4-byte asynchronous copy that writes zero when `valid` is false (the source is not read)
+__device__ __forceinline__ void cp_async4_zfill(void *smem, const void *gmem, bool valid) {
+    const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+    const unsigned bytes = valid ? 4u : 0u;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+// arrive on `bar` once all earlier cp.async copies of this thread have landed (the arrival is
+// part of the barrier's expected count)
+__device__ __forceinline__ void cp_async_mbar_arrive(uint64_t *bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+}  // namespace km

@@ -18,7 +18,7 @@ import torch
 from torch import Tensor
 
 from . import _lib
-from ._lib import KM_MAX_BATCH_DIMS, KERNEL_TYPES, KmBatch, KmView, check, lib
+from ._lib import KmError, KM_MAX_BATCH_DIMS, KERNEL_TYPES, KmBatch, KmView, check, lib
 
 BLOCK_SIZE = 128
 NUM_PARAMS = {"rbf": 2, "spectral": 3, "locally_periodic": 4}
@@ -221,45 +221,64 @@ def matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: T
     return out
 
 
-def _grad_call(fn, kernel_type, x1, x2, left, right, params, start, end, swap: bool) -> Tensor:
+#: column counts for which the gradient ops take the tensor-core kernels on ``path="auto"``
+GRAD_TENSOR_CORE_K = range(0, 0)
+
+
+def _grad_call(which: str, kernel_type, x1, x2, left, right, params, start, end, path: str) -> Tensor:
+    """``which``: "matmul_bwd" (C argument order rhs ... out_grad) or "bilinear_derivative"."""
     kid, dev, batch, m, n, (x1e, x2e, pe, se, ee, le, rte) = _prep(
         kernel_type, x1, x2, params, start, end, [(left, 2), (right, 2)])
     if left.shape[-2] != m or right.shape[-2] != n or left.shape[-1] != right.shape[-1]:
         raise RuntimeError(f"left must be (.., {m}, k) and right (.., {n}, k); got {tuple(left.shape)} and {tuple(right.shape)}")
     k = left.shape[-1]
+    if path not in ("auto", "fma", "tc"):
+        raise ValueError(f"unknown path {path!r}")
+    tc = path == "tc" or (path == "auto" and k in GRAD_TENSOR_CORE_K)
     P = NUM_PARAMS[kernel_type]
     grad = torch.empty(*batch, P, device=dev, dtype=torch.float32)
     grade = grad.reshape(-1, P) if len(batch) > KM_MAX_BATCH_DIMS else grad
     kb = _km_batch(batch)
-    ws_bytes = lib.km_grad_workspace_bytes(kid, kb, m)
+    lv, rv = _view(le, 2), _view(rte, 2)
+    if tc:
+        ws_bytes = lib.km_grad_tc_workspace_bytes(kb, m, n, k, rv)
+        if ws_bytes == 0:
+            raise KmError(f"the tensor-core gradient takes at most 32 columns, got {k}")
+        fn = lib.km_matmul_bwd_tc_f32 if which == "matmul_bwd" else lib.km_bilinear_derivative_tc_f32
+    else:
+        ws_bytes = lib.km_grad_workspace_bytes(kid, kb, m)
+        fn = lib.km_matmul_bwd_f32 if which == "matmul_bwd" else lib.km_bilinear_derivative_f32
     ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
-    a, b = (_view(rte, 2), _view(le, 2)) if swap else (_view(le, 2), _view(rte, 2))
     with torch.cuda.device(dev):
-        if swap:  # matmul_bwd argument order: rhs ... out_grad
-            check(fn(kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), a, _view(pe, 1), _view(se, 1), _view(ee, 1),
-                     b, _view(grade, 1), ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
+        if which == "matmul_bwd":  # argument order: rhs ... out_grad
+            check(fn(kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), rv, _view(pe, 1), _view(se, 1), _view(ee, 1),
+                     lv, _view(grade, 1), ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
         else:
-            check(fn(kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), a, b, _view(pe, 1), _view(se, 1), _view(ee, 1),
+            check(fn(kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), lv, rv, _view(pe, 1), _view(se, 1), _view(ee, 1),
                      _view(grade, 1), ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
+    if tc:
+        grad._km_workspace = ws  # keeps the status word reachable for tc_status()
     return grad
 
 
-def matmul_bwd(kernel_type: str, x1, x2, rhs, params, start, end, out_grad) -> Tensor:
+def matmul_bwd(kernel_type: str, x1, x2, rhs, params, start, end, out_grad, *, path: str = "auto") -> Tensor:
     """Gradient of ``sum(out_grad * matmul(...))`` wrt ``params`` -> ``(*batch, P)``.
 
     Reference: ``matmul_bwd.call(x1, x2, rhs, params, start, end, out_grad)``
-    (native/matmul_bwd/matmul_bwd.cpp:6-19).
+    (native/matmul_bwd/matmul_bwd.cpp:6-19).  ``path`` as in ``matmul`` (the tensor-core kernel
+    takes at most 32 columns).
     """
-    return _grad_call(lib.km_matmul_bwd_f32, kernel_type, x1, x2, out_grad, rhs, params, start, end, swap=True)
+    return _grad_call("matmul_bwd", kernel_type, x1, x2, out_grad, rhs, params, start, end, path)
 
 
-def bilinear_derivative(kernel_type: str, x1, x2, left_vecs, right_vecs, params, start, end) -> Tensor:
+def bilinear_derivative(kernel_type: str, x1, x2, left_vecs, right_vecs, params, start, end, *,
+                        path: str = "auto") -> Tensor:
     """Gradient of ``sum_c left[:, c]^T K right[:, c]`` wrt ``params`` -> ``(*batch, P)``.
 
     Reference: ``bilinear_derivative.call(x1, x2, left_vecs, right_vecs, params, start, end)``
     (native/bilinear_derivative/bilinear_derivative.cpp:6-21).
     """
-    return _grad_call(lib.km_bilinear_derivative_f32, kernel_type, x1, x2, left_vecs, right_vecs, params, start, end, swap=False)
+    return _grad_call("bilinear_derivative", kernel_type, x1, x2, left_vecs, right_vecs, params, start, end, path)
 
 
 def dense(kernel_type: str, x1, x2, params, start, end) -> Tensor:

@@ -73,3 +73,103 @@ def test_auto_path_uses_tensor_cores_from_64_columns():
     assert ops.TENSOR_CORE_MIN_K == 64
     out = _run("rbf", 300, 300, 64, square=True)
     assert hasattr(out, "_km_workspace")
+
+
+# ------------------------------------------------------------------ narrow right-hand sides
+# k <= 16 takes the kernel that hands the kernel-matrix tiles over in tensor memory.
+
+
+@pytest.mark.parametrize("kt", KERNEL_TYPES)
+@pytest.mark.parametrize("k", [1, 5, 12, 16])
+def test_tc_narrow_product_matches_oracle(kt, k):
+    _run(kt, 600, 800, k)
+
+
+def test_tc_narrow_long_bands_many_accumulator_groups():
+    # unbanded with n = 3000: 188 tiles of 16 columns = 24 accumulator groups, 47 slot refills
+    _run("spectral", 257, 3000, 16, cutoff=None)
+    _run("rbf", 128, 2049, 7, cutoff=None)
+
+
+def test_tc_narrow_batched_shared_and_private_rhs():
+    _run("spectral", 500, 500, 16, batch=(2, 3), shared_rhs=True, square=True)
+    _run("locally_periodic", 301, 199, 9, batch=(4,), shared_rhs=False)
+
+
+def test_tc_narrow_strided_operands_and_empty_bands():
+    from kernel_matmul_b200 import ops
+    from oracle import oracle as O
+
+    x1 = torch.sort(torch.rand(700) * 10)[0]
+    x2 = torch.sort(torch.rand(640) * 3)[0]
+    start, end = O.make_ranges(0.5, x1, x2)
+    assert bool((start == end).any())
+    params = torch.tensor([0.8, 0.7, 1.2])
+    rhs_wide = torch.randn(640, 40)
+    rhs = rhs_wide[:, 3:33:2]  # 15 columns, column stride 2
+    x2_wide = torch.stack([x2, -x2], dim=-1).cuda()
+    out = ops.matmul("spectral", x1.cuda(), x2_wide[:, 0], rhs_wide.cuda()[:, 3:33:2], params.cuda(), start.cuda(),
+                     end.cuda(), path="tc")
+    assert ops.tc_status(out) == 0
+    assert rel_err(out, O.matmul("spectral", x1, x2, rhs.contiguous(), params, start, end)) <= 1e-5
+
+
+# --------------------------------------------------------------------- tensor-core gradients
+
+
+def _run_grad(kt, m, n, k, batch=(), cutoff=2.0, square=False, which="bilinear_derivative"):
+    from conftest import assert_grad_close
+    from kernel_matmul_b200 import ops
+    from oracle import oracle as O
+
+    x1 = torch.sort(torch.rand(*batch, m) * 10)[0]
+    x2 = x1 if square else torch.sort(torch.rand(*batch, n) * 10)[0]
+    n = x2.shape[-1]
+    params = make_params(kt, batch)
+    start, end = O.make_ranges(cutoff, x1) if square else O.make_ranges(cutoff, x1, x2)
+    left = torch.randn(*batch, m, k)
+    right = torch.randn(*batch, n, k)
+    d = lambda t: t.cuda()  # noqa: E731
+    if which == "bilinear_derivative":
+        ref = O.bilinear_derivative(kt, x1, x2, left, right, params, start, end)
+        scale = O.bilinear_derivative(kt, x1, x2, left, right, params, start, end, absolute=True)
+        out = ops.bilinear_derivative(kt, d(x1), d(x2), d(left), d(right), d(params), d(start), d(end), path="tc")
+        fma = ops.bilinear_derivative(kt, d(x1), d(x2), d(left), d(right), d(params), d(start), d(end), path="fma")
+    else:
+        ref = O.matmul_bwd(kt, x1, x2, right, params, start, end, left)
+        scale = O.matmul_bwd(kt, x1, x2, right, params, start, end, left, absolute=True)
+        out = ops.matmul_bwd(kt, d(x1), d(x2), d(right), d(params), d(start), d(end), d(left), path="tc")
+        fma = ops.matmul_bwd(kt, d(x1), d(x2), d(right), d(params), d(start), d(end), d(left), path="fma")
+    assert ops.tc_status(out) == 0
+    assert out.shape == ref.shape
+    assert_grad_close(out, ref, scale)
+    assert_grad_close(fma, ref, scale)
+
+
+@pytest.mark.parametrize("kt", KERNEL_TYPES)
+@pytest.mark.parametrize("k", [1, 8, 11, 16, 17, 32])
+def test_tc_gradient_matches_oracle(kt, k):
+    _run_grad(kt, 600, 800, k)
+
+
+@pytest.mark.parametrize("which", ["bilinear_derivative", "matmul_bwd"])
+def test_tc_gradient_batched_ragged(which):
+    _run_grad("spectral", 301, 199, 16, batch=(3,), which=which)
+    _run_grad("locally_periodic", 500, 500, 32, batch=(2, 2), square=True, which=which)
+
+
+def test_tc_gradient_unbanded_long_bands():
+    _run_grad("spectral", 257, 3000, 16, cutoff=None)
+    _run_grad("rbf", 130, 2049, 24, cutoff=None)
+
+
+def test_tc_gradient_rejects_wide_operands():
+    from kernel_matmul_b200 import ops
+    from kernel_matmul_b200._lib import KmError
+
+    x = torch.sort(torch.rand(256) * 10)[0].cuda()
+    start = torch.zeros(2, dtype=torch.int32).cuda()
+    end = torch.full((2,), 256, dtype=torch.int32).cuda()
+    v = torch.randn(256, 40).cuda()
+    with pytest.raises(KmError):
+        ops.bilinear_derivative("rbf", x, x, v, v, torch.tensor([1.0, 1.0]).cuda(), start, end, path="tc")
