@@ -135,6 +135,38 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
 }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ f32x2 splat2(float v) { return pack2(v, v); }
+// elementwise SFU functions of a pair
+__device__ __forceinline__ f32x2 ex2_approx2(f32x2 x) {
+    float a, b;
+    unpack2(x, a, b);
+    return pack2(ex2_approx(a), ex2_approx(b));
+}
+__device__ __forceinline__ f32x2 cos_approx2(f32x2 x) {
+    float a, b;
+    unpack2(x, a, b);
+    return pack2(cos_approx(a), cos_approx(b));
+}
+__device__ __forceinline__ f32x2 sin_approx2(f32x2 x) {
+    float a, b;
+    unpack2(x, a, b);
+    return pack2(sin_approx(a), sin_approx(b));
+}
 
 // Kernel functions.
 //
@@ -172,6 +204,17 @@ struct KernelFn<KM_KERNEL_RBF> {
         sums[0] = fmaf(v, t2, sums[0]);
         sums[1] += v;
     }
+    // the same for two entries at once with packed FP32 operations (half the issue slots);
+    // sums2[q] holds the two partial sums of sums[q]
+    __device__ __forceinline__ void accumulate2(f32x2 tau, f32x2 coeff, f32x2 *sums2) const {
+        const f32x2 t2 = mul2(tau, tau);
+        const f32x2 v = mul2(coeff, ex2_approx2(mul2(splat2(c0), t2)));
+        sums2[0] = fma2(v, t2, sums2[0]);
+        sums2[1] = add2(v, sums2[1]);
+    }
+    __device__ __forceinline__ f32x2 unscaled2(f32x2 tau) const {
+        return ex2_approx2(mul2(splat2(c0), mul2(tau, tau)));
+    }
     __device__ __forceinline__ void finish_grad(const double *sums, float *grad) const {
         const double l = ell;
         // d kappa / d p0 = -s e tau^2 ; d p0 / d l = -1 / l^3
@@ -205,6 +248,19 @@ struct KernelFn<KM_KERNEL_SPECTRAL> {
         sums[0] = fmaf(vc, t2, sums[0]);
         sums[1] = fmaf(vs, tau, sums[1]);
         sums[2] += vc;
+    }
+    __device__ __forceinline__ void accumulate2(f32x2 tau, f32x2 coeff, f32x2 *sums2) const {
+        const f32x2 t2 = mul2(tau, tau);
+        const f32x2 ph = mul2(splat2(w), tau);
+        const f32x2 v = mul2(coeff, ex2_approx2(mul2(splat2(c0), t2)));
+        const f32x2 vc = mul2(v, cos_approx2(ph));
+        const f32x2 vs = mul2(v, sin_approx2(ph));
+        sums2[0] = fma2(vc, t2, sums2[0]);
+        sums2[1] = fma2(vs, tau, sums2[1]);
+        sums2[2] = add2(vc, sums2[2]);
+    }
+    __device__ __forceinline__ f32x2 unscaled2(f32x2 tau) const {
+        return mul2(ex2_approx2(mul2(splat2(c0), mul2(tau, tau))), cos_approx2(mul2(splat2(w), tau)));
     }
     __device__ __forceinline__ void finish_grad(const double *sums, float *grad) const {
         const double l = ell;
@@ -247,6 +303,22 @@ struct KernelFn<KM_KERNEL_LOCALLY_PERIODIC> {
         sums[1] = fmaf(v, sn2, sums[1]);
         sums[2] = fmaf(v * sn, cs * tau, sums[2]);
         sums[3] += v;
+    }
+    __device__ __forceinline__ void accumulate2(f32x2 tau, f32x2 coeff, f32x2 *sums2) const {
+        const f32x2 ph = mul2(splat2(w), tau);
+        const f32x2 sn = sin_approx2(ph);
+        const f32x2 cs = cos_approx2(ph);
+        const f32x2 t2 = mul2(tau, tau);
+        const f32x2 sn2 = mul2(sn, sn);
+        const f32x2 v = mul2(coeff, ex2_approx2(fma2(splat2(c0), t2, mul2(splat2(c1), sn2))));
+        sums2[0] = fma2(v, t2, sums2[0]);
+        sums2[1] = fma2(v, sn2, sums2[1]);
+        sums2[2] = fma2(mul2(v, sn), mul2(cs, tau), sums2[2]);
+        sums2[3] = add2(v, sums2[3]);
+    }
+    __device__ __forceinline__ f32x2 unscaled2(f32x2 tau) const {
+        const f32x2 sn = sin_approx2(mul2(splat2(w), tau));
+        return ex2_approx2(fma2(mul2(splat2(c0), tau), tau, mul2(splat2(c1), mul2(sn, sn))));
     }
     __device__ __forceinline__ void finish_grad(const double *sums, float *grad) const {
         const double l = ell, lp = ell_per, pr = period, s = scale;

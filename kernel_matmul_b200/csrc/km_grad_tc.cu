@@ -10,8 +10,9 @@
 // copies of images laid out by a pre-pass) into a tensor-memory stage, while the 128 * G consumer
 // threads -- one tensor-memory lane = one row each -- read the previous stage with tcgen05.ld,
 // evaluate the factors of d kappa / d p per entry and add coeff * factor to their running sums.
-// Per entry the FP32 pipe runs ~11 operations instead of k + 11, so the kernel is bound by the
-// SFU operations of kappa (3 per spectral entry).
+// Per entry the FP32 pipe runs ~11 operations instead of k + 11, issued as packed f32x2
+// instructions for two entries at a time, so the kernel is bound by the SFU operations of kappa
+// (3 per spectral entry).
 //
 // Reduction and chain rule are those of km_grad.cu: one partial record per (batch, row block),
 // then the fixed-order fp64 sum of launch_grad_finish.  Every mbarrier wait is bounded; a
@@ -157,9 +158,9 @@ __global__ void __launch_bounds__(128 * G + 32, 4) grad_tc_kernel(const GradTcAr
     const uint32_t tmem_base = tmem_base_slot;
 
     bool failed = false;
-    float sums[NS];
+    f32x2 sums2[NS];  // two partial sums per raw sum (packed FP32 arithmetic)
 #pragma unroll
-    for (int q = 0; q < NS; q++) sums[q] = 0.0f;
+    for (int q = 0; q < NS; q++) sums2[q] = 0ull;
 
     if (is_ctl_warp) {
         // -------------------------------------------- slot fetches (all lanes) + MMA issue (lane 0)
@@ -228,7 +229,7 @@ __global__ void __launch_bounds__(128 * G + 32, 4) grad_tc_kernel(const GradTcAr
         const int g = tid >> 7;
         const int row_local = tid & 127;
         const int64_t row = r * KM_BLOCK_SIZE + row_local;
-        const float x1v = row < a.m ? x1[row * a.x1.s0] : 0.0f;
+        const f32x2 x1v2 = splat2(row < a.m ? x1[row * a.x1.s0] : 0.0f);
         const uint32_t tmem_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(g * CPT);
 
         for (int t = 0; t < tiles; t++) {
@@ -251,17 +252,19 @@ __global__ void __launch_bounds__(128 * G + 32, 4) grad_tc_kernel(const GradTcAr
                 if (p + 1 < PIECES) tmem_ld16_nowait(tmem_lane + (uint32_t)(ds * GT_COLS + (p + 1) * 16), cbuf[(p + 1) & 1]);
 #pragma unroll
                 for (int h = 0; h < 4; h++) {
-                    const float4 xv = *reinterpret_cast<const float4 *>(xs + p * 16 + h * 4);
-                    const float xj[4] = {xv.x, xv.y, xv.z, xv.w};
+                    // four entries as two packed pairs
+                    const ulonglong2 xv = *reinterpret_cast<const ulonglong2 *>(xs + p * 16 + h * 4);
+                    float cf[4];
 #pragma unroll
                     for (int u = 0; u < 4; u++) {
-                        float coeff = __uint_as_float(cbuf[p & 1][h * 4 + u]);
+                        cf[u] = __uint_as_float(cbuf[p & 1][h * 4 + u]);
                         if (partial) {
                             const int j = j0 + p * 16 + h * 4 + u;
-                            if (j < band_lo || j >= band_hi) coeff = 0.0f;
+                            if (j < band_lo || j >= band_hi) cf[u] = 0.0f;
                         }
-                        fn.accumulate(x1v - xj[u], coeff, sums);
                     }
+                    fn.accumulate2(sub2(x1v2, xv.x), pack2(cf[0], cf[1]), sums2);
+                    fn.accumulate2(sub2(x1v2, xv.y), pack2(cf[2], cf[3]), sums2);
                 }
                 if (p + 1 < PIECES) tmem_ld_wait();
             }
@@ -274,7 +277,9 @@ __global__ void __launch_bounds__(128 * G + 32, 4) grad_tc_kernel(const GradTcAr
         // warp part of the CTA reduction
 #pragma unroll
         for (int q = 0; q < NS; q++) {
-            float v = sums[q];
+            float v, v_hi;
+            unpack2(sums2[q], v, v_hi);
+            v += v_hi;
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
             if (lane == 0) warp_sums[warp][q] = v;

@@ -20,9 +20,7 @@
 //    (TN_ISSUERS) did not raise that rate and costs issue slots, so there is one.)
 //  * accumulators live in tensor memory for at most TN_PROMO tiles (the tensor core adds with
 //    truncation; 16 hi*hi MMAs keep that bias below 1e-6) and are then added to fp32 registers
-//    of the generator that owns the row, two accumulators alternating.  Every MMA accumulates
-//    (MMAs of different issuers would not be ordered against each other); the generators write
-//    zeros into an accumulator when they have collected it.
+//    of the generator that owns the row, two accumulators alternating.
 //
 // Four CTAs share an SM (128 tensor-memory columns each).  All hand-offs are mbarriers; every
 // wait is bounded and a give-up is reported through the status word of the workspace.
@@ -45,6 +43,10 @@ constexpr int TN_TMEM_COLS = 128;
 #endif
 constexpr int TN_ISSUERS = TN_ISSUERS_DEF;        // control warps; warp w issues the 8-column steps w, w + TN_ISSUERS, ..
 constexpr int TN_THREADS = 128 + 32 * TN_ISSUERS;
+// MMAs of different issuers are not ordered against each other: with several issuers every MMA
+// accumulates and the generators zero an accumulator after collecting it; a single issuer
+// simply starts each group with a non-accumulating MMA.
+constexpr bool TN_ZEROED_ACC = TN_ISSUERS > 1;
 constexpr int TN_ACC_COL = TN_A_STAGES * 2 * TN_BK;  // first accumulator column (96)
 constexpr size_t TN_SMEM_BYTES = 48 * 1024;     // > slots: caps the SM at four CTAs (4 x 128 tensor-memory columns)
 static_assert(TN_ACC_COL + 2 * TN_N <= TN_TMEM_COLS, "tensor-memory budget");
@@ -146,8 +148,8 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    // both accumulators start at zero (every MMA accumulates)
-    if (!is_ctl_warp) {
+    // both accumulators start at zero when every MMA accumulates
+    if (TN_ZEROED_ACC && !is_ctl_warp) {
         uint32_t zero[16];
 #pragma unroll
         for (int u = 0; u < 16; u++) zero[u] = 0u;
@@ -223,7 +225,8 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
                 // this issuer's share of the tile's 8-column steps: the small cross terms first, hi * hi last
 #pragma unroll
                 for (int ks = issuer; ks < TN_BK / 8; ks += TN_ISSUERS) {
-                    mma_tf32_ts(d_tmem, a_hi + ks * 8, b_lo + ks * kstep, idesc, 1u);
+                    mma_tf32_ts(d_tmem, a_hi + ks * 8, b_lo + ks * kstep, idesc,
+                                (TN_ZEROED_ACC || ks > 0 || !grp_first) ? 1u : 0u);
                     mma_tf32_ts(d_tmem, a_lo + ks * 8, b_hi + ks * kstep, idesc, 1u);
                 }
 #pragma unroll
@@ -270,7 +273,7 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
             tmem_ld_wait();
 #pragma unroll
             for (int u = 0; u < 16; u++) acc[u] += __uint_as_float(v[u]);
-            if (rezero) {
+            if (TN_ZEROED_ACC && rezero) {
 #pragma unroll
                 for (int u = 0; u < 16; u++) v[u] = 0u;
                 tmem_st16(tmem_lane + (uint32_t)(TN_ACC_COL + ai * N), v);
@@ -324,6 +327,7 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
                 for (int u = 0; u < TN_BK; u++)
                     if (j0 + u < band_lo || j0 + u >= band_hi) kv[u] = 0.0f;
             }
+            // (scalar arithmetic on purpose: packed f32x2 operations made this kernel slower)
             uint32_t hi[TN_BK], lo[TN_BK];
 #pragma unroll
             for (int u = 0; u < TN_BK; u++) {
