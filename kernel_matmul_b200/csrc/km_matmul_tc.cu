@@ -450,6 +450,7 @@ extern "C" int km_matmul_tc_f32(int kernel_type, const km_batch *batch, int64_t 
     a.k = k;
     a.row_blocks = ceil_div(m, KM_BLOCK_SIZE);
     a.rb_begin = 0;
+    a.col_inv_scale = nullptr;
     a.n_pad = tc_n_pad(k);
     a.k_blocks = (int)ceil_div(k, a.n_pad);
     a.tmem_cols = 32;  // two accumulators of n_pad columns, rounded up to a power of two

@@ -3,62 +3,92 @@
 //   out[b, i, :] = sum_{j in band} kappa(x1[b,i], x2[b,j]) * rhs[b, j, :]
 //
 // With few rhs columns the contraction is cheap for the tensor core; what bounds the kernel is
-// generating the kernel-matrix entries (two SFU operations per spectral entry).  So the CTA is
-// built around its 128 generator threads, one per row of the 128-row block:
+// generating the kernel-matrix entries (two SFU operations per spectral entry) and the rate at
+// which a CTA gets tcgen05 instructions issued (one every ~45-100 cycles, measured).  So the
+// CTA is built around its 128 generator threads, one per row of the 128-row block, and the
+// contraction is arranged to need as few MMA instructions as possible:
 //
-//  * a generator evaluates the 16 entries of its row for a tile of 16 band columns, splits each
-//    into hi + lo (3xTF32) and writes both straight into TENSOR MEMORY with tcgen05.st: its row
-//    is its tensor-memory lane, the 16 values are 16 consecutive columns.  This is exactly the
-//    layout tcgen05.mma takes for an A operand in tensor memory (row i in lane i, one K value per
-//    32-bit column), so the kernel matrix never touches shared memory -- per entry the FP32 pipe
-//    only runs the ~7 operations of kappa and the split, against 5 + k on the FMA path;
-//  * a control warp fetches rhs tiles (images laid out by a pre-pass, one bulk copy per 64
-//    columns, hi and lo parts) and x2 values (cp.async) into a ring of shared-memory slots and
-//    one of its lanes issues the MMAs D[128 x 16] += A[128 x 8] . B[8 x 16] with A from tensor
-//    memory and B from shared memory.  (A CTA gets a tcgen05 instruction issued only every
-//    ~45-80 cycles, measured; splitting the MMAs of a tile over several issuing warps
-//    (TN_ISSUERS) did not raise that rate and costs issue slots, so there is one.)
+//  * operands are split into two fp16 parts, x = hi + lo (hi: the 11 leading bits, lo: the next
+//    11; the dropped lo * lo term is 2^-22 relative), so one MMA of kind::f16 covers K = 16 band
+//    columns and 16 columns take three MMAs, hi*lo + lo*hi + hi*hi (3xTF32 would need six: K = 8
+//    per instruction).  Kernel values lie in [-1, 1] and fit fp16 as they are (a lo part below
+//    2^-14 is a subnormal with an absolute error of at most 2^-25); the rhs is scaled per column
+//    by a power of two so that its largest magnitude lies in [2^13, 2^14) -- a pre-pass finds the
+//    column maxima, writes the scaled hi / lo images in the tensor core's K-major layout and
+//    the inverse scales, which the epilogue applies;
+//  * a generator evaluates the 32 entries of its row for a tile, splits them and writes both
+//    parts straight into TENSOR MEMORY with tcgen05.st: its row is its tensor-memory lane, the
+//    values are consecutive columns (two fp16 per column) -- exactly the layout tcgen05.mma takes
+//    for an A operand in tensor memory, so the kernel matrix never touches shared memory;
+//  * a control warp fetches rhs tiles (one bulk copy per 64 band columns) and x2 values
+//    (cp.async) into a ring of shared-memory slots and one of its lanes issues the MMAs
+//    D[128 x 16] += A[128 x 16] . B[16 x 16], six per tile;
 //  * accumulators live in tensor memory for at most TN_PROMO tiles (the tensor core adds with
-//    truncation; 16 hi*hi MMAs keep that bias below 1e-6) and are then added to fp32 registers
-//    of the generator that owns the row, two accumulators alternating.
+//    truncation) and are then added to fp32 registers of the generator that owns the row, two
+//    accumulators alternating.
 //
 // Four CTAs share an SM (128 tensor-memory columns each).  All hand-offs are mbarriers; every
 // wait is bounded and a give-up is reported through the status word of the workspace.
+#include <cuda_fp16.h>
+
 #include "km_tcgen05.cuh"
 
 namespace km {
 
 constexpr int TN_N = 16;                        // GEMM N: rhs columns (padded)
-constexpr int TN_BK = 16;                       // band columns per A stage
-constexpr int TN_SUPER = 4;                     // A tiles per rhs / x2 slot
+constexpr int TN_BK = 32;                       // band columns per tile: two MMA steps of K = 16
+constexpr int TN_SUPER = 2;                     // tiles per rhs / x2 slot
 constexpr int TN_SCOLS = TN_BK * TN_SUPER;      // band columns per slot (64)
-constexpr int TN_A_STAGES = 3;                  // A stages in tensor memory (32 columns each: hi | lo)
+constexpr int TN_A_STAGES = 3;                  // A stages in tensor memory
+constexpr int TN_A_COLS = TN_BK;                // tensor-memory columns per A stage: per 16 band columns hi 8 | lo 8
 constexpr int TN_SLOTS = 4;                     // rhs / x2 slots in shared memory
 constexpr int TN_PROMO = 8;                     // tiles per accumulator group
-constexpr int TN_IMG_FLOATS = 2 * TN_SCOLS * TN_N;  // hi + lo image of one slot
-constexpr int TN_SLOT_FLOATS = TN_IMG_FLOATS + TN_SCOLS;
+constexpr int TN_IMG_HALFS = 2 * TN_SCOLS * TN_N;   // hi + lo image of one slot (fp16 values)
+constexpr int TN_IMG_BYTES = TN_IMG_HALFS * 2;
+constexpr int TN_SLOT_BYTES = TN_IMG_BYTES + TN_SCOLS * 4;  // image + x2 values
 constexpr int TN_TMEM_COLS = 128;
-#ifndef TN_ISSUERS_DEF
-#define TN_ISSUERS_DEF 1
-#endif
-constexpr int TN_ISSUERS = TN_ISSUERS_DEF;        // control warps; warp w issues the 8-column steps w, w + TN_ISSUERS, ..
-constexpr int TN_THREADS = 128 + 32 * TN_ISSUERS;
-// MMAs of different issuers are not ordered against each other: with several issuers every MMA
-// accumulates and the generators zero an accumulator after collecting it; a single issuer
-// simply starts each group with a non-accumulating MMA.
-constexpr bool TN_ZEROED_ACC = TN_ISSUERS > 1;
-constexpr int TN_ACC_COL = TN_A_STAGES * 2 * TN_BK;  // first accumulator column (96)
+constexpr int TN_ACC_COL = TN_A_STAGES * TN_A_COLS;  // first accumulator column (96); two accumulators of 16
+constexpr int TN_THREADS = 160;
 constexpr size_t TN_SMEM_BYTES = 48 * 1024;     // > slots: caps the SM at four CTAs (4 x 128 tensor-memory columns)
+// per image slot in the workspace: [16 column maxima (bit patterns) | 16 inverse scales | padding]
+constexpr int TN_SCALE_WORDS = 64;
 static_assert(TN_ACC_COL + 2 * TN_N <= TN_TMEM_COLS, "tensor-memory budget");
-static_assert(TN_SLOTS * TN_SLOT_FLOATS * sizeof(float) <= TN_SMEM_BYTES, "shared-memory budget");
+static_assert(TN_SLOTS * TN_SLOT_BYTES <= TN_SMEM_BYTES, "shared-memory budget");
 
-// Pre-pass: rhs -> per (slot, 64-column group) image [part: hi, lo][chunk = jj / 4][c][jj % 4].
-// hi is the raw fp32 word (the tensor core reads its TF32 bits), lo = x - trunc_tf32(x).  Rows
-// past n and columns past k are zero.  Also clears the status word.
-__global__ void __launch_bounds__(256) tcn_rhs_images_kernel(Batch batch, int64_t slots, int64_t n, int64_t k,
-                                                             int64_t supers, View<const float> rhs, float *images,
-                                                             int *status) {
+// Pre-pass 1: column maxima of |rhs| as float bit patterns (monotone for non-negative floats).
+// The maxima words must be zero on entry.  Also clears the status word.
+__global__ void __launch_bounds__(256) tcn_colmax_kernel(Batch batch, int64_t slots, int64_t n, int64_t k,
+                                                         View<const float> rhs, unsigned *scales, int *status) {
     if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
+    const int c = threadIdx.x % TN_N;
+    const int64_t rows_per_pass = (int64_t)gridDim.x * (256 / TN_N);
+    for (int64_t slot = 0; slot < slots; slot++) {
+        const BatchIndex bi = decompose(batch, slot);
+        const float *base = batch_ptr(rhs, bi);
+        unsigned mx = 0u;
+        if (c < k)
+            for (int64_t j = blockIdx.x * (256 / TN_N) + threadIdx.x / TN_N; j < n; j += rows_per_pass)
+                mx = max(mx, __float_as_uint(fabsf(base[j * rhs.s0 + c * rhs.s1])));
+        // c = lane % 16: lanes l and l + 16 hold the same column
+        mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+        if ((threadIdx.x & 31) < TN_N && mx != 0u) atomicMax(scales + slot * TN_SCALE_WORDS + c, mx);
+    }
+}
+
+// Power-of-two scale that brings a column maximum into [2^13, 2^14); 1 for empty or non-finite columns.
+__device__ __forceinline__ float tcn_column_scale(unsigned max_bits) {
+    const int e = (int)(max_bits >> 23);  // biased exponent of the maximum: 2^(e - 127) <= max < 2^(e - 126)
+    if (e == 0 || e == 255) return 1.0f;
+    const int se = min(max(267 - e, 1), 254);  // scale = 2^(14 - (e - 126)), biased exponent 267 - e
+    return __uint_as_float((unsigned)se << 23);
+}
+
+// Pre-pass 2: rhs -> per (slot, 64-column group) image [part: hi, lo][chunk = jj / 8][c][jj % 8]
+// of fp16 values of the scaled column, y s = hi + lo (the K-major core-matrix layout of a
+// kind::f16 B operand); rows past n and columns past k are zero.  Also writes the inverse scales.
+__global__ void __launch_bounds__(256) tcn_rhs_images_kernel(Batch batch, int64_t slots, int64_t n, int64_t k,
+                                                             int64_t supers, View<const float> rhs, __half *images,
+                                                             unsigned *scales) {
     const int64_t total = slots * supers * (int64_t)(TN_SCOLS * TN_N);
     for (int64_t idx = blockIdx.x * 256LL + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * 256) {
         int64_t rem = idx;
@@ -69,40 +99,68 @@ __global__ void __launch_bounds__(256) tcn_rhs_images_kernel(Batch batch, int64_
         const int64_t sup = rem % supers;
         const int64_t slot = rem / supers;
         const int64_t j = sup * TN_SCOLS + jj;
+        const float sc = tcn_column_scale(scales[slot * TN_SCALE_WORDS + c]);
         float v = 0.0f;
         if (j < n && c < k) {
             const BatchIndex bi = decompose(batch, slot);
-            v = batch_ptr(rhs, bi)[j * rhs.s0 + c * rhs.s1];
+            v = batch_ptr(rhs, bi)[j * rhs.s0 + c * rhs.s1] * sc;
         }
-        float *img = images + (slot * supers + sup) * TN_IMG_FLOATS;
-        const int at = (jj >> 2) * (TN_N * 4) + c * 4 + (jj & 3);
-        img[at] = v;
-        img[TN_SCOLS * TN_N + at] = v - tf32_hi(v);
+        const __half hi = __float2half_rn(v);
+        const __half lo = __float2half_rn(v - __half2float(hi));
+        __half *img = images + (slot * supers + sup) * TN_IMG_HALFS;
+        const int at = (jj >> 3) * (TN_N * 8) + c * 8 + (jj & 7);
+        img[at] = hi;
+        img[TN_SCOLS * TN_N + at] = lo;
+        if (sup == 0 && jj == 0) reinterpret_cast<float *>(scales)[slot * TN_SCALE_WORDS + TN_N + c] = 1.0f / sc;
     }
+}
+
+// D (fp32, tensor memory) (+)= A (tensor memory, fp16: row i in lane i, two K values per 32-bit
+// column) . B (smem, fp16); M = 128, N from idesc, K = 16.
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// two fp32 -> one register of two fp16: `even` in the low half (K index 2i), `odd` in the high half
+__device__ __forceinline__ uint32_t pack_f16_rz(float even, float odd) {
+    uint32_t r;
+    asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(odd), "f"(even));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_f16_rn(float even, float odd) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(odd), "f"(even));
+    return r;
 }
 
 template <int KT>
 __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs a) {
     constexpr int N = TN_N;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[TN_SLOTS];    // rhs image + x2 of a slot landed
-    __shared__ __align__(8) uint64_t bar_sfree[TN_SLOTS];   // MMAs reading a slot are done
+    __shared__ __align__(8) uint64_t bar_full[TN_SLOTS];      // rhs image + x2 of a slot landed
+    __shared__ __align__(8) uint64_t bar_sfree[TN_SLOTS];     // MMAs reading a slot are done
     __shared__ __align__(8) uint64_t bar_ready[TN_A_STAGES];  // A stage written by the generators
     __shared__ __align__(8) uint64_t bar_empty[TN_A_STAGES];  // MMAs reading an A stage are done
-    __shared__ __align__(8) uint64_t bar_acc[2];            // accumulator group complete
-    __shared__ __align__(8) uint64_t bar_free[2];           // accumulator added to the registers
+    __shared__ __align__(8) uint64_t bar_acc[2];              // accumulator group complete
+    __shared__ __align__(8) uint64_t bar_free[2];             // accumulators added to the registers
     __shared__ uint32_t tmem_base_slot;
     __shared__ int fail_flag;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const bool is_ctl_warp = warp >= 4;
-    const int issuer = warp - 4;  // control warps: 0 also fetches
+    const bool is_ctl_warp = warp == 4;
 
-    float *smem_f = reinterpret_cast<float *>(smem_raw);
-    auto slot_img = [&](int sl) { return smem_f + sl * TN_SLOT_FLOATS; };
-    auto slot_x2 = [&](int sl) { return smem_f + sl * TN_SLOT_FLOATS + TN_IMG_FLOATS; };
+    auto slot_img = [&](int sl) { return smem_raw + sl * TN_SLOT_BYTES; };
+    auto slot_x2 = [&](int sl) { return reinterpret_cast<float *>(smem_raw + sl * TN_SLOT_BYTES + TN_IMG_BYTES); };
 
     int64_t item = blockIdx.x;
     const int64_t b = item % a.batch.count;
@@ -122,47 +180,38 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
     const int tiles = band_hi > band_lo ? (band_hi + TN_BK - 1) / TN_BK - tile_lo : 0;
     const int super_lo = tile_lo / TN_SUPER;
     const int supers = tiles > 0 ? (tile_lo + tiles - 1) / TN_SUPER - super_lo + 1 : 0;
-    const float *images = a.images + (a.image_slot_stride ? b * a.image_slot_stride : 0);
+    // a.images: fp16 images; a.image_slot_stride: bytes between image slots (0: rhs shared by all batches)
+    const int64_t img_slot = a.image_slot_stride ? b : 0;
+    const unsigned char *images = reinterpret_cast<const unsigned char *>(a.images) + img_slot * a.image_slot_stride;
+    const float *inv_scale = a.col_inv_scale + img_slot * TN_SCALE_WORDS;
 
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < TN_SLOTS; s++) {
             mbar_init(&bar_full[s], 33);  // 32 lanes' cp.async arrivals + the bulk copy's expect_tx arrival
-            mbar_init(&bar_sfree[s], TN_ISSUERS);
+            mbar_init(&bar_sfree[s], 1);
         }
 #pragma unroll
         for (int s = 0; s < TN_A_STAGES; s++) {
             mbar_init(&bar_ready[s], 4);
-            mbar_init(&bar_empty[s], TN_ISSUERS);
+            mbar_init(&bar_empty[s], 1);
         }
 #pragma unroll
         for (int i = 0; i < 2; i++) {
-            mbar_init(&bar_acc[i], TN_ISSUERS);
+            mbar_init(&bar_acc[i], 1);
             mbar_init(&bar_free[i], 4);
         }
         fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 4) tmem_alloc(&tmem_base_slot, TN_TMEM_COLS);
+    if (is_ctl_warp) tmem_alloc(&tmem_base_slot, TN_TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
-    // both accumulators start at zero when every MMA accumulates
-    if (TN_ZEROED_ACC && !is_ctl_warp) {
-        uint32_t zero[16];
-#pragma unroll
-        for (int u = 0; u < 16; u++) zero[u] = 0u;
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-        tmem_st16(lane_addr + (uint32_t)TN_ACC_COL, zero);
-        tmem_st16(lane_addr + (uint32_t)(TN_ACC_COL + TN_N), zero);
-        tmem_st_wait();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
 
-    constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
+    // instruction descriptor: D fp32, A / B fp16 (format code 0), both K-major, M = 128, N
+    constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
     bool failed = false;
 
     float acc[N];
@@ -184,18 +233,17 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
             }
             cp_async_mbar_arrive(&bar_full[sl]);
             if (lane == 0) {
-                constexpr uint32_t bytes = TN_IMG_FLOATS * sizeof(float);
-                mbar_expect_tx(&bar_full[sl], bytes);
-                bulk_copy_g2s(slot_img(sl), images + sup * TN_IMG_FLOATS, bytes, &bar_full[sl]);
+                mbar_expect_tx(&bar_full[sl], TN_IMG_BYTES);
+                bulk_copy_g2s(slot_img(sl), images + sup * TN_IMG_BYTES, TN_IMG_BYTES, &bar_full[sl]);
             }
         };
-        if (issuer == 0)
-            for (int sr = 0; sr < min(supers, TN_SLOTS); sr++) fetch(sr);
+        for (int sr = 0; sr < min(supers, TN_SLOTS); sr++) fetch(sr);
 
+        // B: core matrices of 8 columns (N) x 16 bytes (8 fp16 along K); K-adjacent matrices N * 16 bytes apart
         constexpr uint32_t lbo_b = N * 16, sbo = 128;
-        constexpr uint64_t slot_step = (uint64_t)(TN_SLOT_FLOATS * 4) >> 4;
-        constexpr uint64_t part_step = (uint64_t)(TN_SCOLS * N * 4) >> 4;  // hi -> lo image
-        constexpr uint64_t kstep = (uint64_t)(2 * lbo_b) >> 4;             // 8 band columns = 2 chunks
+        constexpr uint64_t slot_step = (uint64_t)TN_SLOT_BYTES >> 4;
+        constexpr uint64_t part_step = (uint64_t)(TN_SCOLS * N * 2) >> 4;  // hi -> lo image
+        constexpr uint64_t kstep = (uint64_t)(2 * lbo_b) >> 4;             // 16 band columns = 2 chunks
         const uint64_t d_b0 = smem_desc(smem_u32(slot_img(0)), lbo_b, sbo);
         int s = 0, use = 0, in_grp = 0, grp = 0;
         for (int t = 0; t < tiles; t++) {
@@ -220,25 +268,23 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t d_tmem = tmem_base + (uint32_t)(TN_ACC_COL + ai * N);
-                const uint32_t a_hi = tmem_base + (uint32_t)(s * 2 * TN_BK), a_lo = a_hi + TN_BK;
-                const uint64_t b_hi = d_b0 + sl * slot_step + (uint64_t)(q * (TN_BK / 8)) * kstep, b_lo = b_hi + part_step;
-                // this issuer's share of the tile's 8-column steps: the small cross terms first, hi * hi last
+                const uint32_t a_hi = tmem_base + (uint32_t)(s * TN_A_COLS), a_lo = a_hi + 8;
+                const uint64_t b_hi = d_b0 + sl * slot_step + (uint64_t)(q * (TN_BK / 16)) * kstep, b_lo = b_hi + part_step;
+                // the small cross terms first, hi * hi last
 #pragma unroll
-                for (int ks = issuer; ks < TN_BK / 8; ks += TN_ISSUERS) {
-                    mma_tf32_ts(d_tmem, a_hi + ks * 8, b_lo + ks * kstep, idesc,
-                                (TN_ZEROED_ACC || ks > 0 || !grp_first) ? 1u : 0u);
-                    mma_tf32_ts(d_tmem, a_lo + ks * 8, b_hi + ks * kstep, idesc, 1u);
+                for (int ks = 0; ks < TN_BK / 16; ks++) {
+                    mma_f16_ts(d_tmem, a_hi + ks * 16, b_lo + ks * kstep, idesc, (ks > 0 || !grp_first) ? 1u : 0u);
+                    mma_f16_ts(d_tmem, a_lo + ks * 16, b_hi + ks * kstep, idesc, 1u);
                 }
 #pragma unroll
-                for (int ks = issuer; ks < TN_BK / 8; ks += TN_ISSUERS)
-                    mma_tf32_ts(d_tmem, a_hi + ks * 8, b_hi + ks * kstep, idesc, 1u);
+                for (int ks = 0; ks < TN_BK / 16; ks++) mma_f16_ts(d_tmem, a_hi + ks * 16, b_hi + ks * kstep, idesc, 1u);
                 mma_commit(&bar_empty[s]);
                 if (slot_last) mma_commit(&bar_sfree[sl]);
                 if (grp_last) mma_commit(&bar_acc[ai]);
             }
             __syncwarp();
             // after the first tile of a slot: the previous slot is re-filled once its MMAs are done
-            if (issuer == 0 && slot_first && sr >= 1 && sr - 1 + TN_SLOTS < supers) {
+            if (slot_first && sr >= 1 && sr - 1 + TN_SLOTS < supers) {
                 const int prev = sr - 1;
                 ok = mbar_wait(&bar_sfree[prev % TN_SLOTS], (unsigned)((prev / TN_SLOTS) & 1));
                 if (!__all_sync(0xffffffffu, ok)) {
@@ -266,19 +312,13 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
         const float x1v = row < a.m ? x1[row * a.x1.s0] : 0.0f;
         const uint32_t tmem_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
 
-        auto collect = [&](int ai, bool rezero) {
+        auto collect = [&](int ai) {
             tc_fence_after();
             uint32_t v[16];
             tmem_ld16_nowait(tmem_lane + (uint32_t)(TN_ACC_COL + ai * N), v);
             tmem_ld_wait();
 #pragma unroll
             for (int u = 0; u < 16; u++) acc[u] += __uint_as_float(v[u]);
-            if (TN_ZEROED_ACC && rezero) {
-#pragma unroll
-                for (int u = 0; u < 16; u++) v[u] = 0u;
-                tmem_st16(tmem_lane + (uint32_t)(TN_ACC_COL + ai * N), v);
-                tmem_st_wait();
-            }
             tc_fence_before();
         };
 
@@ -299,7 +339,7 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
                     failed = true;
                     break;
                 }
-                collect(ai, true);
+                collect(ai);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_free[ai]);
             }
@@ -312,30 +352,39 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
                 tc_fence_after();
             }
             const float4 *xs = reinterpret_cast<const float4 *>(slot_x2(sl) + q * TN_BK);
-            float kv[TN_BK];
-#pragma unroll
-            for (int h = 0; h < TN_BK / 4; h++) {
-                const float4 xv = xs[h];
-                kv[4 * h + 0] = fn.unscaled(x1v - xv.x);
-                kv[4 * h + 1] = fn.unscaled(x1v - xv.y);
-                kv[4 * h + 2] = fn.unscaled(x1v - xv.z);
-                kv[4 * h + 3] = fn.unscaled(x1v - xv.w);
-            }
             const int j0 = ta * TN_BK;
-            if (j0 < band_lo || j0 + TN_BK > band_hi) {
+            const bool partial = j0 < band_lo || j0 + TN_BK > band_hi;
+            // 16 entries at a time: hi = kv truncated to fp16 (= the fp32 value with 10 mantissa
+            // bits for kv in fp16's normal range; below 2^-14 the two differ by less than 2^-24,
+            // far under the tolerance), lo = kv - hi rounded to fp16.  Tensor-memory columns of
+            // the 16 band columns: [8 hi pairs | 8 lo pairs].
 #pragma unroll
-                for (int u = 0; u < TN_BK; u++)
-                    if (j0 + u < band_lo || j0 + u >= band_hi) kv[u] = 0.0f;
-            }
-            // (scalar arithmetic on purpose: packed f32x2 operations made this kernel slower)
-            uint32_t hi[TN_BK], lo[TN_BK];
+            for (int half = 0; half < TN_BK / 16; half++) {
+                float kv[16];
 #pragma unroll
-            for (int u = 0; u < TN_BK; u++) {
-                hi[u] = __float_as_uint(kv[u]);
-                lo[u] = __float_as_uint(kv[u] - tf32_hi(kv[u]));
+                for (int h = 0; h < 4; h++) {
+                    const float4 xv = xs[half * 4 + h];
+                    kv[4 * h + 0] = fn.unscaled(x1v - xv.x);
+                    kv[4 * h + 1] = fn.unscaled(x1v - xv.y);
+                    kv[4 * h + 2] = fn.unscaled(x1v - xv.z);
+                    kv[4 * h + 3] = fn.unscaled(x1v - xv.w);
+                }
+                if (partial) {
+#pragma unroll
+                    for (int u = 0; u < 16; u++) {
+                        const int j = j0 + half * 16 + u;
+                        if (j < band_lo || j >= band_hi) kv[u] = 0.0f;
+                    }
+                }
+                uint32_t parts[16];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const float e = kv[2 * u], o = kv[2 * u + 1];
+                    parts[u] = pack_f16_rz(e, o);
+                    parts[8 + u] = pack_f16_rn(e - tf32_hi(e), o - tf32_hi(o));
+                }
+                tmem_st16(tmem_lane + (uint32_t)(s * TN_A_COLS + half * 16), parts);
             }
-            tmem_st16(tmem_lane + (uint32_t)(s * 2 * TN_BK), hi);
-            tmem_st16(tmem_lane + (uint32_t)(s * 2 * TN_BK + TN_BK), lo);
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
@@ -349,7 +398,7 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
                 failed = true;
                 break;
             }
-            collect(grp & 1, false);
+            collect(grp & 1);
         }
         if (failed) atomicExch(&fail_flag, 1);
     }
@@ -361,7 +410,16 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
     } else if (!is_ctl_warp) {
         const int64_t row = r * KM_BLOCK_SIZE + tid;
         if (row < a.m) {
-            const float scale = fn.scale;
+            // output scale times the inverse of the rhs column scale
+            float sc[N];
+#pragma unroll
+            for (int c = 0; c < N; c += 4) {
+                const float4 v = *reinterpret_cast<const float4 *>(inv_scale + c);
+                sc[c] = v.x * fn.scale;
+                sc[c + 1] = v.y * fn.scale;
+                sc[c + 2] = v.z * fn.scale;
+                sc[c + 3] = v.w * fn.scale;
+            }
             float *orow = out + (row - a.rb_begin * KM_BLOCK_SIZE) * a.out.s0;
             const bool vec_ok = a.out.s1 == 1 && (a.out.s0 % 4 == 0) && (a.k % 4 == 0) &&
                                 ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
@@ -369,21 +427,25 @@ __global__ void __launch_bounds__(TN_THREADS, 4) matmul_tcn_kernel(const TcArgs 
 #pragma unroll
                 for (int c = 0; c < N; c += 4)
                     if (c < a.k)
-                        *reinterpret_cast<float4 *>(orow + c) =
-                            make_float4(acc[c] * scale, acc[c + 1] * scale, acc[c + 2] * scale, acc[c + 3] * scale);
+                        *reinterpret_cast<float4 *>(orow + c) = make_float4(
+                            acc[c] * sc[c], acc[c + 1] * sc[c + 1], acc[c + 2] * sc[c + 2], acc[c + 3] * sc[c + 3]);
             } else {
 #pragma unroll
                 for (int c = 0; c < N; c++)
-                    if (c < a.k) orow[c * a.out.s1] = acc[c] * scale;
+                    if (c < a.k) orow[c * a.out.s1] = acc[c] * sc[c];
             }
         }
     }
-    if (warp == 4) tmem_free(tmem_base, TN_TMEM_COLS);
+    if (is_ctl_warp) tmem_free(tmem_base, TN_TMEM_COLS);
 }
+
+// workspace: [status, 256 B][per image slot: column maxima and inverse scales, 256 B][images]
+static size_t tcn_scale_bytes(int64_t slots) { return (size_t)slots * TN_SCALE_WORDS * sizeof(float); }
 
 size_t tcn_workspace_bytes(const Batch &b, int64_t n, const View<const float> &rhs) {
     const int64_t supers = ceil_div(n, TN_SCOLS);
-    return (size_t)TC_STATUS_BYTES + (size_t)(tc_slots(b, rhs) * supers) * TN_IMG_FLOATS * sizeof(float);
+    const int64_t slots = tc_slots(b, rhs);
+    return (size_t)TC_STATUS_BYTES + tcn_scale_bytes(slots) + (size_t)(slots * supers) * TN_IMG_BYTES;
 }
 
 template <int KT>
@@ -404,13 +466,21 @@ static int launch_tcn(const TcArgs &a, cudaStream_t s) {
 int tcn_matmul(int kernel_type, TcArgs a, const View<const float> &rhs, void *workspace, cudaStream_t s) {
     const int64_t slots = tc_slots(a.batch, rhs);
     const int64_t supers = ceil_div(a.n, TN_SCOLS);
-    a.status = static_cast<int *>(workspace);
-    float *images = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + TC_STATUS_BYTES);
-    a.images = images;
-    a.image_slot_stride = slots > 1 ? supers * (int64_t)TN_IMG_FLOATS : 0;
+    unsigned char *ws = static_cast<unsigned char *>(workspace);
+    a.status = reinterpret_cast<int *>(ws);
+    unsigned *scales = reinterpret_cast<unsigned *>(ws + TC_STATUS_BYTES);
+    __half *images = reinterpret_cast<__half *>(ws + TC_STATUS_BYTES + tcn_scale_bytes(slots));
+    a.images = reinterpret_cast<const float *>(images);
+    a.image_slot_stride = slots > 1 ? supers * (int64_t)TN_IMG_BYTES : 0;  // bytes, for this kernel
+    a.col_inv_scale = reinterpret_cast<const float *>(scales) + TN_N;
+    cudaError_t err = cudaMemsetAsync(scales, 0, tcn_scale_bytes(slots), s);
+    if (err != cudaSuccess) return cuda_fail(err, "km_matmul_tc_f32 (narrow) cudaMemsetAsync");
+    const unsigned max_blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(a.n, 16), 148 * 8));
+    tcn_colmax_kernel<<<max_blocks, 256, 0, s>>>(a.batch, slots, a.n, a.k, rhs, scales, a.status);
+    KM_CHECK_LAUNCH("km_matmul_tc_f32 (narrow) column-maximum launch");
     const int64_t total = slots * supers * (int64_t)(TN_SCOLS * TN_N);
     const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(total, 256), 148 * 32));
-    tcn_rhs_images_kernel<<<blocks, 256, 0, s>>>(a.batch, slots, a.n, a.k, supers, rhs, images, a.status);
+    tcn_rhs_images_kernel<<<blocks, 256, 0, s>>>(a.batch, slots, a.n, a.k, supers, rhs, images, scales);
     KM_CHECK_LAUNCH("km_matmul_tc_f32 (narrow) pre-pass launch");
     switch (kernel_type) {
     case KM_KERNEL_RBF: return launch_tcn<KM_KERNEL_RBF>(a, s);

@@ -21,7 +21,8 @@ struct TcArgs {
     View<const int> start, end;
     View<float> out;
     const float *images;         // [slot][k block][tile][chunk][c][4]
-    int64_t image_slot_stride;   // floats between batch slots (0: rhs shared by all batches)
+    int64_t image_slot_stride;   // floats (narrow kernel: bytes) between batch slots (0: rhs shared by all batches)
+    const float *col_inv_scale;  // narrow kernel: per image slot, inverse of the per-column rhs scales
     int *status;
 };
 

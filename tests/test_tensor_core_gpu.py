@@ -173,3 +173,26 @@ def test_tc_gradient_rejects_wide_operands():
     v = torch.randn(256, 40).cuda()
     with pytest.raises(KmError):
         ops.bilinear_derivative("rbf", x, x, v, v, torch.tensor([1.0, 1.0]).cuda(), start, end, path="tc")
+
+
+def test_tc_narrow_column_scales():
+    # the narrow kernel scales every rhs column by a power of two: columns of very different
+    # magnitude (and a zero column) must each keep fp32-level accuracy
+    from kernel_matmul_b200 import ops
+    from oracle import oracle as O
+
+    x = torch.sort(torch.rand(700) * 10)[0]
+    start, end = O.make_ranges(2.0, x)
+    params = torch.tensor([1.3, 0.6, 0.9])
+    rhs = torch.randn(700, 12)
+    mags = torch.tensor([1e-30, 1e-12, 1e-3, 1.0, 7.0, 1e4, 1e12, 1e30, 0.0, 3e-5, 2e5, 1.0])
+    rhs = rhs * mags
+    rhs[:, 11] = torch.randn(700).abs() * torch.logspace(-20, 0, 700)  # wide range inside one column
+    out = ops.matmul("spectral", x.cuda(), x.cuda(), rhs.cuda(), params.cuda(), start.cuda(), end.cuda(), path="tc")
+    assert ops.tc_status(out) == 0
+    ref = O.matmul("spectral", x, x, rhs, params, start, end)
+    for c in range(12):
+        if mags[c] == 0:
+            assert bool((out[:, c] == 0).all())
+        else:
+            assert rel_err(out[:, c], ref[:, c]) <= 1e-5, c
