@@ -16,8 +16,10 @@ Printed keys (one JSON line, rank 0):
   e2e        the same metric through the public ops with HOST (pinned) buffers: every step
              copies x, rhs, params and out_grad to the device, builds the band on the device,
              runs forward + gradient and copies out and grad back;
-  roofline   the dominant kernel against the FP32-pipe peak measured live with the library's
-             FFMA calibration kernel (FMA-equivalent TFLOP/s = 2 x FP32-pipe instructions);
+  roofline   the dominant kernel against the pipe that bounds it, measured live with the library's
+             calibration kernels: the SFU rate for the tensor-core kernels (the contraction runs as
+             tcgen05.mma; generating kappa costs 2-3 SFU operations per entry), the FP32 FFMA rate
+             for the FMA-pipe kernels (FMA-equivalent TFLOP/s = 2 x FP32-pipe instructions);
   cpu_baseline  the dense PyTorch formulation (materialise K, mask by ranges, matmul, autograd)
              in fp32 on all host cores, on a bounded sample of the same workload.
 
@@ -309,18 +311,29 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
         return out, g
 
     for _ in range(max(args.warmup, 3)):
-        step()
+        out_w, g_w = step()
     torch.cuda.synchronize()
+    # which kernels the ops chose (tensor cores for this width and size, else the FMA pipe);
+    # a tensor-core kernel reports a bounded wait that gave up through its status word
+    tc_fwd, tc_bwd = hasattr(out_w, "_km_workspace"), hasattr(g_w, "_km_workspace")
+    if ops.tc_status(out_w) != 0 or ops.tc_status(g_w) != 0:
+        raise RuntimeError("a tensor-core kernel reported a failed wait")
 
-    # ---- live FP32 peak (FFMA calibration kernel of the library)
+    # ---- live FP32 and SFU peaks (calibration kernels of the library)
     flops = ctypes.c_double()
+    sfu_ops = ctypes.c_double()
     stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
     def probe():
         check(lib.km_probe_fp32_peak(20000, None, ctypes.byref(flops), stream))
 
+    def probe_sfu():
+        check(lib.km_probe_sfu_peak(20000, None, ctypes.byref(sfu_ops), stream))
+
     probe()
     fp32_peak = max(flops.value / (cuda_ms(probe) * 1e-3) for _ in range(3)) / 1e12
+    probe_sfu()
+    sfu_peak = max(sfu_ops.value / (cuda_ms(probe_sfu) * 1e-3) for _ in range(3)) / 1e12
 
     # ---- timed region
     if world > 1:
@@ -398,9 +411,16 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
         e2e_value = units_all / (e2e_total / args.steps * 1e-3)
         fwd = statistics.mean(fwd_ms)
         bwd = statistics.mean(bwd_ms)
+        # Per-entry budgets.  FMA-pipe kernels: generation + k FMAs (+ P in the gradient).
+        # Tensor-core kernels: the contraction runs as tcgen05.mma, the threads only generate
+        # (forward: + 2 operations for the hi / lo split; gradient: + one FMA per parameter).
+        fwd_name = "matmul_tcn_kernel" if tc_fwd else "matmul_fma_kernel"
+        bwd_name = "grad_tc_kernel" if tc_bwd else "grad_band_kernel"
         kernels = {
-            "matmul_fma_kernel": {"ms": fwd, "fp32_instr_per_entry": fp32_instr_fwd(kt, k), "sfu_per_entry": GEN_FWD[kt][1]},
-            "grad_band_kernel": {"ms": bwd, "fp32_instr_per_entry": fp32_instr_bwd(kt, k), "sfu_per_entry": GEN_BWD[kt][1]},
+            fwd_name: {"ms": fwd, "sfu_per_entry": GEN_FWD[kt][1], "contraction": "tcgen05.mma kind::f16 (fp16 hi/lo split)" if tc_fwd else "fma.rn.f32x2",
+                       "fp32_instr_per_entry": GEN_FWD[kt][0] + 2 if tc_fwd else fp32_instr_fwd(kt, k)},
+            bwd_name: {"ms": bwd, "sfu_per_entry": GEN_BWD[kt][1], "contraction": "tcgen05.mma kind::tf32 (3xTF32)" if tc_bwd else "fma.rn.f32x2",
+                       "fp32_instr_per_entry": GEN_BWD[kt][0] + NPARAMS[kt] if tc_bwd else fp32_instr_bwd(kt, k)},
         }
         traffic = None
         tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
@@ -410,9 +430,22 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
         for kname, kd in kernels.items():
             kd["achieved_tflops"] = 2.0 * E * kd["fp32_instr_per_entry"] / (kd["ms"] * 1e-3) / 1e12
             kd["frac_fp32"] = kd["achieved_tflops"] / fp32_peak
-            sm_clk = (clocks["sm_mhz"] or 1965.0) * 1e6
-            kd["frac_sfu"] = E * kd["sfu_per_entry"] / (kd["ms"] * 1e-3) / (148 * 16 * sm_clk)
+            kd["achieved_sfu_tops"] = E * kd["sfu_per_entry"] / (kd["ms"] * 1e-3) / 1e12
+            kd["frac_sfu"] = kd["achieved_sfu_tops"] / sfu_peak
         d = kernels[dom]
+        dom_tc = (dom == fwd_name and tc_fwd) or (dom == bwd_name and tc_bwd)
+        if dom_tc:
+            roof = {"bound": "sfu", "kernel": dom, "achieved": d["achieved_sfu_tops"], "peak": sfu_peak,
+                    "unit": "Tops/s (special-function operations)", "frac": d["frac_sfu"], "traffic": traffic,
+                    "peak_source": "measured live: km_probe_sfu_peak (ex2.approx issue rate of all SMs); achieved = "
+                                   "algorithmic SFU operations per launch / CUDA-event time.  The contraction runs on "
+                                   "the tensor cores (a few % of their peak at this width); what bounds the kernel is "
+                                   "generating the kernel entries"}
+        else:
+            roof = {"bound": "fp32", "kernel": dom, "achieved": d["achieved_tflops"], "peak": fp32_peak,
+                    "unit": "TFLOP/s", "frac": d["frac_fp32"], "traffic": traffic,
+                    "peak_source": "measured live: km_probe_fp32_peak (FFMA issue rate of all SMs); achieved = 2 x "
+                                   "algorithmic FP32-pipe instructions per launch / CUDA-event time"}
         peaks = {}
         ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
         if os.path.exists(ppath):
@@ -428,17 +461,17 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
                 "per_rank": "own batch of 16 components (same seeded parameters on every rank), no collective",
             },
             "roofline": {
-                "bound": "fp32", "kernel": dom, "achieved": d["achieved_tflops"], "peak": fp32_peak,
-                "unit": "TFLOP/s", "frac": d["frac_fp32"], "traffic": traffic,
-                "peak_source": "measured live: km_probe_fp32_peak (FFMA issue rate of all SMs); achieved = 2 x "
-                               "algorithmic FP32-pipe instructions per launch / CUDA-event time",
+                **roof,
+                "fp32_peak_tflops": fp32_peak, "sfu_peak_tops": sfu_peak,
                 "hbm": {"algorithmic_bytes_per_step": hbm_bytes,
                         "frac_of_measured_hbm": (hbm_bytes / (ms_per_step * 1e-3)) / (peaks.get("hbm_gbs", 6650.0) * 1e9)},
                 "kernels": kernels,
             },
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "ms_per_step": e2e_total / args.steps},
-            "gpu_launches": 3 * args.steps,
+            # forward: product kernel (+ column-maximum and image pre-passes on the tensor-core path);
+            # gradient: band kernel + finish kernel (+ image pre-pass on the tensor-core path)
+            "gpu_launches": ((3 if tc_fwd else 1) + (3 if tc_bwd else 2)) * args.steps,
             "clocks": clocks,
             "wall_s": wall,
         }
@@ -621,7 +654,13 @@ def run_single_op(args, local: int) -> None:
 
     probe()
     fp32_peak = max(flops.value / (cuda_ms(probe) * 1e-3) for _ in range(3)) / 1e12
-    sm_clock = fp32_peak * 1e12 / (148 * 128 * 2)
+    sfu_ops = ctypes.c_double()
+
+    def probe_sfu():
+        check(lib.km_probe_sfu_peak(20000, None, ctypes.byref(sfu_ops), stream))
+
+    probe_sfu()
+    sfu_peak = max(sfu_ops.value / (cuda_ms(probe_sfu) * 1e-3) for _ in range(3)) / 1e12
 
     if name == "rbf_small":
         w = workloads.rbf_small()
@@ -642,8 +681,9 @@ def run_single_op(args, local: int) -> None:
         kt, k = "locally_periodic", w.rhs.shape[-1]
         E = int(ops.count_entries(w.n, w.n, start, end))
         fn = lambda: ops.bilinear_derivative(kt, xb, xb, lhs, rhs, params, start, end)  # noqa: E731
-        model = {"bound": "fp32", "fp32_instr": fp32_instr_bwd(kt, k), "sfu": GEN_BWD[kt][1]}
-        units, kernel = E * k, "grad_band_kernel"
+        # tensor-core gradient (k <= 32): threads only evaluate the factors of d kappa / d p
+        model = {"bound": "sfu", "fp32_instr": GEN_BWD[kt][0] + NPARAMS[kt], "sfu": GEN_BWD[kt][1]}
+        units, kernel = E * k, "grad_tc_kernel"
     elif name == "rbf_unbanded":
         w = workloads.rbf_unbanded(lookups=16)
         x = w.x.to(dev)
@@ -686,9 +726,13 @@ def run_single_op(args, local: int) -> None:
     elif model["bound"] == "hbm":
         roof.update(achieved=model["bytes"] / t / 1e9, peak=peaks.get("hbm_gbs", 6650.0), unit="GB/s",
                     peak_source="MEASURED_PEAKS.json hbm_gbs; algorithmic bytes = row + col + out per lookup")
+    elif model["bound"] == "sfu":
+        roof.update(achieved=E * model["sfu"] / t / 1e12, peak=sfu_peak, unit="Tops/s (special-function operations)",
+                    peak_source="live SFU probe (km_probe_sfu_peak); the coefficients run as tcgen05.mma",
+                    frac_fp32=2.0 * E * model["fp32_instr"] / t / 1e12 / fp32_peak)
     else:
         roof.update(achieved=2.0 * E * model["fp32_instr"] / t / 1e12, peak=fp32_peak, unit="TFLOP/s",
-                    peak_source="live FFMA probe", frac_sfu=E * model["sfu"] / t / (148 * 16 * sm_clock))
+                    peak_source="live FFMA probe", frac_sfu=E * model["sfu"] / t / 1e12 / sfu_peak)
     roof["frac"] = roof["achieved"] / roof["peak"]
     print(json.dumps({
         "metric": METRIC if name != "rbf_unbanded_index" else "gathered_kernel_entries_per_s",

@@ -297,6 +297,12 @@ KM_API int km_count_entries(const km_batch *batch, int64_t m, int64_t n, const k
  * FP32 FMA peak the roofline fractions are quoted against. */
 KM_API int km_probe_fp32_peak(int64_t iters, float *sink, double *flops_out, void *stream);
 
+/* Special-function-unit calibration: `iters` rounds of 8 independent ex2.approx chains per thread
+ * on every SM; the number of SFU operations is returned in *ops_out (host).  No reference
+ * counterpart; bench.py times it to obtain the measured SFU rate, which bounds the tensor-core
+ * kernels (their FP32-pipe work per entry is small; kappa costs 1-3 SFU operations per entry). */
+KM_API int km_probe_sfu_peak(int64_t iters, float *sink, double *ops_out, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -94,6 +94,8 @@ def _load() -> ctypes.CDLL:
     lib.km_count_entries.argtypes = [bp, i64, i64, wp, wp, vp, vp]
     lib.km_probe_fp32_peak.restype = ctypes.c_int
     lib.km_probe_fp32_peak.argtypes = [i64, vp, ctypes.POINTER(ctypes.c_double), vp]
+    lib.km_probe_sfu_peak.restype = ctypes.c_int
+    lib.km_probe_sfu_peak.argtypes = [i64, vp, ctypes.POINTER(ctypes.c_double), vp]
     return lib
 
 
@@ -106,7 +108,7 @@ EXPORTED = [
     "km_bilinear_derivative_f32", "km_bilinear_derivative_static_f32", "km_matmul_bwd_f32", "km_dense_f32", "km_dense_bwd_f32",
     "km_index_f32", "km_index_bwd_workspace_bytes", "km_index_bwd_f32", "km_make_ranges_f32",
     "km_make_ranges_symmetric_f32", "km_transpose_ranges_i32", "km_count_entries",
-    "km_probe_fp32_peak",
+    "km_probe_fp32_peak", "km_probe_sfu_peak",
 ]
 
 

@@ -68,6 +68,21 @@ __global__ void __launch_bounds__(256) fp32_peak_kernel(int64_t iters, float *si
     if (sink != nullptr && s == 123.456f) *sink = s;
 }
 
+// 8 independent chains of SFU exponentials per thread: measures the special-function rate.
+__global__ void __launch_bounds__(512) sfu_peak_kernel(int64_t iters, float *sink) {
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = (float)(threadIdx.x + i) * 1e-3f;
+    for (int64_t it = 0; it < iters; it++) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = ex2_approx(v[i]);
+    }
+    float s = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) s += v[i];
+    if (sink != nullptr && s == 123.456f) *sink = s;
+}
+
 }  // namespace km
 
 extern "C" const char *km_last_error(void) { return km::g_error; }
@@ -110,5 +125,20 @@ extern "C" int km_probe_fp32_peak(int64_t iters, float *sink, double *flops_out,
     fp32_peak_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(iters, sink);
     KM_CHECK_LAUNCH("km_probe_fp32_peak launch");
     if (flops_out) *flops_out = 2.0 * (double)blocks * threads * (double)iters * 64.0;
+    return KM_OK;
+}
+
+extern "C" int km_probe_sfu_peak(int64_t iters, float *sink, double *ops_out, void *stream) {
+    using namespace km;
+    KM_REQUIRE(iters > 0, KM_ERR_INVALID_ARGUMENT, "km_probe_sfu_peak: iters must be positive");
+    int dev = 0, sms = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return cuda_fail(err, "cudaGetDevice");
+    err = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (err != cudaSuccess) return cuda_fail(err, "cudaDeviceGetAttribute");
+    const int blocks = sms * 2, threads = 512;
+    sfu_peak_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(iters, sink);
+    KM_CHECK_LAUNCH("km_probe_sfu_peak launch");
+    if (ops_out) *ops_out = (double)blocks * threads * (double)iters * 8.0;
     return KM_OK;
 }

@@ -196,3 +196,32 @@ def test_tc_narrow_column_scales():
             assert bool((out[:, c] == 0).all())
         else:
             assert rel_err(out[:, c], ref[:, c]) <= 1e-5, c
+
+
+def test_auto_path_selection_for_narrow_operands():
+    from kernel_matmul_b200 import ops
+    from oracle import oracle as O
+
+    batch = (4,)
+    x = torch.sort(torch.rand(8192) * 100)[0]
+    start, end = O.make_ranges(2.0, x)
+    params = make_params("spectral", batch)
+    xd, sd, ed, pd = x.cuda(), start.cuda(), end.cuda(), params.cuda()
+    for k, expect_tc in [(16, True), (9, True), (4, False)]:
+        rhs = torch.randn(8192, k).cuda()
+        out = ops.matmul("spectral", xd.expand(4, -1), xd.expand(4, -1), rhs.expand(4, -1, -1), pd, sd, ed)
+        assert hasattr(out, "_km_workspace") == expect_tc
+        assert ops.tc_status(out) == 0
+        fma = ops.matmul("spectral", xd.expand(4, -1), xd.expand(4, -1), rhs.expand(4, -1, -1), pd, sd, ed, path="fma")
+        assert rel_err(out, fma) <= 1e-5
+    left = torch.randn(4, 8192, 16).cuda()
+    right = torch.randn(4, 8192, 16).cuda()
+    g = ops.bilinear_derivative("spectral", xd.expand(4, -1), xd.expand(4, -1), left, right, pd, sd, ed)
+    assert hasattr(g, "_km_workspace") and ops.tc_status(g) == 0
+    g4 = ops.bilinear_derivative("spectral", xd.expand(4, -1), xd.expand(4, -1), left[..., :4], right[..., :4], pd, sd, ed)
+    assert not hasattr(g4, "_km_workspace")
+    # small problems stay on the FMA pipe whatever the width
+    xs = xd[:300]
+    ss, es = O.make_ranges(2.0, x[:300])
+    small = ops.matmul("spectral", xs, xs, torch.randn(300, 16).cuda(), pd[0], ss.cuda(), es.cuda())
+    assert not hasattr(small, "_km_workspace")
