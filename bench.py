@@ -1,6 +1,7 @@
 """Benchmark of the kernel-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+                    [--path auto|fma|tc]
 
 Workload at the default settings: the spectral-mixture configuration (16 components sharing
 x and rhs, m = n = 65536 sorted U[0, 500], l ~ LogUniform[0.5, 5], f ~ U[0, 2], cutoff 4 l,
@@ -305,9 +306,11 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
 
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB of L2
 
+    path = args.path
+
     def step():
-        out = ops.matmul(kt, xb, xb, rhs, params, start, end)
-        g = ops.matmul_bwd(kt, xb, xb, rhs, params, start, end, og)
+        out = ops.matmul(kt, xb, xb, rhs, params, start, end, path=path)
+        g = ops.matmul_bwd(kt, xb, xb, rhs, params, start, end, og, path=path)
         return out, g
 
     for _ in range(max(args.warmup, 3)):
@@ -348,9 +351,9 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
         flush.fill_(1)
         e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
         e0.record()
-        ops.matmul(kt, xb, xb, rhs, params, start, end)
+        ops.matmul(kt, xb, xb, rhs, params, start, end, path=path)
         e1.record()
-        ops.matmul_bwd(kt, xb, xb, rhs, params, start, end, og)
+        ops.matmul_bwd(kt, xb, xb, rhs, params, start, end, og, path=path)
         e2.record()
         e2.synchronize()
         fwd_ms.append(e0.elapsed_time(e1))
@@ -379,8 +382,8 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
         dog = hog.to(dev, non_blocking=True)
         st, en = workloads.band(w, dx)
         dxb = dx.expand(B, -1)
-        out = ops.matmul(kt, dxb, dxb, drhs, dp, st, en)
-        g = ops.matmul_bwd(kt, dxb, dxb, drhs, dp, st, en, dog)
+        out = ops.matmul(kt, dxb, dxb, drhs, dp, st, en, path=path)
+        g = ops.matmul_bwd(kt, dxb, dxb, drhs, dp, st, en, dog, path=path)
         hout.copy_(out, non_blocking=True)
         hgrad.copy_(g, non_blocking=True)
 
@@ -456,7 +459,7 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": {
-                "workload": w.name, "ops": "matmul fwd + matmul_bwd", "entries_per_rank": E, "rhs_cols": k,
+                "workload": w.name, "ops": "matmul fwd + matmul_bwd", "path": path, "entries_per_rank": E, "rhs_cols": k,
                 "units_per_step": units_all, "l2": "flushed between steps (256 MB write)",
                 "per_rank": "own batch of 16 components (same seeded parameters on every rank), no collective",
             },
@@ -753,6 +756,9 @@ def main() -> None:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="spectral_mixture")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--path", default="auto", choices=["auto", "fma", "tc"],
+                    help="default workload: kernels of the ops (auto: what the ops choose; fma: FMA-pipe kernels; "
+                         "tc: tensor-core kernels)")
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.impl == "reference":
