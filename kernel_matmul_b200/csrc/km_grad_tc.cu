@@ -17,6 +17,8 @@
 // Reduction and chain rule are those of km_grad.cu: one partial record per (batch, row block),
 // then the fixed-order fp64 sum of launch_grad_finish.  Every mbarrier wait is bounded; a
 // give-up is reported through the status word of the workspace.
+#include <type_traits>
+
 #include "km_tcgen05.cuh"
 
 namespace km {
@@ -74,8 +76,11 @@ __global__ void __launch_bounds__(256) grad_tc_images_kernel(Batch batch, int64_
 
 // G consumer groups of 128 threads (group g takes the columns [g * 64 / G, (g + 1) * 64 / G) of
 // every tile) + one control warp.
+#ifndef GT_MIN_CTAS
+#define GT_MIN_CTAS 4
+#endif
 template <int KT, int G>
-__global__ void __launch_bounds__(128 * G + 32, 4) grad_tc_kernel(const GradTcArgs a) {
+__global__ void __launch_bounds__(128 * G + 32, GT_MIN_CTAS) grad_tc_kernel(const GradTcArgs a) {
     constexpr int WARPS = 4 * G;
     constexpr int NS = KernelFn<KT>::NSUMS;
     constexpr int CPT = GT_COLS / G;   // columns per thread and tile
@@ -242,32 +247,41 @@ __global__ void __launch_bounds__(128 * G + 32, 4) grad_tc_kernel(const GradTcAr
             }
             tc_fence_after();
             const int j0 = (tile_lo + t) * GT_COLS + g * CPT;
-            const bool partial = j0 < band_lo || j0 + CPT > band_hi;
             const float *xs = slot_x2(sl) + g * CPT;
-            uint32_t cbuf[2][16];
-            tmem_ld16_nowait(tmem_lane + (uint32_t)(ds * GT_COLS), cbuf[0]);
-            tmem_ld_wait();
+            // Two copies of the loop body: the band mask costs ~8 instructions per entry when the
+            // compiler turns it into selects, and only the first and last tile of a band need it.
+            auto consume = [&](auto masked_tag) {
+                constexpr bool MASKED = decltype(masked_tag)::value;
+                uint32_t cbuf[2][16];
+                tmem_ld16_nowait(tmem_lane + (uint32_t)(ds * GT_COLS), cbuf[0]);
+                tmem_ld_wait();
 #pragma unroll
-            for (int p = 0; p < PIECES; p++) {
-                if (p + 1 < PIECES) tmem_ld16_nowait(tmem_lane + (uint32_t)(ds * GT_COLS + (p + 1) * 16), cbuf[(p + 1) & 1]);
+                for (int p = 0; p < PIECES; p++) {
+                    if (p + 1 < PIECES)
+                        tmem_ld16_nowait(tmem_lane + (uint32_t)(ds * GT_COLS + (p + 1) * 16), cbuf[(p + 1) & 1]);
 #pragma unroll
-                for (int h = 0; h < 4; h++) {
-                    // four entries as two packed pairs
-                    const ulonglong2 xv = *reinterpret_cast<const ulonglong2 *>(xs + p * 16 + h * 4);
-                    float cf[4];
+                    for (int h = 0; h < 4; h++) {
+                        // four entries as two packed pairs
+                        const ulonglong2 xv = *reinterpret_cast<const ulonglong2 *>(xs + p * 16 + h * 4);
+                        uint32_t cf[4];
 #pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        cf[u] = __uint_as_float(cbuf[p & 1][h * 4 + u]);
-                        if (partial) {
-                            const int j = j0 + p * 16 + h * 4 + u;
-                            if (j < band_lo || j >= band_hi) cf[u] = 0.0f;
+                        for (int u = 0; u < 4; u++) {
+                            cf[u] = cbuf[p & 1][h * 4 + u];
+                            if (MASKED) {
+                                const int j = j0 + p * 16 + h * 4 + u;
+                                if (j < band_lo || j >= band_hi) cf[u] = 0u;
+                            }
                         }
+                        fn.accumulate2(sub2(x1v2, xv.x), (f32x2)cf[0] | ((f32x2)cf[1] << 32), sums2);
+                        fn.accumulate2(sub2(x1v2, xv.y), (f32x2)cf[2] | ((f32x2)cf[3] << 32), sums2);
                     }
-                    fn.accumulate2(sub2(x1v2, xv.x), pack2(cf[0], cf[1]), sums2);
-                    fn.accumulate2(sub2(x1v2, xv.y), pack2(cf[2], cf[3]), sums2);
+                    if (p + 1 < PIECES) tmem_ld_wait();
                 }
-                if (p + 1 < PIECES) tmem_ld_wait();
-            }
+            };
+            if (j0 < band_lo || j0 + CPT > band_hi)
+                consume(std::true_type{});
+            else
+                consume(std::false_type{});
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_dfree[ds]);
@@ -323,8 +337,10 @@ static int launch_grad_tc(const GradTcArgs &a, cudaStream_t s) {
     return KM_OK;
 }
 
+// consumer groups for up to 16 columns (one group: more registers per thread; measured equal for
+// spectral kernels and 10 % faster for RBF than two groups)
 #ifndef GT_G_SMALL
-#define GT_G_SMALL 2
+#define GT_G_SMALL 1
 #endif
 template <int KT>
 static int dispatch_grad_tc(const GradTcArgs &a, cudaStream_t s) {

@@ -1,129 +1,207 @@
-// Forward product on the 5th-generation tensor cores (tcgen05 + TMEM) for wide right-hand sides.
+// Forward product on the tensor cores with the kernel-matrix tiles handed over in tensor memory.
 //
 //   out[b, i, :] = sum_{j in band} kappa(x1[b,i], x2[b,j]) * rhs[b, j, :]
 //
-// is a dense contraction once rhs has tens of columns: per 128-row block it is the GEMM
-// D[128 x N] = A[128 x band] . B[band x N] whose A operand (the kernel-matrix tile) never
-// exists in memory.  One CTA owns a row block; its threads generate A tiles of 128 x 32 entries
-// straight into shared memory in the tensor core's K-major core-matrix layout, a single thread
-// issues tcgen05.mma instructions that accumulate into tensor memory, and the generation of
-// tile t+1 overlaps the MMAs of tile t (two shared-memory stages, mbarrier hand-off through
-// tcgen05.commit).  The rhs tiles arrive as one bulk asynchronous copy per tile
-// (cp.async.bulk, the non-tensor form of TMA, completing on an mbarrier) from images that a
-// small pre-pass kernel lays out once per call.
+// For the widths this path sees (1 ... a few hundred rhs columns) the contraction is cheap for
+// the tensor core; what bounds the kernel is generating the kernel-matrix entries (two SFU
+// operations per spectral entry) and the rate at which a CTA gets tcgen05 instructions issued
+// (one every ~45-100 cycles, measured).  So the
+// CTA is built around its 128 generator threads, one per row of the 128-row block, and the
+// contraction is arranged to need as few MMA instructions as possible:
 //
-// Precision: the tensor cores multiply TF32 (10-bit mantissa).  To stay within fp32 accuracy
-// both operands are split x = hi + lo with hi the TF32-truncated value and lo the exact
-// remainder, and three MMAs hi*hi + hi*lo + lo*hi are issued per K step ("3xTF32"); the
-// dropped lo*lo term and the truncation of lo are ~2^-21 relative.  The tensor core adds into
-// its fp32 accumulator with truncation, a bias that grows with the number of accumulations
-// (measured: 1.5e-5 relative after 750 MMAs), so a tensor-memory accumulator only ever holds
-// a group of TC_PROMO tiles (16 hi*hi MMAs, bias < 1e-6): within a tile the small cross terms
-// are issued first and the hi*hi MMAs last, and a finished group is added to fp32 registers
-// (round-to-nearest) while the next groups are generated -- two accumulators alternate.
+//  * operands are split into two fp16 parts, x = hi + lo (hi: the 11 leading bits, lo: the next
+//    11; the dropped lo * lo term is 2^-22 relative), so one MMA of kind::f16 covers K = 16 band
+//    columns and 16 columns take three MMAs, hi*lo + lo*hi + hi*hi (3xTF32 would need six: K = 8
+//    per instruction).  Kernel values lie in [-1, 1] and fit fp16 as they are (a lo part below
+//    2^-14 is a subnormal with an absolute error of at most 2^-25); the rhs is scaled per column
+//    by a power of two so that its largest magnitude lies in [2^13, 2^14) -- a pre-pass finds the
+//    column maxima, writes the scaled hi / lo images in the tensor core's K-major layout and
+//    the inverse scales, which the epilogue applies;
+//  * a generator evaluates the 32 entries of its row for a tile, splits them and writes both
+//    parts straight into TENSOR MEMORY with tcgen05.st: its row is its tensor-memory lane, the
+//    values are consecutive columns (two fp16 per column) -- exactly the layout tcgen05.mma takes
+//    for an A operand in tensor memory, so the kernel matrix never touches shared memory;
+//  * a control warp fetches rhs tiles (one bulk copy per 64 band columns) and x2 values
+//    (cp.async) into a ring of shared-memory slots and one of its lanes issues the MMAs
+//    D[128 x N] += A[128 x 16] . B[16 x N] (N = 16, 32, 64 or 128; wider right-hand sides are
+//    processed in blocks of 128 columns), six per tile;
+//  * accumulators live in tensor memory for at most TC_PROMO tiles (the tensor core adds with
+//    truncation) and are then added to fp32 registers of the generator that owns the row, two
+//    accumulators alternating.
 //
-// Every wait on an mbarrier is bounded; a wait that gives up records a code in the status word
-// of the workspace and the CTA leaves through the normal exit (tensor memory released).
+// Four CTAs share an SM at N = 16 (128 tensor-memory columns each; three at N = 32, two at
+// N = 64, one with 256 generator threads at N = 128).  All hand-offs are mbarriers; every
+// wait is bounded and a give-up is reported through the status word of the workspace.
+#include <cuda_fp16.h>
+
 #include "km_tcgen05.cuh"
 
 namespace km {
 
-constexpr int TC_BK = 32;             // band columns (GEMM K) per stage
-constexpr int TC_STAGES = 3;           // A (and rhs-lo) stages
-constexpr int TC_B_STAGES = 5;         // raw rhs tiles in flight / in use
-constexpr int TC_B_AHEAD = TC_B_STAGES - TC_STAGES;  // prefetch distance in tiles
-constexpr int TC_PROMO = 4;           // tiles accumulated in tensor memory before promotion to registers
+constexpr int TC_MAX_N = 128;                   // widest GEMM N (rhs columns per CTA) of this kernel
+constexpr int TC_BK = 32;                       // band columns per tile: two MMA steps of K = 16
+constexpr int TC_SUPER = 2;                     // tiles per rhs / x2 slot
+constexpr int TC_SCOLS = TC_BK * TC_SUPER;      // band columns per slot (64)
+constexpr int TC_A_COLS = TC_BK;                // tensor-memory columns per A stage: per 16 band columns hi 8 | lo 8
+constexpr int TC_SLOTS = 4;                     // rhs / x2 slots in shared memory
+constexpr int TC_PROMO = 8;                     // tiles per accumulator group
+// per image slot in the workspace: [TC_MAX_N column maxima (bit patterns) | TC_MAX_N inverse scales]
+constexpr int TC_SCALE_WORDS = 2 * TC_MAX_N;
 
-// ------------------------------------------------------------------------- rhs images pre-pass
+// Per GEMM width N (rhs columns padded to 16 / 32 / 64 / 128): tensor-memory and shared-memory budget.
+//   N = 16:  3 A stages (96 columns) + 2 accumulators of 16 = 128 columns, 4 CTAs per SM
+//   N = 32:  2 A stages (64)         + 2 x 32            = 128 columns, 3 CTAs per SM (registers)
+//   N = 64:  3 A stages (96)         + 2 x 64            = 224 -> 256 columns, 2 CTAs per SM
+//   N = 128: 3 A stages (96)         + 2 x 128           = 352 -> 512 columns, 1 CTA per SM with two
+//            generator groups of 128 threads: group g generates the band columns [16g, 16g + 16) of
+//            every tile and owns the accumulator columns [64g, 64g + 64) of its row
+template <int N>
+struct TcCfg {
+    static constexpr int G = N == 128 ? 2 : 1;  // generator groups of 128 threads
+    static constexpr int THREADS = 128 * G + 32;
+    static constexpr int A_STAGES = N == 32 ? 2 : 3;
+    static constexpr int ACC_COL = A_STAGES * TC_A_COLS;
+    static constexpr int TMEM_COLS = N <= 32 ? 128 : (N == 64 ? 256 : 512);
+    static constexpr int MIN_CTAS = N == 16 ? 4 : (N == 32 ? 3 : (N == 64 ? 2 : 1));
+    static constexpr int IMG_HALFS = 2 * TC_SCOLS * N;  // hi + lo image of one slot (fp16 values)
+    static constexpr int IMG_BYTES = IMG_HALFS * 2;
+    static constexpr int SLOT_BYTES = IMG_BYTES + TC_SCOLS * 4;  // image + x2 values
+    // dynamic shared memory: the slots, padded so that no more CTAs fit an SM than its 512
+    // tensor-memory columns can serve
+    static constexpr size_t SMEM_BYTES = N <= 32 ? 48 * 1024 : (N == 64 ? 80 * 1024 : 136 * 1024);
+    static_assert(ACC_COL + 2 * N <= TMEM_COLS, "tensor-memory budget");
+    static_assert(TC_SLOTS * SLOT_BYTES <= SMEM_BYTES, "shared-memory budget");
+};
 
-// Writes, for every (slot, k block, 32-column tile), the rhs tile transposed into the K-major
-// core-matrix layout: image[chunk = jj / 4][c][jj % 4], c the column inside the k block (the
-// tensor core reads the TF32 bits of these words as the "hi" operand; the "lo" operand is
-// derived from them in shared memory by the product kernel).  Rows past n and columns past k
-// are zero.  Also clears the status word.
-__global__ void __launch_bounds__(256) tc_rhs_images_kernel(Batch batch, int64_t slots, int64_t n, int64_t k,
-                                                            int64_t tiles, int k_blocks, int n_pad,
-                                                            View<const float> rhs, float *images, int *status) {
+// Pre-pass 1: column maxima of |rhs| as float bit patterns (monotone for non-negative floats).
+// The maxima words must be zero on entry.  Also clears the status word.
+__global__ void __launch_bounds__(256) tc_colmax_kernel(Batch batch, int64_t slots, int64_t n, int64_t k, int npad,
+                                                         int kblocks, View<const float> rhs, unsigned *scales,
+                                                         int *status) {
     if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
-    const int64_t per_tile = (int64_t)TC_BK * n_pad;
-    const int64_t total = slots * k_blocks * tiles * (int64_t)TC_BK * n_pad;
-    for (int64_t idx = blockIdx.x * 256LL + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * 256) {
-        // idx -> (slot, kb, tile, jj, c) with c fastest: coalesced reads of rhs rows
-        int64_t rem = idx;
-        const int c = (int)(rem % n_pad);
-        rem /= n_pad;
-        const int jj = (int)(rem % TC_BK);
-        rem /= TC_BK;
-        const int64_t tile = rem % tiles;
-        rem /= tiles;
-        const int kb = (int)(rem % k_blocks);
-        const int64_t slot = rem / k_blocks;
-        const int64_t j = tile * TC_BK + jj;
-        const int64_t col = (int64_t)kb * n_pad + c;
-        float v = 0.0f;
-        if (j < n && col < k) {
-            const BatchIndex bi = decompose(batch, slot);
-            v = batch_ptr(rhs, bi)[j * rhs.s0 + col * rhs.s1];
+    const int64_t rows_per_pass = (int64_t)gridDim.x * 16;
+    for (int64_t slot = 0; slot < slots; slot++) {
+        const BatchIndex bi = decompose(batch, slot);
+        const float *base = batch_ptr(rhs, bi);
+        for (int c0 = 0; c0 < k; c0 += 16) {
+            const int c = c0 + threadIdx.x % 16;
+            unsigned mx = 0u;
+            if (c < k)
+                for (int64_t j = blockIdx.x * 16 + threadIdx.x / 16; j < n; j += rows_per_pass)
+                    mx = max(mx, __float_as_uint(fabsf(base[j * rhs.s0 + c * rhs.s1])));
+            // column = lane % 16: lanes l and l + 16 hold the same column
+            mx = max(mx, __shfl_xor_sync(0xffffffffu, mx, 16));
+            if ((threadIdx.x & 31) < 16 && mx != 0u)
+                atomicMax(scales + (slot * kblocks + c / npad) * TC_SCALE_WORDS + c % npad, mx);
         }
-        float *img = images + ((slot * k_blocks + kb) * tiles + tile) * per_tile;
-        img[(int64_t)(jj >> 2) * (n_pad * 4) + c * 4 + (jj & 3)] = v;
     }
 }
 
-// ----------------------------------------------------------------------------------- kernel
+// Power-of-two scale that brings a column maximum into [2^13, 2^14); 1 for empty or non-finite columns.
+__device__ __forceinline__ float tc_column_scale(unsigned max_bits) {
+    const int e = (int)(max_bits >> 23);  // biased exponent of the maximum: 2^(e - 127) <= max < 2^(e - 126)
+    if (e == 0 || e == 255) return 1.0f;
+    const int se = min(max(267 - e, 1), 254);  // scale = 2^(14 - (e - 126)), biased exponent 267 - e
+    return __uint_as_float((unsigned)se << 23);
+}
 
-// N = GEMM N (rhs columns per CTA, 64 or 128).  128 * G generator threads + one MMA warp.
-//
-// Generator thread (row = tid % 128, g = tid / 128) produces the columns
-// [g * 32 / G, (g + 1) * 32 / G) of its row in every A tile, derives its share of the rhs "lo"
-// tile, and owns the output columns [g * N / G, (g + 1) * N / G) of its row in registers.  The
-// MMA warp (one lane) fetches rhs tiles ahead of time and issues the MMAs.  The two sides meet
-// only through mbarriers -- there is no CTA-wide barrier inside the band loop:
-//   bar_full[bs]   raw rhs tile landed (bulk copy transaction count)   MMA warp -> generators
-//   bar_ready[s]   A tile and rhs-lo tile of stage s written           generators -> MMA warp
-//   bar_empty[s]   MMAs that read stage s are done (tcgen05.commit)     tensor core -> everyone
-//   bar_acc[ai]    a group of tiles is complete in accumulator ai      tensor core -> generators
-//   bar_free[ai]   accumulator ai has been added to the registers      generators -> MMA warp
-template <int KT, int N, int G>
-__global__ void __launch_bounds__(128 * G + 32) matmul_tc_kernel(const TcArgs a) {
-    constexpr int GEN_THREADS = 128 * G;
-    constexpr int GEN_WARPS = 4 * G;
-    constexpr int A_PART = 128 * TC_BK;  // floats per hi / lo part of an A stage
-    constexpr int B_TILE = TC_BK * N;    // floats per rhs tile image
-    constexpr int NPT = N / G;           // accumulator columns per thread
-    constexpr int CPT = TC_BK / 4 / G;   // 4-column chunks generated per thread and tile
-    static_assert(NPT % 16 == 0, "columns per thread must be a multiple of 16");
-    static_assert((B_TILE / 4) % GEN_THREADS == 0, "rhs tile must split evenly over the threads");
+// Pre-pass 2: rhs -> per (slot, 64-column group) image [part: hi, lo][chunk = jj / 8][c][jj % 8]
+// of fp16 values of the scaled column, y s = hi + lo (the K-major core-matrix layout of a
+// kind::f16 B operand); rows past n and columns past k are zero.  Also writes the inverse scales.
+__global__ void __launch_bounds__(256) tc_rhs_images_kernel(Batch batch, int64_t slots, int64_t n, int64_t k, int npad,
+                                                             int kblocks, int64_t supers, View<const float> rhs,
+                                                             __half *images, unsigned *scales) {
+    const int64_t total = slots * kblocks * supers * (int64_t)(TC_SCOLS * npad);
+    for (int64_t idx = blockIdx.x * 256LL + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * 256) {
+        int64_t rem = idx;
+        const int c = (int)(rem % npad);
+        rem /= npad;
+        const int jj = (int)(rem % TC_SCOLS);
+        rem /= TC_SCOLS;
+        const int64_t sup = rem % supers;
+        rem /= supers;
+        const int kb = (int)(rem % kblocks);
+        const int64_t slot = rem / kblocks;
+        const int64_t j = sup * TC_SCOLS + jj;
+        const int64_t col = (int64_t)kb * npad + c;
+        const int64_t rec = (slot * kblocks + kb) * TC_SCALE_WORDS;
+        const float sc = tc_column_scale(scales[rec + c]);
+        float v = 0.0f;
+        if (j < n && col < k) {
+            const BatchIndex bi = decompose(batch, slot);
+            v = batch_ptr(rhs, bi)[j * rhs.s0 + col * rhs.s1] * sc;
+        }
+        const __half hi = __float2half_rn(v);
+        const __half lo = __float2half_rn(v - __half2float(hi));
+        __half *img = images + ((slot * kblocks + kb) * supers + sup) * (2 * TC_SCOLS * npad);
+        const int at = (jj >> 3) * (npad * 8) + c * 8 + (jj & 7);
+        img[at] = hi;
+        img[TC_SCOLS * npad + at] = lo;
+        if (sup == 0 && jj == 0) reinterpret_cast<float *>(scales)[rec + TC_MAX_N + c] = 1.0f / sc;
+    }
+}
+
+// D (fp32, tensor memory) (+)= A (tensor memory, fp16: row i in lane i, two K values per 32-bit
+// column) . B (smem, fp16); M = 128, N from idesc, K = 16.
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// two fp32 -> one register of two fp16: `even` in the low half (K index 2i), `odd` in the high half
+__device__ __forceinline__ uint32_t pack_f16_rz(float even, float odd) {
+    uint32_t r;
+    asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(odd), "f"(even));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_f16_rn(float even, float odd) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(odd), "f"(even));
+    return r;
+}
+
+template <int KT, int N>
+__global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_tc_kernel(const TcArgs a) {
+    using Cfg = TcCfg<N>;
+    constexpr int G = Cfg::G;
+    constexpr int NPT = N / G;  // accumulator columns per thread
+    constexpr int TC_A_STAGES = Cfg::A_STAGES;
+    constexpr int TC_ACC_COL = Cfg::ACC_COL;
+    constexpr int TC_TMEM_COLS = Cfg::TMEM_COLS;
+    constexpr int TC_IMG_BYTES = Cfg::IMG_BYTES;
+    constexpr int TC_SLOT_BYTES = Cfg::SLOT_BYTES;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[TC_B_STAGES];
-    __shared__ __align__(8) uint64_t bar_ready[TC_STAGES];
-    __shared__ __align__(8) uint64_t bar_empty[TC_STAGES];
-    __shared__ __align__(8) uint64_t bar_acc[2];
-    __shared__ __align__(8) uint64_t bar_free[2];
+    __shared__ __align__(8) uint64_t bar_full[TC_SLOTS];      // rhs image + x2 of a slot landed
+    __shared__ __align__(8) uint64_t bar_sfree[TC_SLOTS];     // MMAs reading a slot are done
+    __shared__ __align__(8) uint64_t bar_ready[TC_A_STAGES];  // A stage written by the generators
+    __shared__ __align__(8) uint64_t bar_empty[TC_A_STAGES];  // MMAs reading an A stage are done
+    __shared__ __align__(8) uint64_t bar_acc[2];              // accumulator group complete
+    __shared__ __align__(8) uint64_t bar_free[2];             // accumulators added to the registers
     __shared__ uint32_t tmem_base_slot;
     __shared__ int fail_flag;
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const bool is_mma_warp = warp == GEN_WARPS;
-    const int row_local = tid & 127;
-    const int g = (tid >> 7) % G;
+    const bool is_ctl_warp = warp == 4 * G;
+    const int g = tid >> 7;            // generator group
+    const int row_local = tid & 127;  // row of the block = tensor-memory lane
 
-    // shared memory: [A hi | A lo | rhs lo] x TC_STAGES, then TC_B_STAGES raw rhs tiles
-    float *smem_f = reinterpret_cast<float *>(smem_raw);
-    constexpr int STAGE_FLOATS = 2 * A_PART + B_TILE;
-    auto a_hi = [&](int s) { return smem_f + s * STAGE_FLOATS; };
-    auto a_lo = [&](int s) { return smem_f + s * STAGE_FLOATS + A_PART; };
-    auto b_lo = [&](int s) { return smem_f + s * STAGE_FLOATS + 2 * A_PART; };
-    auto b_raw = [&](int bs) { return smem_f + TC_STAGES * STAGE_FLOATS + bs * B_TILE; };
+    auto slot_img = [&](int sl) { return smem_raw + sl * TC_SLOT_BYTES; };
+    auto slot_x2 = [&](int sl) { return reinterpret_cast<float *>(smem_raw + sl * TC_SLOT_BYTES + TC_IMG_BYTES); };
 
-    // work item
     int64_t item = blockIdx.x;
     const int64_t b = item % a.batch.count;
     item /= a.batch.count;
     const int64_t r = a.rb_begin + item % a.row_blocks;
-    const int kb = (int)(item / a.row_blocks);
+    const int kb = (int)(item / a.row_blocks);  // block of N rhs columns
 
     const BatchIndex bi = decompose(a.batch, b);
     const float *x1 = batch_ptr(a.x1, bi);
@@ -136,147 +214,169 @@ __global__ void __launch_bounds__(128 * G + 32) matmul_tc_kernel(const TcArgs a)
     const int band_lo = clamp_int(batch_ptr(a.start, bi)[r * a.start.s0], 0, n);
     const int band_hi = max(band_lo, min(batch_ptr(a.end, bi)[r * a.end.s0], n));
     const int tile_lo = band_lo / TC_BK;
-    const int tile_hi = (band_hi + TC_BK - 1) / TC_BK;  // exclusive
-    const int tiles = band_hi > band_lo ? tile_hi - tile_lo : 0;
-    const float *images = a.images + (a.image_slot_stride ? b * a.image_slot_stride : 0) +
-                          (int64_t)kb * a.tiles * (int64_t)B_TILE;
+    const int tiles = band_hi > band_lo ? (band_hi + TC_BK - 1) / TC_BK - tile_lo : 0;
+    const int super_lo = tile_lo / TC_SUPER;
+    const int supers = tiles > 0 ? (tile_lo + tiles - 1) / TC_SUPER - super_lo + 1 : 0;
+    // a.images: fp16 images; a.image_slot_stride: bytes between image slots (0: rhs shared by all batches)
+    const int64_t img_rec = (a.image_slot_stride ? b : 0) * a.k_blocks + kb;  // (image slot, column block)
+    const unsigned char *images = reinterpret_cast<const unsigned char *>(a.images) + img_rec * (a.tiles * (int64_t)TC_IMG_BYTES);
+    const float *inv_scale = a.col_inv_scale + img_rec * TC_SCALE_WORDS;
+    const int64_t k_here = min((int64_t)N, a.k - (int64_t)kb * N);  // columns of this block
 
     if (tid == 0) {
 #pragma unroll
-        for (int s = 0; s < TC_B_STAGES; s++) mbar_init(&bar_full[s], 1);
+        for (int s = 0; s < TC_SLOTS; s++) {
+            mbar_init(&bar_full[s], 33);  // 32 lanes' cp.async arrivals + the bulk copy's expect_tx arrival
+            mbar_init(&bar_sfree[s], 1);
+        }
 #pragma unroll
-        for (int s = 0; s < TC_STAGES; s++) {
-            mbar_init(&bar_ready[s], GEN_WARPS);
+        for (int s = 0; s < TC_A_STAGES; s++) {
+            mbar_init(&bar_ready[s], 4 * G);
             mbar_init(&bar_empty[s], 1);
         }
 #pragma unroll
         for (int i = 0; i < 2; i++) {
             mbar_init(&bar_acc[i], 1);
-            mbar_init(&bar_free[i], GEN_WARPS);
+            mbar_init(&bar_free[i], 4 * G);
         }
         fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (is_mma_warp) tmem_alloc(&tmem_base_slot, (unsigned)a.tmem_cols);
+    if (is_ctl_warp) tmem_alloc(&tmem_base_slot, TC_TMEM_COLS);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
-    // instruction descriptor: D fp32, A / B tf32, both K-major, M = 128, N
-    constexpr uint32_t idesc = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
-    constexpr uint32_t img_bytes = B_TILE * sizeof(float);
+    // instruction descriptor: D fp32, A / B fp16 (format code 0), both K-major, M = 128, N
+    constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(N >> 3) << 17) | ((128u >> 4) << 24);
     bool failed = false;
 
     float acc[NPT];
 #pragma unroll
     for (int c = 0; c < NPT; c++) acc[c] = 0.0f;
 
-    if (is_mma_warp) {
-        // ------------------------------------------------------------ rhs fetch + MMA issue
-        if (lane == 0) {
-            auto fetch_rhs = [&](int t) {
-                const int bs = t % TC_B_STAGES;
-                mbar_expect_tx(&bar_full[bs], img_bytes);
-                bulk_copy_g2s(b_raw(bs), images + (int64_t)(tile_lo + t) * B_TILE, img_bytes, &bar_full[bs]);
-            };
-            for (int t = 0; t < min(tiles, TC_B_AHEAD); t++) fetch_rhs(t);
-            // Shared-memory descriptors: built once; per tile only the 14-bit start-address field
-            // moves (by whole stages), per K step by two core-matrix columns.  This thread is the
-            // only one issuing MMAs, so its instruction count per tile is on the critical path.
-            constexpr uint32_t lbo_a = 128 * 16, lbo_b = N * 16, sbo = 128;
-            constexpr uint64_t stage_step = (uint64_t)(STAGE_FLOATS * 4) >> 4;
-            constexpr uint64_t braw_step = (uint64_t)(B_TILE * 4) >> 4;
-            constexpr uint64_t ks_a = (uint64_t)(2 * lbo_a) >> 4, ks_b = (uint64_t)(2 * lbo_b) >> 4;
-            const uint64_t d_ah0 = smem_desc(smem_u32(a_hi(0)), lbo_a, sbo);
-            const uint64_t d_al0 = smem_desc(smem_u32(a_lo(0)), lbo_a, sbo);
-            const uint64_t d_bl0 = smem_desc(smem_u32(b_lo(0)), lbo_b, sbo);
-            const uint64_t d_br0 = smem_desc(smem_u32(b_raw(0)), lbo_b, sbo);
-            int s = 0, use = 0, bs = 0, in_grp = 0, grp = 0;  // ring counters of tile t
-            for (int t = 0; t < tiles; t++) {
-                const int ai = grp & 1;
-                const bool grp_first = in_grp == 0;
-                const bool grp_last = in_grp == TC_PROMO - 1 || t == tiles - 1;
-                // stage s (and the raw-rhs buffer of tile t - TC_STAGES) is free once its MMAs are done
-                if (use > 0 && !mbar_wait(&bar_empty[s], (unsigned)((use - 1) & 1))) failed = true;
-                if (!failed && t + TC_B_AHEAD < tiles) fetch_rhs(t + TC_B_AHEAD);
-                // the accumulator must have been collected by every generator warp
-                if (!failed && grp_first && grp >= 2 && !mbar_wait(&bar_free[ai], (unsigned)(((grp >> 1) - 1) & 1))) failed = true;
-                if (!failed && !mbar_wait(&bar_ready[s], (unsigned)(use & 1))) failed = true;
-                if (failed) break;
-                tc_fence_after();
-                const uint32_t d_tmem = tmem_base + (uint32_t)(ai * N);
-                const uint64_t dah = d_ah0 + s * stage_step, dal = d_al0 + s * stage_step;
-                const uint64_t dbl = d_bl0 + s * stage_step, dbh = d_br0 + bs * braw_step;
-                // cross terms first (tiny accumulator, truncation irrelevant), hi * hi last
+    if (is_ctl_warp) {
+        // ------------------------------------------- slot fetches (all lanes) + MMA issue (lane 0)
+        auto fetch = [&](int sr) {
+            const int sl = sr % TC_SLOTS;
+            const int64_t sup = super_lo + sr;
+            float *xs = slot_x2(sl);
 #pragma unroll
-                for (int ks = 0; ks < TC_BK / 8; ks++) {
-                    mma_tf32(d_tmem, dah + ks * ks_a, dbl + ks * ks_b, idesc, (ks > 0 || !grp_first) ? 1u : 0u);
-                    mma_tf32(d_tmem, dal + ks * ks_a, dbh + ks * ks_b, idesc, 1u);
-                }
-#pragma unroll
-                for (int ks = 0; ks < TC_BK / 8; ks++) mma_tf32(d_tmem, dah + ks * ks_a, dbh + ks * ks_b, idesc, 1u);
-                mma_commit(&bar_empty[s]);
-                if (grp_last) mma_commit(&bar_acc[ai]);
-                // advance the ring counters
-                if (++s == TC_STAGES) {
-                    s = 0;
-                    use++;
-                }
-                if (++bs == TC_B_STAGES) bs = 0;
-                if (++in_grp == TC_PROMO) {
-                    in_grp = 0;
-                    grp++;
-                }
+            for (int u = 0; u < TC_SCOLS / 32; u++) {
+                const int jj = lane + 32 * u;
+                const int64_t j = sup * TC_SCOLS + jj;
+                const bool valid = j < n;
+                cp_async4_zfill(xs + jj, x2 + (valid ? j : 0) * a.x2.s0, valid);
             }
-            if (failed) atomicExch(&fail_flag, 1);
+            cp_async_mbar_arrive(&bar_full[sl]);
+            if (lane == 0) {
+                mbar_expect_tx(&bar_full[sl], TC_IMG_BYTES);
+                bulk_copy_g2s(slot_img(sl), images + sup * TC_IMG_BYTES, TC_IMG_BYTES, &bar_full[sl]);
+            }
+        };
+        for (int sr = 0; sr < min(supers, TC_SLOTS); sr++) fetch(sr);
+
+        // B: core matrices of 8 columns (N) x 16 bytes (8 fp16 along K); K-adjacent matrices N * 16 bytes apart
+        constexpr uint32_t lbo_b = N * 16, sbo = 128;
+        constexpr uint64_t slot_step = (uint64_t)TC_SLOT_BYTES >> 4;
+        constexpr uint64_t part_step = (uint64_t)(TC_SCOLS * N * 2) >> 4;  // hi -> lo image
+        constexpr uint64_t kstep = (uint64_t)(2 * lbo_b) >> 4;             // 16 band columns = 2 chunks
+        const uint64_t d_b0 = smem_desc(smem_u32(slot_img(0)), lbo_b, sbo);
+        int s = 0, use = 0, in_grp = 0, grp = 0;
+        for (int t = 0; t < tiles; t++) {
+            const int ta = tile_lo + t;
+            const int q = ta & (TC_SUPER - 1);
+            const int sr = ta / TC_SUPER - super_lo;
+            const int sl = sr % TC_SLOTS;
+            const int ai = grp & 1;
+            const bool grp_first = in_grp == 0;
+            const bool grp_last = in_grp == TC_PROMO - 1 || t == tiles - 1;
+            const bool slot_first = t == 0 || q == 0;
+            const bool slot_last = q == TC_SUPER - 1 || t == tiles - 1;
+            bool ok = true;
+            if (slot_first) ok = mbar_wait(&bar_full[sl], (unsigned)((sr / TC_SLOTS) & 1));
+            // the accumulator must have been collected by every generator warp
+            if (ok && grp_first && grp >= 2) ok = mbar_wait(&bar_free[ai], (unsigned)(((grp >> 1) - 1) & 1));
+            if (ok) ok = mbar_wait(&bar_ready[s], (unsigned)(use & 1));
+            if (!__all_sync(0xffffffffu, ok)) {
+                failed = true;
+                break;
+            }
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t d_tmem = tmem_base + (uint32_t)(TC_ACC_COL + ai * N);
+                const uint32_t a_hi = tmem_base + (uint32_t)(s * TC_A_COLS), a_lo = a_hi + 8;
+                const uint64_t b_hi = d_b0 + sl * slot_step + (uint64_t)(q * (TC_BK / 16)) * kstep, b_lo = b_hi + part_step;
+                // the small cross terms first, hi * hi last
+#pragma unroll
+                for (int ks = 0; ks < TC_BK / 16; ks++) {
+                    mma_f16_ts(d_tmem, a_hi + ks * 16, b_lo + ks * kstep, idesc, (ks > 0 || !grp_first) ? 1u : 0u);
+                    mma_f16_ts(d_tmem, a_lo + ks * 16, b_hi + ks * kstep, idesc, 1u);
+                }
+#pragma unroll
+                for (int ks = 0; ks < TC_BK / 16; ks++) mma_f16_ts(d_tmem, a_hi + ks * 16, b_hi + ks * kstep, idesc, 1u);
+                mma_commit(&bar_empty[s]);
+                if (slot_last) mma_commit(&bar_sfree[sl]);
+                if (grp_last) mma_commit(&bar_acc[ai]);
+            }
+            __syncwarp();
+            // after the first tile of a slot: the previous slot is re-filled once its MMAs are done
+            if (slot_first && sr >= 1 && sr - 1 + TC_SLOTS < supers) {
+                const int prev = sr - 1;
+                ok = mbar_wait(&bar_sfree[prev % TC_SLOTS], (unsigned)((prev / TC_SLOTS) & 1));
+                if (!__all_sync(0xffffffffu, ok)) {
+                    failed = true;
+                    break;
+                }
+                fetch(prev + TC_SLOTS);
+            }
+            if (++s == TC_A_STAGES) {
+                s = 0;
+                use++;
+            }
+            if (++in_grp == TC_PROMO) {
+                in_grp = 0;
+                grp++;
+            }
         }
+        if (failed && lane == 0) atomicExch(&fail_flag, 1);
+        // no cp.async may be in flight when the CTA exits
+        cp_async_wait<0>();
         __syncwarp();
     } else {
-        // ------------------------------------------------------------------- generators
+        // ----------------------------------------------------------------------- generators
         const int64_t row = r * KM_BLOCK_SIZE + row_local;
         const float x1v = row < a.m ? x1[row * a.x1.s0] : 0.0f;
-        const uint32_t tmem_mine = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(g * NPT);
+        const uint32_t tmem_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
 
         auto collect = [&](int ai) {
             tc_fence_after();
-            uint32_t v[NPT / 16][16];
 #pragma unroll
-            for (int q = 0; q < NPT / 16; q++) tmem_ld16_nowait(tmem_mine + (uint32_t)(ai * N + q * 16), v[q]);
-            tmem_ld_wait();
+            for (int q = 0; q < NPT / 16; q++) {
+                uint32_t v[16];
+                tmem_ld16_nowait(tmem_lane + (uint32_t)(TC_ACC_COL + ai * N + g * NPT + q * 16), v);
+                tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < NPT / 16; q++)
-#pragma unroll
-                for (int u = 0; u < 16; u++) acc[q * 16 + u] += __uint_as_float(v[q][u]);
+                for (int u = 0; u < 16; u++) acc[q * 16 + u] += __uint_as_float(v[u]);
+            }
             tc_fence_before();
         };
-        // x2 values of this thread's columns, fetched one tile ahead
-        auto load_x2 = [&](int jt, float (&xv)[CPT][4]) {
-#pragma unroll
-            for (int q = 0; q < CPT; q++)
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int j = jt * TC_BK + (g * CPT + q) * 4 + u;
-                    xv[q][u] = j < n ? __ldg(x2 + (int64_t)j * a.x2.s0) : 0.0f;
-                }
-        };
-        float xnext[CPT][4];
-        if (tiles > 0) load_x2(tile_lo, xnext);
 
         for (int t = 0; t < tiles; t++) {
-            const int s = t % TC_STAGES, use = t / TC_STAGES, bs = t % TC_B_STAGES;
-            const int jt = tile_lo + t;
+            const int ta = tile_lo + t;
+            const int q = ta & (TC_SUPER - 1);
+            const int sr = ta / TC_SUPER - super_lo;
+            const int sl = sr % TC_SLOTS;
+            const int s = t % TC_A_STAGES, use = t / TC_A_STAGES;
             const int grp = t / TC_PROMO, ai = grp & 1;
-            float xv[CPT][4];
-#pragma unroll
-            for (int q = 0; q < CPT; q++)
-#pragma unroll
-                for (int u = 0; u < 4; u++) xv[q][u] = xnext[q][u];
-            if (t + 1 < tiles) load_x2(jt + 1, xnext);
-
+            if ((t == 0 || q == 0) && !mbar_wait_warp(&bar_full[sl], (unsigned)((sr / TC_SLOTS) & 1))) {
+                failed = true;
+                break;
+            }
             // an accumulator that is about to be reused is first added to the registers
             if ((t % TC_PROMO) == 0 && grp >= 2) {
-                if (!mbar_wait(&bar_acc[ai], (unsigned)((grp / 2 - 1) & 1))) {
+                if (!mbar_wait_warp(&bar_acc[ai], (unsigned)((grp / 2 - 1) & 1))) {
                     failed = true;
                     break;
                 }
@@ -284,50 +384,50 @@ __global__ void __launch_bounds__(128 * G + 32) matmul_tc_kernel(const TcArgs a)
                 __syncwarp();
                 if (lane == 0) mbar_arrive(&bar_free[ai]);
             }
-            // stage s must have been read by the MMAs of tile t - TC_STAGES
-            if (use > 0 && !mbar_wait(&bar_empty[s], (unsigned)((use - 1) & 1))) {
-                failed = true;
-                break;
+            // stage s must have been read by the MMAs of tile t - TC_A_STAGES
+            if (use > 0) {
+                if (!mbar_wait_warp(&bar_empty[s], (unsigned)((use - 1) & 1))) {
+                    failed = true;
+                    break;
+                }
+                tc_fence_after();
             }
-            // kernel entries: this thread's row, its share of the 32 columns, 4 at a time
-            const int j0 = jt * TC_BK;
-            const bool partial = (j0 < band_lo) || (j0 + TC_BK > band_hi);
-            float *ah = a_hi(s), *al = a_lo(s);
+            const float4 *xs = reinterpret_cast<const float4 *>(slot_x2(sl) + q * TC_BK);
+            const int j0 = ta * TC_BK;
+            const bool partial = j0 < band_lo || j0 + TC_BK > band_hi;
+            // 16 entries at a time: hi = kv truncated to fp16 (= the fp32 value with 10 mantissa
+            // bits for kv in fp16's normal range; below 2^-14 the two differ by less than 2^-24,
+            // far under the tolerance), lo = kv - hi rounded to fp16.  Tensor-memory columns of
+            // the 16 band columns: [8 hi pairs | 8 lo pairs].
 #pragma unroll
-            for (int q = 0; q < CPT; q++) {
-                const int chunk = g * CPT + q;
-                float kv[4], lo[4];
+            for (int half = g; half < TC_BK / 16; half += G) {  // this group's 16-column steps
+                float kv[16];
 #pragma unroll
-                for (int u = 0; u < 4; u++) kv[u] = fn.unscaled(x1v - xv[q][u]);
+                for (int h = 0; h < 4; h++) {
+                    const float4 xv = xs[half * 4 + h];
+                    kv[4 * h + 0] = fn.unscaled(x1v - xv.x);
+                    kv[4 * h + 1] = fn.unscaled(x1v - xv.y);
+                    kv[4 * h + 2] = fn.unscaled(x1v - xv.z);
+                    kv[4 * h + 3] = fn.unscaled(x1v - xv.w);
+                }
                 if (partial) {
 #pragma unroll
-                    for (int u = 0; u < 4; u++) {
-                        const int j = j0 + chunk * 4 + u;
+                    for (int u = 0; u < 16; u++) {
+                        const int j = j0 + half * 16 + u;
                         if (j < band_lo || j >= band_hi) kv[u] = 0.0f;
                     }
                 }
+                uint32_t parts[16];
 #pragma unroll
-                for (int u = 0; u < 4; u++) lo[u] = kv[u] - tf32_hi(kv[u]);
-                // [chunk][row][16 bytes]: the tensor core reads only the TF32 bits of kv as "hi"
-                *reinterpret_cast<float4 *>(ah + (chunk * 128 + row_local) * 4) = make_float4(kv[0], kv[1], kv[2], kv[3]);
-                *reinterpret_cast<float4 *>(al + (chunk * 128 + row_local) * 4) = make_float4(lo[0], lo[1], lo[2], lo[3]);
-            }
-            // lo part of the rhs tile (the raw tile itself serves as hi)
-            if (!mbar_wait(&bar_full[bs], (unsigned)((t / TC_B_STAGES) & 1))) {
-                failed = true;
-                break;
-            }
-            {
-                const float4 *raw = reinterpret_cast<const float4 *>(b_raw(bs));
-                float4 *lo4 = reinterpret_cast<float4 *>(b_lo(s));
-#pragma unroll
-                for (int q = 0; q < B_TILE / 4 / GEN_THREADS; q++) {
-                    const float4 v = raw[q * GEN_THREADS + tid];
-                    lo4[q * GEN_THREADS + tid] =
-                        make_float4(v.x - tf32_hi(v.x), v.y - tf32_hi(v.y), v.z - tf32_hi(v.z), v.w - tf32_hi(v.w));
+                for (int u = 0; u < 8; u++) {
+                    const float e = kv[2 * u], o = kv[2 * u + 1];
+                    parts[u] = pack_f16_rz(e, o);
+                    parts[8 + u] = pack_f16_rn(e - tf32_hi(e), o - tf32_hi(o));
                 }
+                tmem_st16(tmem_lane + (uint32_t)(s * TC_A_COLS + half * 16), parts);
             }
-            fence_async_smem();
+            tmem_st_wait();
+            tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_ready[s]);
         }
@@ -335,7 +435,7 @@ __global__ void __launch_bounds__(128 * G + 32) matmul_tc_kernel(const TcArgs a)
         // drain: the last two groups still sit in tensor memory
         const int groups = (tiles + TC_PROMO - 1) / TC_PROMO;
         for (int grp = max(0, groups - 2); grp < groups && !failed; grp++) {
-            if (!mbar_wait(&bar_acc[grp & 1], (unsigned)((grp / 2) & 1))) {
+            if (!mbar_wait_warp(&bar_acc[grp & 1], (unsigned)((grp / 2) & 1))) {
                 failed = true;
                 break;
             }
@@ -348,66 +448,103 @@ __global__ void __launch_bounds__(128 * G + 32) matmul_tc_kernel(const TcArgs a)
     __syncthreads();
     if (fail_flag) {
         if (tid == 0) atomicExch(a.status, 1);
-    } else if (!is_mma_warp) {
-        // Output.  Each thread holds NPT consecutive columns of one row; a warp transposes its
-        // 32 x NPT block through shared memory (the stages are idle now) so that every store
-        // instruction writes whole 128-byte row segments.
-        const float scale = fn.scale;
-        const int64_t row0 = r * KM_BLOCK_SIZE + (warp & 3) * 32;  // first row of this warp
-        const int64_t out_row0 = row0 - a.rb_begin * KM_BLOCK_SIZE;
-        const int64_t col0 = (int64_t)kb * N + g * NPT;
-        constexpr int PITCH = NPT + 4;  // floats; keeps float4 alignment, staggers banks
-        float *tile = smem_f + warp * (32 * PITCH);
+    } else if (!is_ctl_warp) {
+        const int64_t row = r * KM_BLOCK_SIZE + row_local;
+        if (row < a.m) {
+            // output scale times the inverse of the rhs column scale
+            float *orow = out + (row - a.rb_begin * KM_BLOCK_SIZE) * a.out.s0 + (int64_t)kb * N * a.out.s1;
+            const bool vec_ok = a.out.s1 == 1 && (a.out.s0 % 4 == 0) && (k_here % 4 == 0) &&
+                                ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+            const float scale = fn.scale;
 #pragma unroll
-        for (int c = 0; c < NPT; c += 4)
-            *reinterpret_cast<float4 *>(tile + lane * PITCH + c) =
-                make_float4(acc[c] * scale, acc[c + 1] * scale, acc[c + 2] * scale, acc[c + 3] * scale);
-        __syncwarp();
-        const bool vec_ok = a.out.s1 == 1 && (a.out.s0 % 4 == 0) && (col0 + NPT <= a.k) &&
-                            ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
-        constexpr int V = NPT / 4;          // float4 per row
-        constexpr int ROWS_PER_IT = 32 / V;  // rows written per store instruction
-        if (vec_ok) {
+            for (int cl = 0; cl < NPT; cl += 4) {
+                const int c = g * NPT + cl;  // column inside this block of N
+                if (c < k_here) {
+                    const float4 is = *reinterpret_cast<const float4 *>(inv_scale + c);
+                    const float4 v = make_float4(acc[cl] * (is.x * scale), acc[cl + 1] * (is.y * scale),
+                                                 acc[cl + 2] * (is.z * scale), acc[cl + 3] * (is.w * scale));
+                    if (vec_ok) {
+                        *reinterpret_cast<float4 *>(orow + c) = v;
+                    } else {
+                        const float e[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
-            for (int it = 0; it < 32 / ROWS_PER_IT; it++) {
-                const int rr = it * ROWS_PER_IT + lane / V, cc = (lane % V) * 4;
-                if (row0 + rr < a.m)
-                    *reinterpret_cast<float4 *>(out + (out_row0 + rr) * a.out.s0 + col0 + cc) =
-                        *reinterpret_cast<const float4 *>(tile + rr * PITCH + cc);
-            }
-        } else {
-            for (int rr = 0; rr < 32; rr++) {
-                if (row0 + rr >= a.m) break;
-                for (int cc = lane; cc < NPT; cc += 32)
-                    if (col0 + cc < a.k) out[(out_row0 + rr) * a.out.s0 + (col0 + cc) * a.out.s1] = tile[rr * PITCH + cc];
+                        for (int u = 0; u < 4; u++)
+                            if (c + u < k_here) orow[(c + u) * a.out.s1] = e[u];
+                    }
+                }
             }
         }
     }
-    if (is_mma_warp) tmem_free(tmem_base, (unsigned)a.tmem_cols);
+    if (is_ctl_warp) tmem_free(tmem_base, TC_TMEM_COLS);
 }
 
-static int tc_n_pad(int64_t k) { return k <= 64 ? 64 : 128; }
+// workspace: [status, 256 B][per (image slot, column block): column maxima and inverse scales][images]
+static int tc_n_pad(int64_t k) { return k <= 16 ? 16 : (k <= 32 ? 32 : (k <= 64 ? 64 : 128)); }
+static int64_t tc_k_blocks(int64_t k) { return std::max<int64_t>(1, ceil_div(k, TC_MAX_N)); }
+static size_t tc_scale_bytes(int64_t slots, int64_t kblocks) {
+    return (size_t)(slots * kblocks) * TC_SCALE_WORDS * sizeof(float);
+}
 
-template <int KT, int N, int G>
+static size_t tc_workspace_bytes(const Batch &b, int64_t n, int64_t k, const View<const float> &rhs) {
+    const int64_t supers = ceil_div(n, TC_SCOLS);
+    const int64_t slots = tc_slots(b, rhs), kblocks = tc_k_blocks(k);
+    return (size_t)TC_STATUS_BYTES + tc_scale_bytes(slots, kblocks) +
+           (size_t)(slots * kblocks * supers) * (2 * TC_SCOLS * tc_n_pad(k)) * 2;
+}
+
+template <int KT, int N>
 static int launch_tc_n(const TcArgs &a, cudaStream_t s) {
     const int64_t items = a.batch.count * a.row_blocks * a.k_blocks;
     if (items > 0x7fffffffLL) {
         set_error("km_matmul_tc_f32: too many work items (%lld)", (long long)items);
         return KM_ERR_UNSUPPORTED;
     }
-    constexpr size_t smem = ((size_t)TC_STAGES * (2 * 128 * TC_BK + TC_BK * N) + (size_t)TC_B_STAGES * TC_BK * N) * sizeof(float);
-    auto kernel = matmul_tc_kernel<KT, N, G>;
+    auto kernel = matmul_tc_kernel<KT, N>;
+    constexpr size_t smem = TcCfg<N>::SMEM_BYTES;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(matmul_tc)");
-    kernel<<<(unsigned)items, 128 * G + 32, smem, s>>>(a);
+    kernel<<<(unsigned)items, TcCfg<N>::THREADS, smem, s>>>(a);
     KM_CHECK_LAUNCH("km_matmul_tc_f32 launch");
     return KM_OK;
 }
 
 template <int KT>
-static int launch_tc(const TcArgs &a, cudaStream_t s) {
-    if (a.n_pad == 64) return launch_tc_n<KT, 64, 2>(a, s);
-    return launch_tc_n<KT, 128, 4>(a, s);
+static int launch_tc(const TcArgs &a, int n_pad, cudaStream_t s) {
+    if (n_pad == 16) return launch_tc_n<KT, 16>(a, s);
+    if (n_pad == 32) return launch_tc_n<KT, 32>(a, s);
+    if (n_pad == 64) return launch_tc_n<KT, 64>(a, s);
+    return launch_tc_n<KT, 128>(a, s);
+}
+
+static int tc_matmul(int kernel_type, TcArgs a, const View<const float> &rhs, void *workspace, cudaStream_t s) {
+    const int64_t slots = tc_slots(a.batch, rhs);
+    const int64_t supers = ceil_div(a.n, TC_SCOLS);
+    const int n_pad = tc_n_pad(a.k);
+    const int64_t kblocks = tc_k_blocks(a.k);
+    unsigned char *ws = static_cast<unsigned char *>(workspace);
+    a.status = reinterpret_cast<int *>(ws);
+    unsigned *scales = reinterpret_cast<unsigned *>(ws + TC_STATUS_BYTES);
+    __half *images = reinterpret_cast<__half *>(ws + TC_STATUS_BYTES + tc_scale_bytes(slots, kblocks));
+    a.images = reinterpret_cast<const float *>(images);
+    a.image_slot_stride = slots > 1 ? 1 : 0;  // this kernel only asks whether every batch has its own images
+    a.k_blocks = (int)kblocks;
+    a.tiles = supers;                         // 64-column groups per image
+    a.n_pad = n_pad;
+    a.col_inv_scale = reinterpret_cast<const float *>(scales) + TC_MAX_N;
+    cudaError_t err = cudaMemsetAsync(scales, 0, tc_scale_bytes(slots, kblocks), s);
+    if (err != cudaSuccess) return cuda_fail(err, "km_matmul_tc_f32 cudaMemsetAsync");
+    const unsigned max_blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(a.n, 16), 148 * 8));
+    tc_colmax_kernel<<<max_blocks, 256, 0, s>>>(a.batch, slots, a.n, a.k, n_pad, (int)kblocks, rhs, scales, a.status);
+    KM_CHECK_LAUNCH("km_matmul_tc_f32 column-maximum launch");
+    const int64_t total = slots * kblocks * supers * (int64_t)(TC_SCOLS * n_pad);
+    const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(total, 256), 148 * 32));
+    tc_rhs_images_kernel<<<blocks, 256, 0, s>>>(a.batch, slots, a.n, a.k, n_pad, (int)kblocks, supers, rhs, images, scales);
+    KM_CHECK_LAUNCH("km_matmul_tc_f32 pre-pass launch");
+    switch (kernel_type) {
+    case KM_KERNEL_RBF: return launch_tc<KM_KERNEL_RBF>(a, n_pad, s);
+    case KM_KERNEL_SPECTRAL: return launch_tc<KM_KERNEL_SPECTRAL>(a, n_pad, s);
+    default: return launch_tc<KM_KERNEL_LOCALLY_PERIODIC>(a, n_pad, s);
+    }
 }
 
 }  // namespace km
@@ -416,12 +553,7 @@ extern "C" size_t km_matmul_tc_workspace_bytes(const km_batch *batch, int64_t n,
     using namespace km;
     Batch b;
     if (batch == nullptr || rhs == nullptr || make_batch(batch, &b) != KM_OK || n < 0 || k <= 0) return 0;
-    const View<const float> rv = make_view<const float>(rhs, b);
-    if (k <= TCN_MAX_K) return tcn_workspace_bytes(b, n, rv);
-    const int n_pad = tc_n_pad(k);
-    const int64_t k_blocks = ceil_div(k, n_pad);
-    const int64_t tiles = ceil_div(n, TC_BK);
-    return (size_t)TC_STATUS_BYTES + (size_t)(tc_slots(b, rv) * k_blocks * tiles) * (TC_BK * n_pad) * sizeof(float);
+    return tc_workspace_bytes(b, n, k, make_view<const float>(rhs, b));
 }
 
 extern "C" int km_matmul_tc_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
@@ -450,36 +582,13 @@ extern "C" int km_matmul_tc_f32(int kernel_type, const km_batch *batch, int64_t 
     a.k = k;
     a.row_blocks = ceil_div(m, KM_BLOCK_SIZE);
     a.rb_begin = 0;
-    a.col_inv_scale = nullptr;
-    a.n_pad = tc_n_pad(k);
-    a.k_blocks = (int)ceil_div(k, a.n_pad);
-    a.tmem_cols = 32;  // two accumulators of n_pad columns, rounded up to a power of two
-    while (a.tmem_cols < TC_STAGES * a.n_pad) a.tmem_cols *= 2;
-    a.tiles = ceil_div(n, TC_BK);
     a.x1 = make_view<const float>(x1, a.batch);
     a.x2 = make_view<const float>(x2, a.batch);
     a.params = make_view<const float>(params, a.batch);
     a.start = make_view<const int>(start, a.batch);
     a.end = make_view<const int>(end, a.batch);
     a.out = make_view<float>(out, a.batch);
-    const View<const float> rv = make_view<const float>(rhs, a.batch);
-    if (k <= TCN_MAX_K) return tcn_matmul(kernel_type, a, rv, workspace, static_cast<cudaStream_t>(stream));
-    const int64_t slots = tc_slots(a.batch, rv);
-    a.status = static_cast<int *>(workspace);
-    float *images = reinterpret_cast<float *>(static_cast<unsigned char *>(workspace) + TC_STATUS_BYTES);
-    a.images = images;
-    a.image_slot_stride = slots > 1 ? (int64_t)a.k_blocks * a.tiles * ((int64_t)TC_BK * a.n_pad) : 0;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-
-    const int64_t total = slots * a.k_blocks * a.tiles * (int64_t)TC_BK * a.n_pad;
-    const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(total, 256), 148 * 32));
-    tc_rhs_images_kernel<<<blocks, 256, 0, s>>>(a.batch, slots, n, k, a.tiles, a.k_blocks, a.n_pad, rv, images, a.status);
-    KM_CHECK_LAUNCH("km_matmul_tc_f32 pre-pass launch");
-    switch (kernel_type) {
-    case KM_KERNEL_RBF: return launch_tc<KM_KERNEL_RBF>(a, s);
-    case KM_KERNEL_SPECTRAL: return launch_tc<KM_KERNEL_SPECTRAL>(a, s);
-    default: return launch_tc<KM_KERNEL_LOCALLY_PERIODIC>(a, s);
-    }
+    return tc_matmul(kernel_type, a, make_view<const float>(rhs, a.batch), workspace, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int km_workspace_status(const void *workspace, int32_t *status_out, void *stream) {

@@ -1,5 +1,5 @@
 // tcgen05 / tensor-memory / mbarrier / bulk-copy PTX wrappers shared by the tensor-core kernels
-// (km_matmul_tc.cu, km_matmul_tcn.cu, km_grad_tc.cu).  sm_100a only.
+// (km_matmul_tc.cu, km_grad_tc.cu).  sm_100a only.
 #pragma once
 
 #include "km_common.cuh"
@@ -8,21 +8,20 @@ namespace km {
 
 constexpr int TC_STATUS_BYTES = 256;  // status word + padding in front of the workspace payload
 
-// Arguments of the tensor-core products (filled by km_matmul_tc_f32).
+// Arguments of the tensor-core product (filled by km_matmul_tc_f32).
 struct TcArgs {
     Batch batch;
     int64_t m, n, k;
     int64_t row_blocks, rb_begin;
-    int k_blocks;  // blocks of n_pad rhs columns
-    int n_pad;     // GEMM N per block: multiple of 16, <= 256
-    int tmem_cols; // power of two >= max(32, n_pad)
-    int64_t tiles; // ceil(n / TC_BK)
+    int k_blocks;   // blocks of n_pad rhs columns
+    int n_pad;      // GEMM N per block: 16, 32, 64 or 128
+    int64_t tiles;  // 64-column groups per image: ceil(n / 64)
     View<const float> x1, x2, params;
     View<const int> start, end;
     View<float> out;
-    const float *images;         // [slot][k block][tile][chunk][c][4]
-    int64_t image_slot_stride;   // floats (narrow kernel: bytes) between batch slots (0: rhs shared by all batches)
-    const float *col_inv_scale;  // narrow kernel: per image slot, inverse of the per-column rhs scales
+    const float *images;         // fp16 images [image slot][column block][64-column group][hi, lo][chunk][c][8]
+    int64_t image_slot_stride;   // non-zero: every batch has its own images (0: rhs shared by all batches)
+    const float *col_inv_scale;  // per (image slot, column block): inverse of the per-column rhs scales
     int *status;
 };
 
@@ -32,12 +31,6 @@ inline int64_t tc_slots(const Batch &b, const View<const float> &rhs) {
     for (int d = 0; d < b.ndim; d++) shared = shared && (rhs.bs[d] == 0 || b.size[d] == 1);
     return shared ? 1 : b.count;
 }
-
-// Narrow right-hand sides (k <= TCN_MAX_K): kernel-matrix tiles handed to the tensor core
-// through tensor memory (km_matmul_tcn.cu).  `a` carries everything but the images.
-constexpr int TCN_MAX_K = 16;
-size_t tcn_workspace_bytes(const Batch &b, int64_t n, const View<const float> &rhs);
-int tcn_matmul(int kernel_type, TcArgs a, const View<const float> &rhs, void *workspace, cudaStream_t stream);
 
 constexpr unsigned TC_WAIT_POLLS = 1u << 18;  // each poll may block for a short, system-defined time
 
@@ -52,7 +45,12 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, unsigned bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// Bounded wait for the phase with the given parity.  false = gave up.
+// Bounded wait for the phase with the given parity.  false = gave up.  Each try_wait may suspend
+// the thread for up to TC_WAIT_HINT_NS (it resumes as soon as the phase completes), which keeps
+// waiting warps from spending issue slots on polling.
+#ifndef TC_WAIT_HINT_NS
+#define TC_WAIT_HINT_NS 1000
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
     const uint32_t addr = smem_u32(bar);
     for (unsigned poll = 0; poll < TC_WAIT_POLLS; poll++) {
@@ -60,11 +58,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
         asm volatile(
             "{\n\t"
             ".reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t"
             "}"
             : "=r"(done)
-            : "r"(addr), "r"(parity)
+            : "r"(addr), "r"(parity), "r"((unsigned)TC_WAIT_HINT_NS)
             : "memory");
         if (done) return true;
     }
@@ -138,21 +136,6 @@ __device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[1
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float tf32_hi(float x) { return __uint_as_float(__float_as_uint(x) & 0xffffe000u); }
-
-// D (fp32, tensor memory) (+)= A (tensor memory, tf32: row i in lane i, one K value per 32-bit
-// column) . B (smem, tf32); M = 128, N from idesc, K = 8.
-__device__ __forceinline__ void mma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                            uint32_t accumulate) {
-    asm volatile(
-        "{\n\t"
-        ".reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
-        "}"
-        :
-        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
-        : "memory");
-}
 
 // registers -> 16 consecutive tensor-memory columns of this thread's lane
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {

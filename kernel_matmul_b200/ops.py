@@ -135,22 +135,20 @@ def _out_batch(batch: tuple[int, ...]) -> tuple[int, ...]:
     return batch
 
 
-#: rhs widths from which ``matmul`` runs the contraction on the tensor cores (tcgen05) instead
-#: of the FMA pipe: the wide kernel (3xTF32, kernel tiles through shared memory) ...
-TENSOR_CORE_MIN_K = 64
-#: ... and the narrow kernel (fp16 hi/lo split, kernel tiles through tensor memory), whose cost
-#: does not depend on the width; below 9 columns the FMA pipe is as fast.
-TENSOR_CORE_NARROW_K = range(9, 17)
+#: rhs widths from which ``matmul`` runs the contraction on the tensor cores (tcgen05; fp16
+#: hi/lo operand split, kernel tiles handed over in tensor memory).  The cost of that kernel
+#: hardly depends on the width; below 9 columns the FMA pipe is as fast.
+TENSOR_CORE_MIN_K = 9
 #: The tensor-core kernels run a pre-pass over the rhs (two or three small launches); they are
 #: chosen on ``path="auto"`` only for problems with at least this many (batch, row block) items.
 TENSOR_CORE_MIN_ITEMS = 256
 
 
-def _auto_tensor_cores(k: int, widths, batch: tuple[int, ...], m: int) -> bool:
+def _enough_items(batch: tuple[int, ...], m: int) -> bool:
     items = -(-m // BLOCK_SIZE)
     for b in batch:
         items *= b
-    return k in widths and items >= TENSOR_CORE_MIN_ITEMS
+    return items >= TENSOR_CORE_MIN_ITEMS
 
 
 def matmul(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor, start: Tensor, end: Tensor,
@@ -159,8 +157,8 @@ def matmul(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor
 
     Reference: ``matmul.call(x1, x2, rhs, params, start, end)`` (native/matmul/matmul.cpp:6-17).
     ``path``: ``"fma"`` (FP32 pipe), ``"tc"`` (tensor cores; fp32-level accuracy through operand
-    splitting) or ``"auto"`` (tensor cores for ``TENSOR_CORE_NARROW_K`` and from
-    ``TENSOR_CORE_MIN_K`` rhs columns, if the problem has ``TENSOR_CORE_MIN_ITEMS`` work items).
+    splitting) or ``"auto"`` (tensor cores from ``TENSOR_CORE_MIN_K`` rhs columns, if the problem
+    has ``TENSOR_CORE_MIN_ITEMS`` work items).
     """
     kid, dev, batch, m, n, (x1e, x2e, pe, se, ee, re) = _prep(kernel_type, x1, x2, params, start, end, [(rhs, 2)])
     if rhs.shape[-2] != n:
@@ -170,7 +168,7 @@ def matmul(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor
         raise ValueError(f"unknown path {path!r}")
     out = torch.empty(*batch, m, k, device=dev, dtype=torch.float32)
     oute = out.reshape(-1, m, k) if len(batch) > KM_MAX_BATCH_DIMS else out
-    if path == "tc" or (path == "auto" and (k >= TENSOR_CORE_MIN_K or _auto_tensor_cores(k, TENSOR_CORE_NARROW_K, batch, m))):
+    if path == "tc" or (path == "auto" and k >= TENSOR_CORE_MIN_K and _enough_items(batch, m)):
         kb = _km_batch(batch)
         rv = _view(re, 2)
         ws_bytes = lib.km_matmul_tc_workspace_bytes(kb, n, k, rv)
@@ -249,7 +247,7 @@ def _grad_call(which: str, kernel_type, x1, x2, left, right, params, start, end,
     k = left.shape[-1]
     if path not in ("auto", "fma", "tc"):
         raise ValueError(f"unknown path {path!r}")
-    tc = path == "tc" or (path == "auto" and _auto_tensor_cores(k, GRAD_TENSOR_CORE_K, batch, m))
+    tc = path == "tc" or (path == "auto" and k in GRAD_TENSOR_CORE_K and _enough_items(batch, m))
     P = NUM_PARAMS[kernel_type]
     grad = torch.empty(*batch, P, device=dev, dtype=torch.float32)
     grade = grad.reshape(-1, P) if len(batch) > KM_MAX_BATCH_DIMS else grad

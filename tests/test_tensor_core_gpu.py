@@ -67,21 +67,18 @@ def test_tc_product_unbanded_and_empty_bands():
     assert rel_err(out, O.matmul("rbf", x1, x2, rhs, params, start, end)) <= 1e-5
 
 
-def test_auto_path_uses_tensor_cores_from_64_columns():
-    from kernel_matmul_b200 import ops
-
-    assert ops.TENSOR_CORE_MIN_K == 64
+def test_tc_product_reports_its_workspace():
     out = _run("rbf", 300, 300, 64, square=True)
     assert hasattr(out, "_km_workspace")
 
 
-# ------------------------------------------------------------------ narrow right-hand sides
-# k <= 16 takes the kernel that hands the kernel-matrix tiles over in tensor memory.
+# ------------------------------------------------------------------ GEMM widths 16 / 32 / 64 / 128
 
 
 @pytest.mark.parametrize("kt", KERNEL_TYPES)
-@pytest.mark.parametrize("k", [1, 5, 12, 16])
+@pytest.mark.parametrize("k", [1, 5, 12, 16, 17, 30, 32, 33, 50, 64])
 def test_tc_narrow_product_matches_oracle(kt, k):
+    # GEMM widths 16 (k <= 16), 32 and 64
     _run(kt, 600, 800, k)
 
 
@@ -89,11 +86,14 @@ def test_tc_narrow_long_bands_many_accumulator_groups():
     # unbanded with n = 3000: 188 tiles of 16 columns = 24 accumulator groups, 47 slot refills
     _run("spectral", 257, 3000, 16, cutoff=None)
     _run("rbf", 128, 2049, 7, cutoff=None)
+    _run("locally_periodic", 257, 3000, 32, cutoff=None)
+    _run("spectral", 130, 2049, 64, cutoff=None)
 
 
 def test_tc_narrow_batched_shared_and_private_rhs():
     _run("spectral", 500, 500, 16, batch=(2, 3), shared_rhs=True, square=True)
     _run("locally_periodic", 301, 199, 9, batch=(4,), shared_rhs=False)
+    _run("rbf", 301, 199, 40, batch=(3,), shared_rhs=False)
 
 
 def test_tc_narrow_strided_operands_and_empty_bands():
