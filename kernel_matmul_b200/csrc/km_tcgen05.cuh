@@ -45,12 +45,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, unsigned bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// Bounded wait for the phase with the given parity.  false = gave up.  Each try_wait may suspend
-// the thread for up to TC_WAIT_HINT_NS (it resumes as soon as the phase completes), which keeps
-// waiting warps from spending issue slots on polling.
-#ifndef TC_WAIT_HINT_NS
-#define TC_WAIT_HINT_NS 1000
-#endif
+// Bounded wait for the phase with the given parity.  false = gave up.  (try_wait suspends the
+// thread for a short, system-defined time; an explicit suspend-time hint was tried and only
+// added instructions.)
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
     const uint32_t addr = smem_u32(bar);
     for (unsigned poll = 0; poll < TC_WAIT_POLLS; poll++) {
@@ -58,11 +55,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
         asm volatile(
             "{\n\t"
             ".reg .pred p;\n\t"
-            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
             "selp.u32 %0, 1, 0, p;\n\t"
             "}"
             : "=r"(done)
-            : "r"(addr), "r"(parity), "r"((unsigned)TC_WAIT_HINT_NS)
+            : "r"(addr), "r"(parity)
             : "memory");
         if (done) return true;
     }
