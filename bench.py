@@ -14,9 +14,10 @@ gradient).
 Printed keys (one JSON line, rank 0):
   value      whole-job units/s with inputs resident in HBM, CUDA-event time per step summed over
              K steps, L2 flushed between steps, max over ranks;
-  e2e        the same metric through the public ops with HOST (pinned) buffers: every step
-             copies x, rhs, params and out_grad to the device, builds the band on the device,
-             runs forward + gradient and copies out and grad back;
+  e2e        the same metric through ``kernel_matmul_b200.host.matmul_and_grad_from_host`` with
+             HOST (pinned) buffers: every step copies x, rhs, params and out_grad to the device,
+             builds the band on the device, runs forward + gradient and copies out and grad back
+             (copies on two extra streams, overlapping the kernels);
   roofline   the dominant kernel against the pipe that bounds it, measured live with the library's
              calibration kernels: the SFU rate for the tensor-core kernels (the contraction runs as
              tcgen05.mma; generating kappa costs 2-3 SFU operations per entry), the FP32 FFMA rate
@@ -375,17 +376,14 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
     h2d = sum(t.numel() * t.element_size() for t in (hx, hrhs, hp, hog))
     d2h = sum(t.numel() * t.element_size() for t in (hout, hgrad))
 
+    from kernel_matmul_b200 import host
+
+    host_streams = host.HostStreams(dev)
+
     def e2e_step():
-        dx = hx.to(dev, non_blocking=True)
-        drhs = hrhs.to(dev, non_blocking=True).expand(B, -1, -1)
-        dp = hp.to(dev, non_blocking=True)
-        dog = hog.to(dev, non_blocking=True)
-        st, en = workloads.band(w, dx)
-        dxb = dx.expand(B, -1)
-        out = ops.matmul(kt, dxb, dxb, drhs, dp, st, en, path=path)
-        g = ops.matmul_bwd(kt, dxb, dxb, drhs, dp, st, en, dog, path=path)
-        hout.copy_(out, non_blocking=True)
-        hgrad.copy_(g, non_blocking=True)
+        # copies in, band construction, product, gradient and copies out, overlapped on three streams
+        host.matmul_and_grad_from_host(kt, hx, hrhs, hp, hog, lambda dx: workloads.band(w, dx), hout, hgrad,
+                                       host_streams, path=path)
 
     for _ in range(2):
         e2e_step()

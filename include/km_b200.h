@@ -279,6 +279,16 @@ KM_API int km_make_ranges_symmetric_f32(int64_t B, int64_t n, const float *x, fl
                                  int32_t block_size, int32_t *start, int32_t *end,
                                  int32_t *flags, void *stream);
 
+/* The symmetric pattern for B kernels with their own cutoffs in one call: cutoffs (device, B
+ * fp32); x (B rows, x_batch_stride elements apart; 0 = one x shared by all).  Equals B calls of
+ * km_make_ranges_symmetric_f32 -- a mixture of components with different lengthscales over the
+ * same inputs builds its bands with one set of launches instead of B.  No reference counterpart
+ * (the reference takes one cutoff per call). */
+KM_API int km_make_ranges_symmetric_cutoffs_f32(int64_t B, int64_t n, const float *x,
+                                         int64_t x_batch_stride, const float *cutoffs,
+                                         int32_t block_size, int32_t *start, int32_t *end,
+                                         int32_t *flags, void *stream);
+
 /* ranges.transpose_ranges(start, end, x1_size, x2_size, block_size)
  * (native/ranges/ranges.cpp:103-150).  start, end (B, R); start_t, end_t (B, ceil(x2_size/block)).
  * The caller checks block alignment (kernel_matmul/ranges.py:110-113). */

@@ -88,6 +88,8 @@ def _load() -> ctypes.CDLL:
     lib.km_make_ranges_f32.argtypes = [i64, i64, i64, vp, vp, ctypes.c_float, i32, i32, vp, vp, vp, vp]
     lib.km_make_ranges_symmetric_f32.restype = ctypes.c_int
     lib.km_make_ranges_symmetric_f32.argtypes = [i64, i64, vp, ctypes.c_float, i32, vp, vp, vp, vp]
+    lib.km_make_ranges_symmetric_cutoffs_f32.restype = ctypes.c_int
+    lib.km_make_ranges_symmetric_cutoffs_f32.argtypes = [i64, i64, vp, i64, vp, i32, vp, vp, vp, vp]
     lib.km_transpose_ranges_i32.restype = ctypes.c_int
     lib.km_transpose_ranges_i32.argtypes = [i64, i64, vp, vp, i64, i64, i32, vp, vp, vp]
     lib.km_count_entries.restype = ctypes.c_int
@@ -107,7 +109,7 @@ EXPORTED = [
     "km_matmul_bwd_tc_f32",
     "km_bilinear_derivative_f32", "km_bilinear_derivative_static_f32", "km_matmul_bwd_f32", "km_dense_f32", "km_dense_bwd_f32",
     "km_index_f32", "km_index_bwd_workspace_bytes", "km_index_bwd_f32", "km_make_ranges_f32",
-    "km_make_ranges_symmetric_f32", "km_transpose_ranges_i32", "km_count_entries",
+    "km_make_ranges_symmetric_f32", "km_make_ranges_symmetric_cutoffs_f32", "km_transpose_ranges_i32", "km_count_entries",
     "km_probe_fp32_peak", "km_probe_sfu_peak",
 ]
 

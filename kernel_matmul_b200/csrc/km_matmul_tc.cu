@@ -17,20 +17,21 @@
 //    by a power of two so that its largest magnitude lies in [2^13, 2^14) -- a pre-pass finds the
 //    column maxima, writes the scaled hi / lo images in the tensor core's K-major layout and
 //    the inverse scales, which the epilogue applies;
-//  * a generator evaluates the 32 entries of its row for a tile, splits them and writes both
+//  * a generator evaluates the entries of its row for a tile (32 band columns; 64 at N = 128,
+//    shared by four generator groups), splits them and writes both
 //    parts straight into TENSOR MEMORY with tcgen05.st: its row is its tensor-memory lane, the
 //    values are consecutive columns (two fp16 per column) -- exactly the layout tcgen05.mma takes
 //    for an A operand in tensor memory, so the kernel matrix never touches shared memory;
 //  * a control warp fetches rhs tiles (one bulk copy per 64 band columns) and x2 values
 //    (cp.async) into a ring of shared-memory slots and one of its lanes issues the MMAs
 //    D[128 x N] += A[128 x 16] . B[16 x N] (N = 16, 32, 64 or 128; wider right-hand sides are
-//    processed in blocks of 128 columns), six per tile;
-//  * accumulators live in tensor memory for at most TC_PROMO tiles (the tensor core adds with
+//    processed in blocks of 128 columns), three per 16 band columns;
+//  * accumulators live in tensor memory for at most 256 band columns (the tensor core adds with
 //    truncation) and are then added to fp32 registers of the generator that owns the row, two
 //    accumulators alternating.
 //
 // Four CTAs share an SM at N = 16 (128 tensor-memory columns each; three at N = 32, two at
-// N = 64, one with 256 generator threads at N = 128).  All hand-offs are mbarriers; every
+// N = 64, one with 512 generator threads at N = 128).  All hand-offs are mbarriers; every
 // wait is bounded and a give-up is reported through the status word of the workspace.
 #include <cuda_fp16.h>
 
@@ -39,28 +40,32 @@
 namespace km {
 
 constexpr int TC_MAX_N = 128;                   // widest GEMM N (rhs columns per CTA) of this kernel
-constexpr int TC_BK = 32;                       // band columns per tile: two MMA steps of K = 16
-constexpr int TC_SUPER = 2;                     // tiles per rhs / x2 slot
-constexpr int TC_SCOLS = TC_BK * TC_SUPER;      // band columns per slot (64)
-constexpr int TC_A_COLS = TC_BK;                // tensor-memory columns per A stage: per 16 band columns hi 8 | lo 8
+constexpr int TC_SCOLS = 64;                    // band columns per rhs / x2 slot
 constexpr int TC_SLOTS = 4;                     // rhs / x2 slots in shared memory
-constexpr int TC_PROMO = 8;                     // tiles per accumulator group
+constexpr int TC_GROUP_COLS = 256;              // band columns per accumulator group (48 MMAs)
 // per image slot in the workspace: [TC_MAX_N column maxima (bit patterns) | TC_MAX_N inverse scales]
 constexpr int TC_SCALE_WORDS = 2 * TC_MAX_N;
 
 // Per GEMM width N (rhs columns padded to 16 / 32 / 64 / 128): tensor-memory and shared-memory budget.
 //   N = 16:  3 A stages (96 columns) + 2 accumulators of 16 = 128 columns, 4 CTAs per SM
 //   N = 32:  2 A stages (64)         + 2 x 32            = 128 columns, 3 CTAs per SM (registers)
-//   N = 64:  3 A stages (96)         + 2 x 64            = 224 -> 256 columns, 2 CTAs per SM
-//   N = 128: 3 A stages (96)         + 2 x 128           = 352 -> 512 columns, 1 CTA per SM with two
-//            generator groups of 128 threads: group g generates the band columns [16g, 16g + 16) of
-//            every tile and owns the accumulator columns [64g, 64g + 64) of its row
+//   N = 64:  3 A stages (96)         + 2 x 64            = 224 -> 256 columns, 2 CTAs per SM with two
+//            generator groups (16 of the 32 band columns of a tile and 32 accumulator columns each)
+//   N = 128: 3 A stages of 64 (192) + 2 x 128           = 448 -> 512 columns, 1 CTA per SM with four
+//            generator groups of 128 threads and tiles of 64 band columns: group g generates the band
+//            columns [16g, 16g + 16) of every tile and owns the accumulator columns [32g, 32g + 32)
+//            of its row
+// A tile is BK band columns (BK / 16 MMA steps of K = 16); a thread generates 16 columns per step it owns.
 template <int N>
 struct TcCfg {
-    static constexpr int G = N == 128 ? 2 : 1;  // generator groups of 128 threads
+    static constexpr int G = N == 128 ? 4 : (N == 64 ? 2 : 1);  // generator groups of 128 threads
     static constexpr int THREADS = 128 * G + 32;
+    static constexpr int BK = N == 128 ? 64 : 32;        // band columns per tile
+    static constexpr int SUPER = TC_SCOLS / BK;           // tiles per rhs / x2 slot
+    static constexpr int A_COLS = BK;                     // tensor-memory columns per A stage: per 16 band columns hi 8 | lo 8
+    static constexpr int PROMO = TC_GROUP_COLS / BK;      // tiles per accumulator group
     static constexpr int A_STAGES = N == 32 ? 2 : 3;
-    static constexpr int ACC_COL = A_STAGES * TC_A_COLS;
+    static constexpr int ACC_COL = A_STAGES * A_COLS;
     static constexpr int TMEM_COLS = N <= 32 ? 128 : (N == 64 ? 256 : 512);
     static constexpr int MIN_CTAS = N == 16 ? 4 : (N == 32 ? 3 : (N == 64 ? 2 : 1));
     static constexpr int IMG_HALFS = 2 * TC_SCOLS * N;  // hi + lo image of one slot (fp16 values)
@@ -193,6 +198,10 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
     using Cfg = TcCfg<N>;
     constexpr int G = Cfg::G;
     constexpr int NPT = N / G;  // accumulator columns per thread
+    constexpr int TC_BK = Cfg::BK;
+    constexpr int TC_SUPER = Cfg::SUPER;
+    constexpr int TC_A_COLS = Cfg::A_COLS;
+    constexpr int TC_PROMO = Cfg::PROMO;
     constexpr int TC_A_STAGES = Cfg::A_STAGES;
     constexpr int TC_ACC_COL = Cfg::ACC_COL;
     constexpr int TC_TMEM_COLS = Cfg::TMEM_COLS;

@@ -22,12 +22,13 @@
 namespace km {
 
 // flags[b] = 1 iff x[b, :] is non-decreasing.  flags must be preset to 1.
-__global__ void check_sorted_kernel(int64_t B, int64_t n, const float *x, int32_t *flags) {
+// `xs`: elements between batch rows of x (n, or 0 when every batch row shares one x).
+__global__ void check_sorted_kernel(int64_t B, int64_t n, const float *x, int64_t xs, int32_t *flags) {
     const int64_t total = B * n;
     for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
          idx += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t j = idx % n;
-        if (j + 1 < n && !(x[idx] <= x[idx + 1])) flags[idx / n] = 0;
+        const int64_t j = idx % n, b = idx / n;
+        if (j + 1 < n && !(x[b * xs + j] <= x[b * xs + j + 1])) flags[b] = 0;
     }
 }
 
@@ -50,15 +51,18 @@ __device__ __forceinline__ int64_t first_true(int64_t G, Pred pred) {
 // Per (batch, row block): lb (first grid column within cutoff below the block's first row) and
 // ub (first grid column beyond cutoff above the block's last row), written to start / end as
 // scratch.  mode 0 = make_ranges, mode 1 = symmetric (only ub, predicate with >=).
-__global__ void range_bounds_kernel(int64_t B, int64_t m, int64_t n, int64_t R, const float *x1, const float *x2,
-                                    float cutoff, int block, int step, int mode, const int32_t *flags,
-                                    int32_t *start, int32_t *end) {
+// `cutoffs` (device, B values) overrides the scalar when not null; x1s / x2s: elements between
+// batch rows (0: shared).
+__global__ void range_bounds_kernel(int64_t B, int64_t m, int64_t n, int64_t R, const float *x1, int64_t x1s,
+                                    const float *x2, int64_t x2s, float cutoff_scalar, const float *cutoffs, int block,
+                                    int step, int mode, const int32_t *flags, int32_t *start, int32_t *end) {
     const int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (idx >= B * R) return;
     const int64_t b = idx / R, i = idx % R;
     if (!flags[b]) return;
-    const float *a = x1 + b * m;
-    const float *c = x2 + b * n;
+    const float cutoff = cutoffs ? cutoffs[b] : cutoff_scalar;
+    const float *a = x1 + b * x1s;
+    const float *c = x2 + b * x2s;
     const int64_t G = (n + step - 1) / step;
     const float last = a[min((i + 1) * (int64_t)block, m) - 1];
     if (mode == 0) {
@@ -150,13 +154,15 @@ __global__ void symmetric_start_kernel(int64_t B, int64_t n, int64_t R, int bloc
 
 // Sequential restatement of the reference scans for batch rows whose x2 is not sorted
 // (native/ranges/ranges.cpp:24-59 and :76-97).  One thread per batch row.
-__global__ void ranges_sequential_kernel(int64_t B, int64_t m, int64_t n, int64_t R, const float *x1,
-                                         const float *x2, float cutoff, int block, int step, int mode,
-                                         const int32_t *flags, int32_t *start, int32_t *end) {
+__global__ void ranges_sequential_kernel(int64_t B, int64_t m, int64_t n, int64_t R, const float *x1, int64_t x1s,
+                                         const float *x2, int64_t x2s, float cutoff_scalar, const float *cutoffs,
+                                         int block, int step, int mode, const int32_t *flags, int32_t *start,
+                                         int32_t *end) {
     const int64_t b = blockIdx.x * (int64_t)blockDim.x + threadIdx.x;
     if (b >= B || flags[b]) return;
-    const float *a = x1 + b * m;
-    const float *c = x2 + b * n;
+    const float cutoff = cutoffs ? cutoffs[b] : cutoff_scalar;
+    const float *a = x1 + b * x1s;
+    const float *c = x2 + b * x2s;
     int32_t *S = start + b * R, *E = end + b * R;
     if (mode == 0) {
         int64_t ps = 0, pe = 0;
@@ -255,9 +261,9 @@ static inline unsigned grid_for(int64_t total, int threads) {
     return (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(total, threads), 1 << 20));
 }
 
-static int make_ranges_common(const char *name, int64_t B, int64_t m, int64_t n, const float *x1, const float *x2,
-                              float cutoff, int block, int step, int mode, int32_t *start, int32_t *end,
-                              int32_t *flags, cudaStream_t s) {
+static int make_ranges_common(const char *name, int64_t B, int64_t m, int64_t n, const float *x1, int64_t x1s,
+                              const float *x2, int64_t x2s, float cutoff, const float *cutoffs, int block, int step,
+                              int mode, int32_t *start, int32_t *end, int32_t *flags, cudaStream_t s) {
     KM_REQUIRE(B >= 0 && m >= 0 && n >= 0 && n <= 0x7fffffffLL - 2 * (int64_t)block && m <= 0x7fffffffLL,
                KM_ERR_INVALID_ARGUMENT, "%s: bad sizes", name);
     KM_REQUIRE(block >= 1, KM_ERR_INVALID_ARGUMENT, "%s: block_size must be >= 1", name);
@@ -266,17 +272,17 @@ static int make_ranges_common(const char *name, int64_t B, int64_t m, int64_t n,
     KM_REQUIRE(x1 && x2 && start && end && flags, KM_ERR_INVALID_ARGUMENT, "%s: null pointer", name);
     KM_REQUIRE(B <= 0x7fffffffLL, KM_ERR_UNSUPPORTED, "%s: too many batch rows", name);
     fill_flags_kernel<<<grid_for(B, 256), 256, 0, s>>>(B, flags);
-    if (n > 1) check_sorted_kernel<<<(unsigned)std::min<int64_t>(ceil_div(B * n, 256), 148 * 16), 256, 0, s>>>(B, n, x2, flags);
-    range_bounds_kernel<<<grid_for(B * R, 256), 256, 0, s>>>(B, m, n, R, x1, x2, cutoff, block, step, mode, flags,
-                                                             start, end);
+    if (n > 1) check_sorted_kernel<<<(unsigned)std::min<int64_t>(ceil_div(B * n, 256), 148 * 16), 256, 0, s>>>(B, n, x2, x2s, flags);
+    range_bounds_kernel<<<grid_for(B * R, 256), 256, 0, s>>>(B, m, n, R, x1, x1s, x2, x2s, cutoff, cutoffs, block, step,
+                                                             mode, flags, start, end);
     if (mode == 0) {
         prefix_max_kernel<<<(unsigned)B, 1024, 0, s>>>(R, flags, start, end, 0, 0);
     } else {
         prefix_max_kernel<<<(unsigned)B, 1024, 0, s>>>(R, flags, end, nullptr, 1, block);
         symmetric_start_kernel<<<grid_for(B * R, 256), 256, 0, s>>>(B, n, R, block, flags, end, start);
     }
-    ranges_sequential_kernel<<<grid_for(B, 32), 32, 0, s>>>(B, m, n, R, x1, x2, cutoff, block, step, mode, flags,
-                                                            start, end);
+    ranges_sequential_kernel<<<grid_for(B, 32), 32, 0, s>>>(B, m, n, R, x1, x1s, x2, x2s, cutoff, cutoffs, block, step,
+                                                            mode, flags, start, end);
     KM_CHECK_LAUNCH(name);
     return KM_OK;
 }
@@ -286,14 +292,25 @@ static int make_ranges_common(const char *name, int64_t B, int64_t m, int64_t n,
 extern "C" int km_make_ranges_f32(int64_t B, int64_t m, int64_t n, const float *x1, const float *x2, float cutoff,
                                   int32_t block_size, int32_t align, int32_t *start, int32_t *end, int32_t *flags,
                                   void *stream) {
-    return km::make_ranges_common("km_make_ranges_f32", B, m, n, x1, x2, cutoff, block_size,
+    return km::make_ranges_common("km_make_ranges_f32", B, m, n, x1, m, x2, n, cutoff, nullptr, block_size,
                                   align ? block_size : 1, 0, start, end, flags, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int km_make_ranges_symmetric_f32(int64_t B, int64_t n, const float *x, float cutoff, int32_t block_size,
                                             int32_t *start, int32_t *end, int32_t *flags, void *stream) {
-    return km::make_ranges_common("km_make_ranges_symmetric_f32", B, n, n, x, x, cutoff, block_size, block_size, 1,
-                                  start, end, flags, static_cast<cudaStream_t>(stream));
+    return km::make_ranges_common("km_make_ranges_symmetric_f32", B, n, n, x, n, x, n, cutoff, nullptr, block_size,
+                                  block_size, 1, start, end, flags, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int km_make_ranges_symmetric_cutoffs_f32(int64_t B, int64_t n, const float *x, int64_t x_batch_stride,
+                                                    const float *cutoffs, int32_t block_size, int32_t *start,
+                                                    int32_t *end, int32_t *flags, void *stream) {
+    KM_REQUIRE(cutoffs != nullptr || B == 0, KM_ERR_INVALID_ARGUMENT, "km_make_ranges_symmetric_cutoffs_f32: null cutoffs");
+    KM_REQUIRE(x_batch_stride == 0 || x_batch_stride >= n, KM_ERR_INVALID_ARGUMENT,
+               "km_make_ranges_symmetric_cutoffs_f32: x_batch_stride must be 0 (shared x) or at least n");
+    return km::make_ranges_common("km_make_ranges_symmetric_cutoffs_f32", B, n, n, x, x_batch_stride, x, x_batch_stride,
+                                  0.0f, cutoffs, block_size, block_size, 1, start, end, flags,
+                                  static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int km_transpose_ranges_i32(int64_t B, int64_t R, const int32_t *start, const int32_t *end,

@@ -84,6 +84,33 @@ def make_ranges(
     return start, end
 
 
+def make_ranges_symmetric_cutoffs(cutoffs: Tensor, x: Tensor, *, block_size: int = _BLOCK_SIZE) -> tuple[Tensor, Tensor]:
+    """The symmetric, block-aligned patterns of ``B`` kernels with their own cutoffs in one call.
+
+    ``cutoffs``: ``(B,)`` float tensor; ``x``: ``(n,)`` (shared by all) or ``(B, n)``.  Returns
+    ``(start, end)`` of shape ``(B, ceil(n / block_size))``, equal to stacking
+    ``make_ranges(cutoffs[b], x[b])``.  A mixture of components with different lengthscales over
+    the same inputs builds its bands with one set of launches instead of ``B`` (the reference
+    takes one cutoff per call, kernel_matmul/ranges.py:14-60).
+    """
+    if cutoffs.dim() != 1 or x.dim() not in (1, 2) or (x.dim() == 2 and x.shape[0] != cutoffs.shape[0]):
+        raise RuntimeError("cutoffs must be (B,) and x (n,) or (B, n)")
+    out_device = x.device
+    dev = _device_for(x)
+    B, n = cutoffs.shape[0], x.shape[-1]
+    rows = int(math.ceil(n / block_size))
+    xd = x.detach().to(device=dev, dtype=torch.float32).contiguous()
+    cd = cutoffs.detach().to(device=dev, dtype=torch.float32).contiguous()
+    start = torch.empty(B, rows, dtype=torch.int32, device=dev)
+    end = torch.empty(B, rows, dtype=torch.int32, device=dev)
+    flags = torch.empty(max(B, 1), dtype=torch.int32, device=dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    with torch.cuda.device(dev):
+        check(lib.km_make_ranges_symmetric_cutoffs_f32(B, n, _ptr(xd), n if x.dim() == 2 else 0, _ptr(cd), block_size,
+                                                       _ptr(start), _ptr(end), _ptr(flags), stream))
+    return start.to(out_device), end.to(out_device)
+
+
 def transpose_ranges(
     start: Tensor, end: Tensor, x1_size: int, x2_size: int, *, block_size: int = _BLOCK_SIZE
 ) -> tuple[Tensor, Tensor]:

@@ -92,6 +92,12 @@ def band(workload: Workload, x_dev: Tensor) -> tuple[Tensor, Tensor]:
     for an unbatched workload)."""
     from . import ranges
 
+    if len(workload.cutoffs) > 1 and all(c is not None for c in workload.cutoffs):
+        # one band per component, all built by one set of launches
+        key = ("cutoffs", str(x_dev.device))
+        if key not in workload.extra:
+            workload.extra[key] = torch.tensor(workload.cutoffs, dtype=torch.float32, device=x_dev.device)
+        return ranges.make_ranges_symmetric_cutoffs(workload.extra[key], x_dev)
     rows = [ranges.make_ranges(c, x_dev) for c in workload.cutoffs]
     if workload.params.dim() == 1:
         return rows[0]

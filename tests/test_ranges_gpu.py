@@ -64,3 +64,22 @@ def test_no_cutoff_and_errors():
     s, e = ranges.make_ranges(1.0, a, b, block_size=2, align=False)
     with pytest.raises(ValueError, match="Ranges must be block-aligned"):
         ranges.transpose_ranges(s, e, 3, 3, block_size=2)
+
+
+def test_symmetric_ranges_with_per_batch_cutoffs():
+    """One call with B cutoffs == B calls with one cutoff each (shared and per-batch x, sorted
+    and unsorted rows), bit for bit."""
+    from kernel_matmul_b200 import ranges
+
+    cutoffs = torch.tensor([0.3, 1.0, 2.5, 7.0, 20.0])
+    x = torch.sort(torch.rand(1000) * 10)[0]
+    s, e = ranges.make_ranges_symmetric_cutoffs(cutoffs.cuda(), x.cuda())
+    for b, c in enumerate(cutoffs.tolist()):
+        rs, re_ = ranges.make_ranges(c, x.cuda())
+        assert torch.equal(s[b], rs) and torch.equal(e[b], re_)
+    xb = torch.sort(torch.rand(5, 700) * 10)[0]
+    xb[3] = torch.rand(700) * 10  # an unsorted row takes the sequential scan
+    s, e = ranges.make_ranges_symmetric_cutoffs(cutoffs.cuda(), xb.cuda())
+    for b, c in enumerate(cutoffs.tolist()):
+        rs, re_ = ranges.make_ranges(c, xb[b].cuda())
+        assert torch.equal(s[b], rs) and torch.equal(e[b], re_)

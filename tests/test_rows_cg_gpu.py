@@ -91,3 +91,31 @@ def test_spectral_mixture_sum_shared_envelope(k, shared_lengthscale):
     scale = O.matmul("spectral", x.expand(B, n), x.expand(B, n), rhs.expand(B, n, k), params,
                      start.expand(B, -1), end.expand(B, -1)).abs().sum(0).max()
     assert float((out.cpu().double() - ref).abs().max() / scale) <= 1e-5
+
+
+def test_host_buffers_step_matches_the_ops():
+    """kernel_matmul_b200.host: overlapped copies + product + gradient == the plain ops."""
+    from kernel_matmul_b200 import host, ops, ranges
+
+    dev = torch.device("cuda:0")
+    B, n, k = 3, 3000, 16
+    x = torch.sort(torch.rand(n) * 50)[0].pin_memory()
+    rhs = torch.randn(n, k).pin_memory()
+    params = torch.stack([1 + torch.rand(B), 0.5 + 0.5 * torch.rand(B), 1 + torch.rand(B)], dim=-1).pin_memory()
+    og = torch.randn(B, n, k).pin_memory()
+    out = torch.empty(B, n, k).pin_memory()
+    grad = torch.empty(B, 3).pin_memory()
+    streams = host.HostStreams(dev)
+    band = lambda dx: ranges.make_ranges(3.0, dx)  # noqa: E731
+    for _ in range(2):  # twice: buffers and streams are reused
+        host.matmul_and_grad_from_host("spectral", x, rhs, params, og, band, out, grad, streams)
+        torch.cuda.current_stream(dev).synchronize()
+        dx = x.to(dev)
+        start, end = band(dx)
+        ref = ops.matmul("spectral", dx.expand(B, -1), dx.expand(B, -1), rhs.to(dev).expand(B, -1, -1), params.to(dev), start, end)
+        gref = ops.matmul_bwd("spectral", dx.expand(B, -1), dx.expand(B, -1), rhs.to(dev).expand(B, -1, -1), params.to(dev),
+                              start, end, og.to(dev))
+        assert torch.equal(out, ref.cpu())
+        assert torch.equal(grad, gref.cpu())
+        out.zero_()
+        grad.zero_()
