@@ -157,9 +157,9 @@ KM_API int km_matmul_bwd_f32(int kernel_type, const km_batch *batch, int64_t m, 
 /* ---------------------------------------------------------------------------------------
  * The same gradients with the coefficients <left[i, :], right[j, :]> computed on the tensor
  * cores (tcgen05.mma, 3xTF32 = fp32-level accuracy) while the threads evaluate the factors of
- * d kappa / d p: the FP32 pipe no longer pays k FMAs per entry.  At most 32 columns (k <= 32;
- * KM_ERR_UNSUPPORTED beyond -- use the entry points above).  Replaces the same reference calls
- * as km_bilinear_derivative_f32 / km_matmul_bwd_f32.
+ * d kappa / d p: the FP32 pipe no longer pays k FMAs per entry.  Up to 64 columns per pass; wider
+ * operands are processed in column blocks of 64.  Replaces the same reference calls as
+ * km_bilinear_derivative_f32 / km_matmul_bwd_f32.
  * workspace: km_grad_tc_workspace_bytes(...) bytes of device memory, 256-byte aligned: a 4-byte
  * status word (0 = ok, non-zero = a bounded wait inside the kernel gave up and the gradient is
  * invalid; read it with km_workspace_status), the per-row-block partial sums, and the hi / lo

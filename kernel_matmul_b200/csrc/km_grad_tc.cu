@@ -1,4 +1,4 @@
-// Hyper-parameter gradients with the coefficients on the tensor cores (k <= 32 columns).
+// Hyper-parameter gradients with the coefficients on the tensor cores.
 //
 //   grad[b, q] = d/d theta_q  sum_{i, j in band} coeff[i, j] * kappa(x1[b,i], x2[b,j]),
 //   coeff[i, j] = <left[b, i, :], right[b, j, :]>
@@ -10,6 +10,8 @@
 // copies of images laid out by a pre-pass) into a tensor-memory stage, while the 128 * G consumer
 // threads -- one tensor-memory lane = one row each -- read the previous stage with tcgen05.ld,
 // evaluate the factors of d kappa / d p per entry and add coeff * factor to their running sums.
+// (Up to 64 columns per CTA; wider operands are processed in column blocks of 64, whose partial
+// sums add up because the coefficient is linear in the columns.)
 // Per entry the FP32 pipe runs ~11 operations instead of k + 11, issued as packed f32x2
 // instructions for two entries at a time, so the kernel is bound by the SFU operations of kappa
 // (3 per spectral entry).
@@ -27,19 +29,21 @@ constexpr int GT_COLS = 64;       // band columns per tile = GEMM N
 constexpr int GT_D_STAGES = 2;    // coefficient tiles in tensor memory
 constexpr int GT_MAX_SLOTS = 4;   // right / x2 slots in shared memory
 constexpr int GT_TMEM_COLS = GT_D_STAGES * GT_COLS;
-constexpr int GT_MAX_K = 32;
+constexpr int GT_MAX_KP = 64;     // GEMM K per CTA; more columns are processed in blocks of 64
 
 struct GradTcArgs {
     Batch batch;
     int64_t m, n, k;
-    int kp;     // k rounded up to a multiple of 8 (GEMM K)
+    int kp;     // GEMM K per column block: min(k, 64) rounded up to a multiple of 8
+    int kblocks;  // column blocks (ceil(k / 64))
+    int64_t tiles_total;  // 64-column tiles of the whole band range: ceil(n / 64)
     int slots;  // shared-memory slots in use (<= GT_MAX_SLOTS)
     int64_t row_blocks;
     View<const float> x1, x2, left, params;
     View<const int> start, end;
-    const float *images;        // [image slot][tile][part: hi, lo][chunk = c / 4][j][c % 4]
+    const float *images;        // [image slot][column block][tile][part: hi, lo][chunk = c / 4][j][c % 4]
     int64_t image_slot_stride;  // floats between batch slots (0: right shared by all batches)
-    float *partials;            // [batch.count][row_blocks][KM_MAX_PARAMS]
+    float *partials;            // [batch.count][row_blocks][kblocks][KM_MAX_PARAMS]
     int *status;
 };
 
@@ -48,11 +52,11 @@ struct GradTcArgs {
 // fp32 word (the tensor core reads its TF32 bits), lo = x - trunc_tf32(x); rows past n and
 // columns past k are zero.  Also clears the status word.
 __global__ void __launch_bounds__(256) grad_tc_images_kernel(Batch batch, int64_t slots, int64_t n, int64_t k, int kp,
-                                                             int64_t tiles, View<const float> right, float *images,
-                                                             int *status) {
+                                                             int kblocks, int64_t tiles, View<const float> right,
+                                                             float *images, int *status) {
     if (blockIdx.x == 0 && threadIdx.x == 0) *status = 0;
     const int64_t img_floats = 2LL * kp * GT_COLS;
-    const int64_t total = slots * tiles * (int64_t)GT_COLS * kp;
+    const int64_t total = slots * kblocks * tiles * (int64_t)GT_COLS * kp;
     for (int64_t idx = blockIdx.x * 256LL + threadIdx.x; idx < total; idx += (int64_t)gridDim.x * 256) {
         int64_t rem = idx;
         const int c = (int)(rem % kp);
@@ -60,14 +64,17 @@ __global__ void __launch_bounds__(256) grad_tc_images_kernel(Batch batch, int64_
         const int jj = (int)(rem % GT_COLS);
         rem /= GT_COLS;
         const int64_t tile = rem % tiles;
-        const int64_t slot = rem / tiles;
+        rem /= tiles;
+        const int kb = (int)(rem % kblocks);
+        const int64_t slot = rem / kblocks;
         const int64_t j = tile * GT_COLS + jj;
+        const int64_t col = (int64_t)kb * kp + c;
         float v = 0.0f;
-        if (j < n && c < k) {
+        if (j < n && col < k) {
             const BatchIndex bi = decompose(batch, slot);
-            v = batch_ptr(right, bi)[j * right.s0 + c * right.s1];
+            v = batch_ptr(right, bi)[j * right.s0 + col * right.s1];
         }
-        float *img = images + (slot * tiles + tile) * img_floats;
+        float *img = images + ((slot * kblocks + kb) * tiles + tile) * img_floats;
         const int at = (c >> 2) * (GT_COLS * 4) + jj * 4 + (c & 3);
         img[at] = v;
         img[kp * GT_COLS + at] = v - tf32_hi(v);
@@ -80,7 +87,7 @@ __global__ void __launch_bounds__(256) grad_tc_images_kernel(Batch batch, int64_
 #define GT_MIN_CTAS 4
 #endif
 template <int KT, int G>
-__global__ void __launch_bounds__(128 * G + 32, GT_MIN_CTAS) grad_tc_kernel(const GradTcArgs a) {
+__global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_tc_kernel(const GradTcArgs a) {
     constexpr int WARPS = 4 * G;
     constexpr int NS = KernelFn<KT>::NSUMS;
     constexpr int CPT = GT_COLS / G;   // columns per thread and tile
@@ -110,7 +117,9 @@ __global__ void __launch_bounds__(128 * G + 32, GT_MIN_CTAS) grad_tc_kernel(cons
 
     int64_t item = blockIdx.x;
     const int64_t b = item % a.batch.count;
-    const int64_t r = item / a.batch.count;
+    item /= a.batch.count;
+    const int64_t r = item % a.row_blocks;
+    const int kb = (int)(item / a.row_blocks);  // block of kp columns of left / right
 
     const BatchIndex bi = decompose(a.batch, b);
     const float *x1 = batch_ptr(a.x1, bi);
@@ -124,7 +133,8 @@ __global__ void __launch_bounds__(128 * G + 32, GT_MIN_CTAS) grad_tc_kernel(cons
     const int band_hi = max(band_lo, min(batch_ptr(a.end, bi)[r * a.end.s0], n));
     const int tile_lo = band_lo / GT_COLS;
     const int tiles = band_hi > band_lo ? (band_hi + GT_COLS - 1) / GT_COLS - tile_lo : 0;
-    const float *images = a.images + (a.image_slot_stride ? b * a.image_slot_stride : 0);
+    const float *images = a.images + (a.image_slot_stride ? b * a.image_slot_stride : 0) +
+                          (int64_t)kb * a.tiles_total * (2LL * a.kp * GT_COLS);
 
     if (tid == 0) {
 #pragma unroll
@@ -147,7 +157,7 @@ __global__ void __launch_bounds__(128 * G + 32, GT_MIN_CTAS) grad_tc_kernel(cons
             float v[4];
 #pragma unroll
             for (int u = 0; u < 4; u++) {
-                const int c = kc * 4 + u;
+                const int64_t c = (int64_t)kb * kp + kc * 4 + u;  // column of left
                 v[u] = (row < a.m && c < a.k) ? left[row * a.left.s0 + c * a.left.s1] : 0.0f;
             }
             float *dst = smem_f + (kc * 128 + row_local) * 4;
@@ -309,19 +319,22 @@ __global__ void __launch_bounds__(128 * G + 32, GT_MIN_CTAS) grad_tc_kernel(cons
 #pragma unroll
             for (int w = 0; w < WARPS; w++) v += warp_sums[w][tid];
         }
-        a.partials[(b * a.row_blocks + r) * KM_MAX_PARAMS + tid] = v;
+        a.partials[((b * a.row_blocks + r) * a.kblocks + kb) * KM_MAX_PARAMS + tid] = v;
     }
     if (is_ctl_warp) tmem_free(tmem_base, GT_TMEM_COLS);
 }
 
-static size_t grad_tc_partials_bytes(const Batch &b, int64_t m) {
-    const size_t raw = (size_t)(b.count * ceil_div(m, KM_BLOCK_SIZE)) * KM_MAX_PARAMS * sizeof(float);
+static int64_t grad_tc_kblocks(int64_t k) { return std::max<int64_t>(1, ceil_div(k, GT_MAX_KP)); }
+static int grad_tc_kp(int64_t k) { return (int)std::max<int64_t>(8, ceil_div(std::min<int64_t>(k, GT_MAX_KP), 8) * 8); }
+
+static size_t grad_tc_partials_bytes(const Batch &b, int64_t m, int64_t k) {
+    const size_t raw = (size_t)(b.count * ceil_div(m, KM_BLOCK_SIZE) * grad_tc_kblocks(k)) * KM_MAX_PARAMS * sizeof(float);
     return (raw + 255) / 256 * 256;
 }
 
 template <int KT, int G>
 static int launch_grad_tc(const GradTcArgs &a, cudaStream_t s) {
-    const int64_t items = a.batch.count * a.row_blocks;
+    const int64_t items = a.batch.count * a.row_blocks * a.kblocks;
     if (items > 0x7fffffffLL) {
         set_error("gradient (tensor cores): too many work items (%lld)", (long long)items);
         return KM_ERR_UNSUPPORTED;
@@ -344,7 +357,10 @@ static int launch_grad_tc(const GradTcArgs &a, cudaStream_t s) {
 #endif
 template <int KT>
 static int dispatch_grad_tc(const GradTcArgs &a, cudaStream_t s) {
-    return a.kp <= 16 ? launch_grad_tc<KT, GT_G_SMALL>(a, s) : launch_grad_tc<KT, 2>(a, s);
+    // consumer groups by GEMM K: shared memory (left rows + right tiles) decides the CTAs per SM
+    if (a.kp <= 16) return launch_grad_tc<KT, GT_G_SMALL>(a, s);
+    if (a.kp <= 32) return launch_grad_tc<KT, 2>(a, s);
+    return launch_grad_tc<KT, 4>(a, s);
 }
 
 static int grad_tc_entry(const char *name, int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
@@ -355,8 +371,6 @@ static int grad_tc_entry(const char *name, int kernel_type, const km_batch *batc
     KM_REQUIRE(batch && x1 && x2 && left && right && params && start && end && grad, KM_ERR_INVALID_ARGUMENT,
                "%s: null argument", name);
     KM_REQUIRE(m >= 0 && n >= 0 && k >= 0 && n <= 0x7fffffffLL - GT_COLS, KM_ERR_INVALID_ARGUMENT, "%s: bad sizes", name);
-    KM_REQUIRE(k <= GT_MAX_K, KM_ERR_UNSUPPORTED, "%s: at most %d columns (got %lld); use the FMA entry point", name,
-               GT_MAX_K, (long long)k);
     GradTcArgs a;
     int rc = make_batch(batch, &a.batch);
     if (rc != KM_OK) return rc;
@@ -369,7 +383,8 @@ static int grad_tc_entry(const char *name, int kernel_type, const km_batch *batc
     a.m = m;
     a.n = n;
     a.k = k;
-    a.kp = (int)std::max<int64_t>(8, ceil_div(k, 8) * 8);
+    a.kp = grad_tc_kp(k);
+    a.kblocks = (int)grad_tc_kblocks(k);
     a.slots = a.kp <= 16 ? 4 : 3;
     a.row_blocks = ceil_div(m, KM_BLOCK_SIZE);
     a.x1 = make_view<const float>(x1, a.batch);
@@ -383,19 +398,20 @@ static int grad_tc_entry(const char *name, int kernel_type, const km_batch *batc
     unsigned char *ws = static_cast<unsigned char *>(workspace);
     a.status = reinterpret_cast<int *>(ws);
     a.partials = reinterpret_cast<float *>(ws + TC_STATUS_BYTES);
-    float *images = reinterpret_cast<float *>(ws + TC_STATUS_BYTES + grad_tc_partials_bytes(a.batch, m));
+    float *images = reinterpret_cast<float *>(ws + TC_STATUS_BYTES + grad_tc_partials_bytes(a.batch, m, k));
     a.images = images;
     const int64_t slots = tc_slots(a.batch, rv);
     const int64_t tiles = ceil_div(n, GT_COLS);
-    a.image_slot_stride = slots > 1 ? tiles * (2LL * a.kp * GT_COLS) : 0;
+    a.tiles_total = tiles;
+    a.image_slot_stride = slots > 1 ? a.kblocks * tiles * (2LL * a.kp * GT_COLS) : 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (a.row_blocks > 0) {
         KM_REQUIRE(x1->data && left->data && start->data && end->data, KM_ERR_INVALID_ARGUMENT,
                    "%s: null data pointer", name);
         KM_REQUIRE(n == 0 || (x2->data && right->data), KM_ERR_INVALID_ARGUMENT, "%s: null data pointer", name);
-        const int64_t total = slots * tiles * (int64_t)GT_COLS * a.kp;
+        const int64_t total = slots * a.kblocks * tiles * (int64_t)GT_COLS * a.kp;
         const unsigned blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(total, 256), 148 * 32));
-        grad_tc_images_kernel<<<blocks, 256, 0, s>>>(a.batch, slots, n, k, a.kp, tiles, rv, images, a.status);
+        grad_tc_images_kernel<<<blocks, 256, 0, s>>>(a.batch, slots, n, k, a.kp, a.kblocks, tiles, rv, images, a.status);
         KM_CHECK_LAUNCH("gradient (tensor cores) pre-pass launch");
         switch (kernel_type) {
         case KM_KERNEL_RBF: rc = dispatch_grad_tc<KM_KERNEL_RBF>(a, s); break;
@@ -404,7 +420,7 @@ static int grad_tc_entry(const char *name, int kernel_type, const km_batch *batc
         }
         if (rc != KM_OK) return rc;
     }
-    return launch_grad_finish(kernel_type, a.batch, a.row_blocks, a.partials, false, a.params, gv, s);
+    return launch_grad_finish(kernel_type, a.batch, a.row_blocks * a.kblocks, a.partials, false, a.params, gv, s);
 }
 
 }  // namespace km
@@ -413,12 +429,11 @@ extern "C" size_t km_grad_tc_workspace_bytes(const km_batch *batch, int64_t m, i
                                              const km_view *right) {
     using namespace km;
     Batch b;
-    if (batch == nullptr || right == nullptr || make_batch(batch, &b) != KM_OK || m < 0 || n < 0 || k < 0 || k > GT_MAX_K)
-        return 0;
+    if (batch == nullptr || right == nullptr || make_batch(batch, &b) != KM_OK || m < 0 || n < 0 || k < 0) return 0;
     const View<const float> rv = make_view<const float>(right, b);
-    const int64_t kp = std::max<int64_t>(8, ceil_div(k, 8) * 8);
-    return (size_t)TC_STATUS_BYTES + grad_tc_partials_bytes(b, m) +
-           (size_t)(tc_slots(b, rv) * ceil_div(n, GT_COLS)) * (2 * kp * GT_COLS) * sizeof(float);
+    const int64_t kp = grad_tc_kp(k);
+    return (size_t)TC_STATUS_BYTES + grad_tc_partials_bytes(b, m, k) +
+           (size_t)(tc_slots(b, rv) * grad_tc_kblocks(k) * ceil_div(n, GT_COLS)) * (2 * kp * GT_COLS) * sizeof(float);
 }
 
 extern "C" int km_bilinear_derivative_tc_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,

@@ -18,7 +18,7 @@ import torch
 from torch import Tensor
 
 from . import _lib
-from ._lib import KmError, KM_MAX_BATCH_DIMS, KERNEL_TYPES, KmBatch, KmView, check, lib
+from ._lib import KM_MAX_BATCH_DIMS, KERNEL_TYPES, KmBatch, KmView, check, lib
 
 BLOCK_SIZE = 128
 NUM_PARAMS = {"rbf": 2, "spectral": 3, "locally_periodic": 4}
@@ -233,9 +233,9 @@ def matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: T
     return out
 
 
-#: column counts for which the gradient ops take the tensor-core kernels on ``path="auto"``
+#: column count from which the gradient ops take the tensor-core kernel on ``path="auto"``
 #: (if the problem has ``TENSOR_CORE_MIN_ITEMS`` work items)
-GRAD_TENSOR_CORE_K = range(8, 33)
+GRAD_TENSOR_CORE_MIN_K = 8
 
 
 def _grad_call(which: str, kernel_type, x1, x2, left, right, params, start, end, path: str) -> Tensor:
@@ -247,7 +247,7 @@ def _grad_call(which: str, kernel_type, x1, x2, left, right, params, start, end,
     k = left.shape[-1]
     if path not in ("auto", "fma", "tc"):
         raise ValueError(f"unknown path {path!r}")
-    tc = path == "tc" or (path == "auto" and k in GRAD_TENSOR_CORE_K and _enough_items(batch, m))
+    tc = path == "tc" or (path == "auto" and k >= GRAD_TENSOR_CORE_MIN_K and _enough_items(batch, m))
     P = NUM_PARAMS[kernel_type]
     grad = torch.empty(*batch, P, device=dev, dtype=torch.float32)
     grade = grad.reshape(-1, P) if len(batch) > KM_MAX_BATCH_DIMS else grad
@@ -255,8 +255,6 @@ def _grad_call(which: str, kernel_type, x1, x2, left, right, params, start, end,
     lv, rv = _view(le, 2), _view(rte, 2)
     if tc:
         ws_bytes = lib.km_grad_tc_workspace_bytes(kb, m, n, k, rv)
-        if ws_bytes == 0:
-            raise KmError(f"the tensor-core gradient takes at most 32 columns, got {k}")
         fn = lib.km_matmul_bwd_tc_f32 if which == "matmul_bwd" else lib.km_bilinear_derivative_tc_f32
     else:
         ws_bytes = lib.km_grad_workspace_bytes(kid, kb, m)
@@ -278,8 +276,7 @@ def matmul_bwd(kernel_type: str, x1, x2, rhs, params, start, end, out_grad, *, p
     """Gradient of ``sum(out_grad * matmul(...))`` wrt ``params`` -> ``(*batch, P)``.
 
     Reference: ``matmul_bwd.call(x1, x2, rhs, params, start, end, out_grad)``
-    (native/matmul_bwd/matmul_bwd.cpp:6-19).  ``path`` as in ``matmul`` (the tensor-core kernel
-    takes at most 32 columns).
+    (native/matmul_bwd/matmul_bwd.cpp:6-19).  ``path`` as in ``matmul``.
     """
     return _grad_call("matmul_bwd", kernel_type, x1, x2, out_grad, rhs, params, start, end, path)
 

@@ -163,16 +163,11 @@ def test_tc_gradient_unbanded_long_bands():
     _run_grad("rbf", 130, 2049, 24, cutoff=None)
 
 
-def test_tc_gradient_rejects_wide_operands():
-    from kernel_matmul_b200 import ops
-    from kernel_matmul_b200._lib import KmError
-
-    x = torch.sort(torch.rand(256) * 10)[0].cuda()
-    start = torch.zeros(2, dtype=torch.int32).cuda()
-    end = torch.full((2,), 256, dtype=torch.int32).cuda()
-    v = torch.randn(256, 40).cuda()
-    with pytest.raises(KmError):
-        ops.bilinear_derivative("rbf", x, x, v, v, torch.tensor([1.0, 1.0]).cuda(), start, end, path="tc")
+@pytest.mark.parametrize("kt", KERNEL_TYPES)
+@pytest.mark.parametrize("k", [33, 40, 64, 65, 100, 130])
+def test_tc_gradient_wide_operands(kt, k):
+    # up to 64 columns: four consumer groups; beyond: column blocks of 64
+    _run_grad(kt, 400, 500, k)
 
 
 def test_tc_narrow_column_scales():
