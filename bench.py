@@ -671,7 +671,7 @@ def run_single_op(args, local: int) -> None:
         E, k, kt = int(ops.count_entries(w.n, w.n, start, end)), 1, "rbf"
         fn = lambda: ops.matmul(kt, x, x, rhs, params, start, end)  # noqa: E731
         model = {"bound": "launch latency", "fp32_instr": fp32_instr_fwd(kt, k), "sfu": GEN_FWD[kt][1]}
-        units, kernel = E * k, "matmul_fma_kernel"
+        units, kernel = E * k, "matmul_fma_cluster_kernel"
     elif name == "locally_periodic_bilinear":
         w = workloads.locally_periodic_bilinear()
         B = w.params.shape[0]

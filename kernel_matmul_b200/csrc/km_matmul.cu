@@ -11,9 +11,13 @@
 //
 // Replaces kernel_matmul_cuda_kernel + the zero fill, parameter transform and column-slab sum
 // around it (reference: native/matmul/matmul.cu:13-203).
+#include <cooperative_groups.h>
+
 #include "km_common.cuh"
 
 namespace km {
+
+namespace cg = cooperative_groups;
 
 template <typename T>
 struct MatmulArgs {
@@ -214,6 +218,111 @@ __global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN, 384 / (32 * (128
     store_tile<KB, RPT, WN>(a, out, r, a.rb_begin * KM_BLOCK_SIZE, k0, fn.scale, smem, tid, acc);
 }
 
+// The same product for SMALL problems (fewer work items than half the SMs): a thread-block
+// cluster of S CTAs shares one work item.  CTA c walks the c-th of S equal segments of the band;
+// the 128 x KB partial tiles meet in distributed shared memory, where CTA 0 adds them in rank
+// order (deterministic) and stores the result.  Without the split a 32-row-block problem keeps
+// 32 of the 148 SMs busy and its run time is the length of one band walk.
+template <int KT, int KB, int RPT, int WN>
+__global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN)
+    matmul_fma_cluster_kernel(const MatmulArgs<float> a) {
+    constexpr int WM = 128 / (32 * RPT);
+    constexpr int THREADS = 32 * WM * WN;
+    extern __shared__ __align__(16) float smem[];
+    constexpr int WALK_FLOATS = (2 * (TILE_N * KB + TILE_N) > WN * 128 * KB) ? 2 * (TILE_N * KB + TILE_N) : WN * 128 * KB;
+    float *tile = smem + WALK_FLOATS;  // this CTA's partial tile (128 x KB), read by CTA 0 of the cluster
+
+    cg::cluster_group cluster = cg::this_cluster();
+    const int S = (int)cluster.num_blocks();
+    const int c = (int)cluster.block_rank();
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31;
+    const int warp = tid >> 5;
+    const int wm = warp % WM;
+    const int wn = warp / WM;
+
+    int64_t item = blockIdx.x / S;
+    const int64_t b = item % a.batch.count;
+    item /= a.batch.count;
+    const int64_t r = a.rb_begin + item % a.row_blocks;
+    const int kb = (int)(item / a.row_blocks);
+    const int64_t k0 = (int64_t)kb * KB;
+
+    const BatchIndex bi = decompose(a.batch, b);
+    const float *x1 = batch_ptr(a.x1, bi);
+    const float *x2 = batch_ptr(a.x2, bi);
+    const float *rhs = batch_ptr(a.rhs, bi);
+    float *out = batch_ptr(a.out, bi);
+    KernelFn<KT> fn;
+    fn.init(batch_ptr(a.params, bi), a.params.s0);
+
+    const int n = (int)a.n;
+    const int band_lo = clamp_int(batch_ptr(a.start, bi)[r * a.start.s0], 0, n);
+    const int band_hi = max(band_lo, min(batch_ptr(a.end, bi)[r * a.end.s0], n));
+    // this CTA's segment (multiples of 4 columns keep the 16-byte copies of rhs rows aligned)
+    const int seg = (((band_hi - band_lo + S - 1) / S) + 3) & ~3;
+    const int seg_lo = min(band_hi, band_lo + c * seg);
+    const int seg_hi = min(band_hi, seg_lo + seg);
+
+    float x1r[RPT];
+    const int64_t row_base = r * KM_BLOCK_SIZE + wm * (32 * RPT) + lane;
+#pragma unroll
+    for (int i = 0; i < RPT; i++) {
+        const int64_t row = row_base + 32 * i;
+        x1r[i] = row < a.m ? x1[row * a.x1.s0] : 0.0f;
+    }
+    constexpr bool PACKED = (KB % 2 == 0);
+    constexpr int KB2 = PACKED ? KB / 2 : 1;
+    float acc[RPT][KB];
+    f32x2 acc2[RPT][KB2];
+#pragma unroll
+    for (int i = 0; i < RPT; i++) {
+#pragma unroll
+        for (int q = 0; q < KB; q++) acc[i][q] = 0.0f;
+#pragma unroll
+        for (int q = 0; q < KB2; q++) acc2[i][q] = 0ull;
+    }
+    const bool vec = (KB % 4 == 0) && a.rhs_vec_ok && (k0 + KB <= a.k);
+    band_walk<KT, KB, RPT, WN, false>(a, fn, x2, rhs, x1r, seg_lo, seg_hi, k0, vec, smem, tid, wn, 1.0f, acc, acc2);
+    if constexpr (PACKED) {
+#pragma unroll
+        for (int i = 0; i < RPT; i++)
+#pragma unroll
+            for (int q = 0; q < KB2; q++) unpack2(acc2[i][q], acc[i][2 * q], acc[i][2 * q + 1]);
+    }
+
+    // CTA partial: combine the WN column-interleaved sums through shared memory
+    float *red = smem;  // red[wn][row_local][KB]
+#pragma unroll
+    for (int i = 0; i < RPT; i++) {
+        const int row_local = wm * (32 * RPT) + lane + 32 * i;
+#pragma unroll
+        for (int q = 0; q < KB; q++) red[(wn * 128 + row_local) * KB + q] = acc[i][q];
+    }
+    __syncthreads();
+    for (int q = tid; q < 128 * KB; q += THREADS) {
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < WN; w++) v += red[w * 128 * KB + q];
+        tile[q] = v;
+    }
+    cluster.sync();  // every CTA's tile is complete and visible to the cluster
+    if (c == 0) {
+        const float scale = fn.scale;
+        for (int q = tid; q < 128 * KB; q += THREADS) {
+            const int row_local = q / KB, col = q % KB;
+            const int64_t row = r * KM_BLOCK_SIZE + row_local;
+            if (row < a.m && k0 + col < a.k) {
+                float v = 0.0f;
+                for (int peer = 0; peer < S; peer++) v += cluster.map_shared_rank(tile, peer)[q];
+                out[(row - a.rb_begin * KM_BLOCK_SIZE) * a.out.s0 + (k0 + col) * a.out.s1] = v * scale;
+            }
+        }
+    }
+    cluster.sync();  // no CTA leaves while its tile may still be read
+}
+
 constexpr int SUM_MAX_SHARED = 1024;  // components whose (frequency, scale) fit the shared table
 
 // Band walk for a SUM of spectral components that share inputs, band and lengthscale:
@@ -404,6 +513,35 @@ static int launch_matmul(const MatmulArgs<float> &a, cudaStream_t stream) {
     if (items > 0x7fffffffLL) {
         set_error("km_matmul_f32: too many work items (%lld)", (long long)items);
         return KM_ERR_UNSUPPORTED;
+    }
+    if constexpr (!SUM && WN > 1) {
+        // small problems: split every band over a cluster of S CTAs (S a power of two, <= 8)
+        int split = 1;
+        while (split < 8 && items * split * 2 <= 148) split *= 2;  // 148 SMs
+        if (split > 1) {
+            auto ckernel = matmul_fma_cluster_kernel<KT, KB, RPT, WN>;
+            // walk stages / reduction buffer, then this CTA's partial tile
+            constexpr size_t csmem = (stage_bytes > red_bytes ? stage_bytes : red_bytes) + 128 * KB * sizeof(float);
+            if (csmem > 48 * 1024) {
+                cudaError_t err = cudaFuncSetAttribute(ckernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)csmem);
+                if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(matmul cluster)");
+            }
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3((unsigned)(items * split));
+            cfg.blockDim = dim3(THREADS);
+            cfg.dynamicSmemBytes = csmem;
+            cfg.stream = stream;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = (unsigned)split;
+            attr[0].val.clusterDim.y = 1;
+            attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            cudaError_t err = cudaLaunchKernelEx(&cfg, ckernel, a);
+            if (err != cudaSuccess) return cuda_fail(err, "km_matmul_f32 cluster launch");
+            return KM_OK;
+        }
     }
     kernel<<<(unsigned)items, THREADS, smem, stream>>>(a);
     KM_CHECK_LAUNCH("km_matmul_f32 launch");
