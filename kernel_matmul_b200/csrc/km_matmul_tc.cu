@@ -431,25 +431,32 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             // the 16 band columns: [8 hi pairs | 8 lo pairs].
 #pragma unroll
             for (int half = g; half < TC_BK / 16; half += G) {  // this group's 16-column steps
-                float kv[16];
+                float kv[16], lo[16];
+                // packed f32x2 arithmetic: two entries per FP32 instruction
+                {
+                    const ulonglong2 *xs2 = reinterpret_cast<const ulonglong2 *>(xs);
+                    const f32x2 x1v2 = splat2(x1v);
+                    f32x2 kv2[8];
 #pragma unroll
-                for (int h = 0; h < 4; h++) {
-                    const float4 xv = xs[half * 4 + h];
-                    kv[4 * h + 0] = fn.unscaled(x1v - xv.x);
-                    kv[4 * h + 1] = fn.unscaled(x1v - xv.y);
-                    kv[4 * h + 2] = fn.unscaled(x1v - xv.z);
-                    kv[4 * h + 3] = fn.unscaled(x1v - xv.w);
+                    for (int h = 0; h < 4; h++) {
+                        const ulonglong2 xv = xs2[half * 4 + h];
+                        kv2[2 * h] = fn.unscaled2(sub2(x1v2, xv.x));
+                        kv2[2 * h + 1] = fn.unscaled2(sub2(x1v2, xv.y));
+                    }
+#pragma unroll
+                    for (int u = 0; u < 8; u++) {
+                        unpack2(kv2[u], kv[2 * u], kv[2 * u + 1]);
+                        const f32x2 l2 = sub2(kv2[u], kv2[u] & 0xffffe000ffffe000ull);
+                        unpack2(l2, lo[2 * u], lo[2 * u + 1]);
+                    }
                 }
                 if (partial) {
 #pragma unroll
                     for (int u = 0; u < 16; u++) {
                         const int j = j0 + half * 16 + u;
-                        if (j < band_lo || j >= band_hi) kv[u] = 0.0f;
+                        if (j < band_lo || j >= band_hi) kv[u] = lo[u] = 0.0f;
                     }
                 }
-                float lo[16];
-#pragma unroll
-                for (int u = 0; u < 16; u++) lo[u] = kv[u] - tf32_hi(kv[u]);
                 split_store16(tmem_lane + (uint32_t)(s * TC_A_COLS + half * 16), kv, lo);
             }
             tmem_st_wait();
