@@ -45,11 +45,25 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, unsigned bytes) {
 __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-// Bounded wait for the phase with the given parity.  false = gave up.  (try_wait suspends the
-// thread for a short, system-defined time; an explicit suspend-time hint was tried and only
-// added instructions.)
+// Bounded wait for the phase with the given parity.  false = gave up.  A non-blocking test comes
+// first (the phase is usually complete already); then try_wait, which suspends the thread for a
+// short, system-defined time per poll (an explicit suspend-time hint only added instructions).
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
     const uint32_t addr = smem_u32(bar);
+    {
+        // the phase is usually complete already: a non-blocking test first
+        uint32_t done;
+        asm volatile(
+            "{\n\t"
+            ".reg .pred p;\n\t"
+            "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t"
+            "}"
+            : "=r"(done)
+            : "r"(addr), "r"(parity)
+            : "memory");
+        if (done) return true;
+    }
     for (unsigned poll = 0; poll < TC_WAIT_POLLS; poll++) {
         uint32_t done;
         asm volatile(
