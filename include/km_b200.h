@@ -106,6 +106,15 @@ KM_API int km_matmul_tc_f32(int kernel_type, const km_batch *batch, int64_t m, i
                             const km_view *out, void *workspace, size_t workspace_bytes,
                             void *stream);
 
+/* The tensor-core product restricted to a window of row blocks (as km_matmul_rows_f32 without
+ * the batch sum): how a single-kernel product is sharded by rows over GPUs. */
+KM_API int km_matmul_tc_rows_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
+                                 int64_t k, const km_view *x1, const km_view *x2,
+                                 const km_view *rhs, const km_view *params, const km_view *start,
+                                 const km_view *end, const km_view *out, int64_t row_block_begin,
+                                 int64_t row_block_count, void *workspace, size_t workspace_bytes,
+                                 void *stream);
+
 KM_API int km_workspace_status(const void *workspace, int32_t *status_out, void *stream);
 
 /* ---------------------------------------------------------------------------------------

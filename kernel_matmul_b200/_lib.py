@@ -57,6 +57,8 @@ def _load() -> ctypes.CDLL:
     lib.km_matmul_tc_workspace_bytes.argtypes = [bp, i64, i64, wp]
     lib.km_matmul_tc_f32.restype = ctypes.c_int
     lib.km_matmul_tc_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, vp, sz, vp]
+    lib.km_matmul_tc_rows_f32.restype = ctypes.c_int
+    lib.km_matmul_tc_rows_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, i64, i64, vp, sz, vp]
     lib.km_workspace_status.restype = ctypes.c_int
     lib.km_workspace_status.argtypes = [vp, ctypes.POINTER(ctypes.c_int32), vp]
     lib.km_grad_workspace_bytes.restype = sz
@@ -104,7 +106,7 @@ def _load() -> ctypes.CDLL:
 lib = _load()
 
 EXPORTED = [
-    "km_last_error", "km_version", "km_num_params", "km_matmul_f32", "km_matmul_rows_f32", "km_matmul_tc_workspace_bytes", "km_matmul_tc_f32",
+    "km_last_error", "km_version", "km_num_params", "km_matmul_f32", "km_matmul_rows_f32", "km_matmul_tc_workspace_bytes", "km_matmul_tc_f32", "km_matmul_tc_rows_f32",
     "km_workspace_status", "km_grad_workspace_bytes", "km_grad_tc_workspace_bytes", "km_bilinear_derivative_tc_f32",
     "km_matmul_bwd_tc_f32",
     "km_bilinear_derivative_f32", "km_bilinear_derivative_static_f32", "km_matmul_bwd_f32", "km_dense_f32", "km_dense_bwd_f32",

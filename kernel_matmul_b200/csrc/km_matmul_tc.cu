@@ -589,12 +589,11 @@ extern "C" size_t km_matmul_tc_workspace_bytes(const km_batch *batch, int64_t n,
     return tc_workspace_bytes(b, n, k, make_view<const float>(rhs, b));
 }
 
-extern "C" int km_matmul_tc_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
-                                const km_view *x1, const km_view *x2, const km_view *rhs, const km_view *params,
-                                const km_view *start, const km_view *end, const km_view *out, void *workspace,
-                                size_t workspace_bytes, void *stream) {
+static int km_matmul_tc_entry(const char *name, int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
+                              const km_view *x1, const km_view *x2, const km_view *rhs, const km_view *params,
+                              const km_view *start, const km_view *end, const km_view *out, int64_t rb_begin,
+                              int64_t rb_count, void *workspace, size_t workspace_bytes, void *stream) {
     using namespace km;
-    const char *name = "km_matmul_tc_f32";
     KM_REQUIRE(valid_kernel_type(kernel_type), KM_ERR_INVALID_ARGUMENT, "%s: unknown kernel type %d", name, kernel_type);
     KM_REQUIRE(batch && x1 && x2 && rhs && params && start && end && out, KM_ERR_INVALID_ARGUMENT, "%s: null argument", name);
     KM_REQUIRE(m >= 0 && n >= 0 && k >= 0 && n <= 0x7fffffffLL - 64 && m <= 0x7fffffffLL * 64, KM_ERR_INVALID_ARGUMENT,
@@ -602,7 +601,12 @@ extern "C" int km_matmul_tc_f32(int kernel_type, const km_batch *batch, int64_t 
     TcArgs a;
     int rc = make_batch(batch, &a.batch);
     if (rc != KM_OK) return rc;
-    if (a.batch.count == 0 || m == 0 || k == 0) return KM_OK;
+    const int64_t total_blocks = ceil_div(m, KM_BLOCK_SIZE);
+    if (rb_count < 0) rb_count = total_blocks - rb_begin;
+    KM_REQUIRE(rb_begin >= 0 && rb_count >= 0 && rb_begin + rb_count <= total_blocks, KM_ERR_INVALID_ARGUMENT,
+               "%s: row-block window [%lld, %lld) outside [0, %lld)", name, (long long)rb_begin,
+               (long long)(rb_begin + rb_count), (long long)total_blocks);
+    if (a.batch.count == 0 || rb_count == 0 || k == 0) return KM_OK;
     KM_REQUIRE(x1->data && out->data && params->data && start->data && end->data, KM_ERR_INVALID_ARGUMENT,
                "%s: null data pointer", name);
     KM_REQUIRE(n == 0 || (x2->data && rhs->data), KM_ERR_INVALID_ARGUMENT, "%s: null data pointer", name);
@@ -613,8 +617,8 @@ extern "C" int km_matmul_tc_f32(int kernel_type, const km_batch *batch, int64_t 
     a.m = m;
     a.n = n;
     a.k = k;
-    a.row_blocks = ceil_div(m, KM_BLOCK_SIZE);
-    a.rb_begin = 0;
+    a.row_blocks = rb_count;
+    a.rb_begin = rb_begin;
     a.x1 = make_view<const float>(x1, a.batch);
     a.x2 = make_view<const float>(x2, a.batch);
     a.params = make_view<const float>(params, a.batch);
@@ -622,6 +626,23 @@ extern "C" int km_matmul_tc_f32(int kernel_type, const km_batch *batch, int64_t 
     a.end = make_view<const int>(end, a.batch);
     a.out = make_view<float>(out, a.batch);
     return tc_matmul(kernel_type, a, make_view<const float>(rhs, a.batch), workspace, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int km_matmul_tc_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
+                                const km_view *x1, const km_view *x2, const km_view *rhs, const km_view *params,
+                                const km_view *start, const km_view *end, const km_view *out, void *workspace,
+                                size_t workspace_bytes, void *stream) {
+    return km_matmul_tc_entry("km_matmul_tc_f32", kernel_type, batch, m, n, k, x1, x2, rhs, params, start, end, out, 0, -1,
+                              workspace, workspace_bytes, stream);
+}
+
+extern "C" int km_matmul_tc_rows_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
+                                     const km_view *x1, const km_view *x2, const km_view *rhs, const km_view *params,
+                                     const km_view *start, const km_view *end, const km_view *out,
+                                     int64_t row_block_begin, int64_t row_block_count, void *workspace,
+                                     size_t workspace_bytes, void *stream) {
+    return km_matmul_tc_entry("km_matmul_tc_rows_f32", kernel_type, batch, m, n, k, x1, x2, rhs, params, start, end, out,
+                              row_block_begin, row_block_count, workspace, workspace_bytes, stream);
 }
 
 extern "C" int km_workspace_status(const void *workspace, int32_t *status_out, void *stream) {

@@ -199,13 +199,14 @@ def tc_status(out: Tensor) -> int:
 
 def matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor, start: Tensor, end: Tensor,
                 *, row_block_begin: int = 0, row_block_count: int | None = None, sum_batches: bool = False,
-                out: Tensor | None = None) -> Tensor:
+                out: Tensor | None = None, path: str = "auto") -> Tensor:
     """``matmul`` restricted to the row blocks ``[row_block_begin, row_block_begin + row_block_count)``
     and, with ``sum_batches``, summed over all batch dims inside the kernel.
 
     Returns ``(*batch, rows, k)`` or, with ``sum_batches``, ``(rows, k)``, where ``rows`` is the
     number of rows of ``x1`` inside the window.  ``out`` may be passed to receive the result
-    (e.g. a rank's slice of an all-gather buffer).
+    (e.g. a rank's slice of an all-gather buffer).  ``path`` as in ``matmul`` (the batch sum runs
+    on the FMA pipe).
     """
     kid, dev, batch, m, n, (x1e, x2e, pe, se, ee, re) = _prep(kernel_type, x1, x2, params, start, end, [(rhs, 2)])
     if rhs.shape[-2] != n:
@@ -225,6 +226,22 @@ def matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: T
     if sum_batches and len(batch) == 0:
         sum_batches = False  # a single kernel: nothing to sum
     oute = out.reshape(-1, rows, k) if (len(batch) > KM_MAX_BATCH_DIMS and not sum_batches) else out
+    if path not in ("auto", "fma", "tc"):
+        raise ValueError(f"unknown path {path!r}")
+    if sum_batches and path == "tc":
+        raise RuntimeError("the batch sum runs on the FMA pipe only")
+    if not sum_batches and rows > 0 and (path == "tc" or (path == "auto" and k >= TENSOR_CORE_MIN_K and
+                                                          _enough_items(batch, row_block_count * BLOCK_SIZE))):
+        kb = _km_batch(batch)
+        rv = _view(re, 2)
+        ws_bytes = lib.km_matmul_tc_workspace_bytes(kb, n, k, rv)
+        ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
+        with torch.cuda.device(dev):
+            check(lib.km_matmul_tc_rows_f32(
+                kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), rv, _view(pe, 1), _view(se, 1), _view(ee, 1),
+                _view(oute, 2), row_block_begin, row_block_count, ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
+        out._km_workspace = ws
+        return out
     with torch.cuda.device(dev):
         check(lib.km_matmul_rows_f32(
             kid, _km_batch(batch), m, n, k, _view(x1e, 1), _view(x2e, 1), _view(re, 2), _view(pe, 1),

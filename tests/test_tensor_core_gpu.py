@@ -220,3 +220,26 @@ def test_auto_path_selection_for_narrow_operands():
     ss, es = O.make_ranges(2.0, x[:300])
     small = ops.matmul("spectral", xs, xs, torch.randn(300, 16).cuda(), pd[0], ss.cuda(), es.cuda())
     assert not hasattr(small, "_km_workspace")
+
+
+@pytest.mark.parametrize("k", [13, 40])
+def test_tc_product_row_window(k):
+    """km_matmul_tc_rows_f32: a window of row blocks equals the rows of the full product."""
+    from kernel_matmul_b200 import ops
+    from oracle import oracle as O
+
+    B, n = 3, 1500
+    x = torch.sort(torch.rand(n) * 20)[0]
+    params = make_params("spectral", (B,))
+    start, end = O.make_ranges(2.0, x)
+    rhs = torch.randn(B, n, k)
+    ref = O.matmul("spectral", x.expand(B, n), x.expand(B, n), rhs, params, start.expand(B, -1), end.expand(B, -1))
+    d = lambda t: t.cuda()  # noqa: E731
+    args = ("spectral", d(x).expand(B, n), d(x).expand(B, n), d(rhs), d(params), d(start).expand(B, -1), d(end).expand(B, -1))
+    out = ops.matmul_rows(*args, row_block_begin=3, row_block_count=4, path="tc")
+    assert ops.tc_status(out) == 0 and out.shape == (B, 512, k)
+    assert rel_err(out, ref[:, 384:896]) <= 1e-5
+    tail = ops.matmul_rows(*args, row_block_begin=10, path="tc")  # ragged last block
+    assert rel_err(tail, ref[:, 1280:]) <= 1e-5
+    full = ops.matmul(*args, path="tc")
+    assert torch.equal(out, full[:, 384:896])
