@@ -13,7 +13,7 @@
 // around it (reference: native/matmul/matmul.cu:13-203).
 #include <cooperative_groups.h>
 
-#include "km_common.cuh"
+#include "km_tcgen05.cuh"
 
 namespace km {
 
@@ -32,6 +32,7 @@ struct MatmulArgs {
     int rhs_vec_ok;  // rhs rows may be copied 16 bytes at a time
     int out_vec_ok;  // out rows may be stored 16 bytes at a time
     int sum_shared_ok;  // batch sum: x1, x2, rhs, start, end are one copy shared by all batches
+    int sum_tc_launched;  // batch sum: the tensor-core kernel runs next to this one and takes the shared-lengthscale case
 };
 
 // Walks the band [band_lo, band_hi) of one row block and one batch and adds
@@ -453,6 +454,7 @@ __global__ void __launch_bounds__(32 * (128 / (32 * RPT)) * WN, 384 / (32 * (128
                 comp[b] = make_float2(2.0f * KM_PI_F * th[a.params.s0], th[2 * a.params.s0]);
             }
             shared_envelope = __syncthreads_and(same) != 0;
+            if (shared_envelope && a.sum_tc_launched) return;  // km_matmul_sum_tc.cu computes this case
             if (shared_envelope) {
                 const int band_lo = clamp_int(a.start.data[r * a.start.s0], 0, n);
                 const int band_hi = max(band_lo, min(a.end.data[r * a.end.s0], n));
@@ -600,10 +602,34 @@ static int matmul_entry(const char *name, int kernel_type, const km_batch *batch
     a.rhs_vec_ok = rows_vectorizable(a.rhs, a.batch) ? 1 : 0;
     a.out_vec_ok = 0;
     a.sum_shared_ok = 1;
+    a.sum_tc_launched = 0;
     for (int d = 0; d < a.batch.ndim; d++)
         if (a.batch.size[d] > 1 && (a.x1.bs[d] || a.x2.bs[d] || a.rhs.bs[d] || a.start.bs[d] || a.end.bs[d])) a.sum_shared_ok = 0;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (sum_batches) {
+        // Spectral components sharing everything but frequency and scale: the tensor-core kernel
+        // takes the case of one common lengthscale (checked on the device by every CTA of both
+        // kernels, so that exactly one of the two does the work).
+        if (kernel_type == KM_KERNEL_SPECTRAL && a.sum_shared_ok && a.batch.count >= 2 &&
+            a.batch.count <= SUM_TC_MAX_COMPONENTS && k <= SUM_TC_MAX_K) {
+            SumTcArgs t;
+            t.batch = a.batch;
+            t.m = m;
+            t.n = n;
+            t.k = k;
+            t.row_blocks = rb_count;
+            t.rb_begin = rb_begin;
+            t.x1 = a.x1;
+            t.x2 = a.x2;
+            t.rhs = a.rhs;
+            t.params = a.params;
+            t.start = a.start;
+            t.end = a.end;
+            t.out = a.out;
+            const int rc = launch_matmul_sum_tc(t, s);
+            if (rc != KM_OK) return rc;
+            a.sum_tc_launched = 1;
+        }
         switch (kernel_type) {
         case KM_KERNEL_RBF: return dispatch_matmul<KM_KERNEL_RBF, true>(a, s);
         case KM_KERNEL_SPECTRAL: return dispatch_matmul<KM_KERNEL_SPECTRAL, true>(a, s);

@@ -1,0 +1,332 @@
+// Batch sum of spectral components on the tensor cores:
+//
+//   out[i, :] = sum_{j in band} ( sum_b s_b exp(-tau^2 / 2 l^2) cos(w_b tau) ) rhs[j, :],   tau = x_i - x_j
+//
+// for B <= 64 components that share inputs, band, right-hand side and lengthscale (the
+// reference's SumKernel over a batch of spectral kernels, kernel_matmul/gpytorch/sum.py:16-24).
+// The FMA-pipe kernel (km_matmul.cu) evaluates one SFU cosine per entry and component.  Here the
+// sum over the components is turned into a dot product the tensor core can do:
+//
+//   cos(w (a_i - a_j)) = cos(w a_i) cos(w a_j) + sin(w a_i) sin(w a_j),   a = x - x0
+//   sum_b s_b cos(w_b tau) = < phi(a_i), psi(a_j) >,
+//   phi(a) = (s_b cos(w_b a), s_b sin(w_b a))_b,   psi(a) = (cos(w_b a), sin(w_b a))_b   in R^(2B)
+//
+// with x0 the centre of the CTA's row block, so that |a| stays as small as |tau| and the phases
+// keep their fp32 accuracy.  Per 128-row block and tile of 64 band columns:
+//   * phi of the 128 rows is computed once, split into fp16 hi / lo and written to tensor
+//     memory (A operand, as in km_matmul_tc.cu);
+//   * psi of the 64 columns (2B SFU operations per column) is written to shared memory as the B
+//     operand, hi / lo fp16 in the K-major core-matrix layout;
+//   * a control warp issues tcgen05.mma kind::f16 (N = 64, K = 16; 3 per 16 values of 2B) into
+//     one of two tensor-memory stages: C[128 x 64] = sum_b s_b cos(w_b tau);
+//   * the row threads read C with tcgen05.ld, multiply by the envelope exp(-tau^2 / 2 l^2) (one
+//     SFU operation per entry) and contract with the rhs tile (k <= 16 columns, FMA pipe).
+// SFU work per entry: 1 + 2B / 128 (psi is shared by the 128 rows) instead of B + 1.
+//
+// No workspace: a CTA whose bounded wait gives up writes NaN into its output rows.
+#include "km_tcgen05.cuh"
+
+namespace km {
+
+constexpr int ST_COLS = 64;       // band columns per tile = GEMM N
+constexpr int ST_IN_STAGES = 4;   // x2 / rhs tiles in shared memory
+constexpr int ST_TMEM_COLS = 256; // A (2 * 64) + two C stages of 64
+constexpr int ST_C_COL = 128;     // first C column
+
+// KB: rhs columns held per thread (8 or 16).
+template <int KB>
+__global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a) {
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bar_in[ST_IN_STAGES];  // x2 + rhs tile landed
+    __shared__ __align__(8) uint64_t bar_bready[2];         // psi tile written
+    __shared__ __align__(8) uint64_t bar_cfull[2];          // C tile complete (tcgen05.commit)
+    __shared__ __align__(8) uint64_t bar_cfree[2];          // C tile consumed
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int fail_flag;
+    __shared__ float w_tab[SUM_TC_MAX_COMPONENTS], s_tab[SUM_TC_MAX_COMPONENTS];
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const bool is_ctl_warp = warp == 4;
+    const int B = (int)a.batch.count;
+    const int Bp = (B + 7) & ~7;  // components padded to whole MMA steps (K = 2 Bp)
+    const int ksteps = Bp / 8;
+
+    // every CTA checks that the components share one lengthscale; if not, the FMA-pipe kernel
+    // launched next to this one does the work and this CTA leaves at once
+    const float ell0 = a.params.data[0];
+    int same = 1;
+    for (int b = tid; b < SUM_TC_MAX_COMPONENTS; b += blockDim.x) {
+        float w = 0.0f, s = 0.0f;
+        if (b < B) {
+            const float *th = batch_ptr(a.params, decompose(a.batch, b));
+            same &= (th[0] == ell0) ? 1 : 0;
+            w = 2.0f * KM_PI_F * th[a.params.s0];
+            s = th[2 * a.params.s0];
+        }
+        w_tab[b] = w;
+        s_tab[b] = s;
+    }
+    if (tid == 0) fail_flag = 0;
+    if (!__syncthreads_and(same)) return;
+    const float c0 = -(0.5f / (ell0 * ell0)) * KM_LOG2E_F;
+
+    // shared memory: two psi stages [part: hi, lo][chunk = K / 8][j][8 halfs], then the input stages
+    const int b_part_bytes = (2 * Bp / 8) * ST_COLS * 16;
+    const int b_stage_bytes = 2 * b_part_bytes;
+    unsigned char *in_base = smem_raw + 2 * b_stage_bytes;
+    constexpr int IN_STAGE_FLOATS = ST_COLS + ST_COLS * KB;  // x2 values, then rhs rows
+    auto b_stage = [&](int st) { return smem_raw + st * b_stage_bytes; };
+    auto in_x2 = [&](int st) { return reinterpret_cast<float *>(in_base) + st * IN_STAGE_FLOATS; };
+    auto in_rhs = [&](int st) { return reinterpret_cast<float *>(in_base) + st * IN_STAGE_FLOATS + ST_COLS; };
+
+    const int64_t r = a.rb_begin + blockIdx.x;
+    const int n = (int)a.n;
+    const int band_lo = clamp_int(a.start.data[r * a.start.s0], 0, n);
+    const int band_hi = max(band_lo, min(a.end.data[r * a.end.s0], n));
+    const int tile_lo = band_lo / ST_COLS;
+    const int tiles = band_hi > band_lo ? (band_hi + ST_COLS - 1) / ST_COLS - tile_lo : 0;
+    const float *x2 = a.x2.data;
+    const float *rhs = a.rhs.data;
+    // origin of the phases: the middle row of the block
+    const float x0 = a.x1.data[min(r * KM_BLOCK_SIZE + KM_BLOCK_SIZE / 2, a.m - 1) * a.x1.s0];
+
+    if (tid == 0) {
+#pragma unroll
+        for (int s = 0; s < ST_IN_STAGES; s++) mbar_init(&bar_in[s], 32);  // one cp.async arrival per lane
+#pragma unroll
+        for (int s = 0; s < 2; s++) {
+            mbar_init(&bar_bready[s], 4);
+            mbar_init(&bar_cfull[s], 1);
+            mbar_init(&bar_cfree[s], 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (is_ctl_warp) tmem_alloc(&tmem_base_slot, ST_TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    bool failed = false;
+
+    float acc[KB];
+#pragma unroll
+    for (int c = 0; c < KB; c++) acc[c] = 0.0f;
+
+    if (is_ctl_warp) {
+        // ------------------------------------------------ input fetches (all lanes) + MMA issue (lane 0)
+        auto fetch = [&](int t) {
+            const int st = t % ST_IN_STAGES;
+            const int64_t j0 = (int64_t)(tile_lo + t) * ST_COLS;
+            float *xs = in_x2(st);
+            float *rs = in_rhs(st);
+#pragma unroll
+            for (int u = 0; u < ST_COLS / 32; u++) {
+                const int jj = lane + 32 * u;
+                const bool valid = j0 + jj < n;
+                cp_async4_zfill(xs + jj, x2 + (valid ? j0 + jj : 0) * a.x2.s0, valid);
+            }
+            for (int q = lane; q < ST_COLS * KB; q += 32) {
+                const int jj = q / KB, c = q % KB;
+                const bool valid = j0 + jj < n && c < a.k;
+                cp_async4_zfill(rs + q, rhs + (valid ? (j0 + jj) * a.rhs.s0 + c * a.rhs.s1 : 0), valid);
+            }
+            cp_async_mbar_arrive(&bar_in[st]);
+        };
+        for (int t = 0; t < min(tiles, ST_IN_STAGES); t++) fetch(t);
+
+        // D fp32, A / B fp16, K-major, M = 128, N = 64
+        constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(ST_COLS >> 3) << 17) | ((128u >> 4) << 24);
+        constexpr uint32_t lbo_b = ST_COLS * 16, sbo = 128;
+        constexpr uint64_t kstep_b = (uint64_t)(2 * lbo_b) >> 4;  // 16 K values = 2 chunks
+        const uint64_t part_step = (uint64_t)b_part_bytes >> 4;
+        const uint64_t stage_step = (uint64_t)b_stage_bytes >> 4;
+        const uint64_t d_b0 = smem_desc(smem_u32(b_stage(0)), lbo_b, sbo);
+        for (int t = 0; t < tiles; t++) {
+            const int st = t & 1;
+            bool ok = true;
+            if (t >= 2) {
+                // C stage free = tile t - 2 consumed, which also frees its input stage
+                ok = mbar_wait(&bar_cfree[st], (unsigned)(((t >> 1) - 1) & 1));
+                if (__all_sync(0xffffffffu, ok) && t + 2 < tiles) fetch(t + 2);
+            }
+            if (ok) ok = mbar_wait(&bar_bready[st], (unsigned)((t >> 1) & 1));
+            if (!__all_sync(0xffffffffu, ok)) {
+                failed = true;
+                break;
+            }
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t d_tmem = tmem_base + (uint32_t)(ST_C_COL + st * ST_COLS);
+                const uint64_t b_hi = d_b0 + st * stage_step, b_lo = b_hi + part_step;
+                for (int ks = 0; ks < ksteps; ks++) {
+                    const uint32_t a_hi = tmem_base + (uint32_t)(16 * ks), a_lo = a_hi + 8;
+                    mma_f16_ts(d_tmem, a_hi, b_lo + ks * kstep_b, idesc, ks > 0 ? 1u : 0u);
+                    mma_f16_ts(d_tmem, a_lo, b_hi + ks * kstep_b, idesc, 1u);
+                }
+                for (int ks = 0; ks < ksteps; ks++)
+                    mma_f16_ts(d_tmem, tmem_base + (uint32_t)(16 * ks), b_hi + ks * kstep_b, idesc, 1u);
+                mma_commit(&bar_cfull[st]);
+            }
+            __syncwarp();
+        }
+        if (failed && lane == 0) atomicExch(&fail_flag, 1);
+        cp_async_wait<0>();  // no copy may be in flight when the CTA exits
+        __syncwarp();
+    } else {
+        // ------------------------------------------------------------------------ row threads
+        const int64_t row = r * KM_BLOCK_SIZE + tid;
+        const float x1v = row < a.m ? a.x1.data[row * a.x1.s0] : x0;
+        const uint32_t tmem_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
+
+        // phi of this row -> tensor memory: per 8 components [8 hi pairs | 8 lo pairs]
+        {
+            const float ai = x1v - x0;
+            for (int ks = 0; ks < ksteps; ks++) {
+                float v[16], lo[16];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    const float ph = w_tab[ks * 8 + u] * ai, sc = s_tab[ks * 8 + u];
+                    v[2 * u] = sc * cos_approx(ph);
+                    v[2 * u + 1] = sc * sin_approx(ph);
+                }
+#pragma unroll
+                for (int u = 0; u < 16; u++) lo[u] = v[u] - tf32_hi(v[u]);
+                split_store16(tmem_lane + (uint32_t)(16 * ks), v, lo);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+        }
+
+        // psi of the tile's columns -> shared memory (thread: column tid % 64, half of the components)
+        auto generate = [&](int t) {
+            const int st = t & 1;
+            const int jj = tid & 63;
+            const float aj = in_x2(t % ST_IN_STAGES)[jj] - x0;
+            unsigned char *hi = b_stage(st) + jj * 16;
+            unsigned char *lo = hi + b_part_bytes;
+            // 4 components = 8 K values = one 16-byte chunk
+            for (int kc = (tid >> 6) * (Bp / 8); kc < ((tid >> 6) + 1) * (Bp / 8); kc++) {
+                float v[8];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const float ph = w_tab[kc * 4 + u] * aj;
+                    v[2 * u] = cos_approx(ph);
+                    v[2 * u + 1] = sin_approx(ph);
+                }
+                uint32_t h[4], l[4];
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(h[u]) : "f"(v[2 * u + 1]), "f"(v[2 * u]));
+                    asm("cvt.rn.f16x2.f32 %0, %1, %2;"
+                        : "=r"(l[u])
+                        : "f"(v[2 * u + 1] - tf32_hi(v[2 * u + 1])), "f"(v[2 * u] - tf32_hi(v[2 * u])));
+                }
+                *reinterpret_cast<uint4 *>(hi + kc * (ST_COLS * 16)) = make_uint4(h[0], h[1], h[2], h[3]);
+                *reinterpret_cast<uint4 *>(lo + kc * (ST_COLS * 16)) = make_uint4(l[0], l[1], l[2], l[3]);
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_bready[st]);
+        };
+
+        if (tiles > 0) {
+            if (!mbar_wait_warp(&bar_in[0], 0u)) failed = true;
+            if (!failed) generate(0);
+        }
+        for (int t = 0; t < tiles && !failed; t++) {
+            const int st = t & 1;
+            if (t + 1 < tiles) {
+                // (the psi stage of tile t + 1 was read by the MMAs of tile t - 1, whose completion
+                // this thread has seen when it consumed tile t - 1)
+                if (!mbar_wait_warp(&bar_in[(t + 1) % ST_IN_STAGES], (unsigned)(((t + 1) / ST_IN_STAGES) & 1))) {
+                    failed = true;
+                    break;
+                }
+                generate(t + 1);
+            }
+            if (!mbar_wait_warp(&bar_cfull[st], (unsigned)((t >> 1) & 1))) {
+                failed = true;
+                break;
+            }
+            tc_fence_after();
+            const int j0 = (tile_lo + t) * ST_COLS;
+            const float *xs = in_x2(t % ST_IN_STAGES);
+            const float *rs = in_rhs(t % ST_IN_STAGES);
+            auto consume = [&](auto masked_tag) {
+                constexpr bool MASKED = decltype(masked_tag)::value;
+#pragma unroll
+                for (int p = 0; p < ST_COLS / 16; p++) {
+                    uint32_t cv[16];
+                    tmem_ld16_nowait(tmem_lane + (uint32_t)(ST_C_COL + st * ST_COLS + p * 16), cv);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int u = 0; u < 16; u++) {
+                        const int jj = p * 16 + u;
+                        const float tau = x1v - xs[jj];
+                        float v = __uint_as_float(cv[u]) * ex2_approx(c0 * tau * tau);
+                        if (MASKED) {
+                            if (j0 + jj < band_lo || j0 + jj >= band_hi) v = 0.0f;
+                        }
+#pragma unroll
+                        for (int c4 = 0; c4 < KB / 4; c4++) {
+                            const float4 rv = *reinterpret_cast<const float4 *>(rs + jj * KB + c4 * 4);
+                            acc[c4 * 4 + 0] = fmaf(v, rv.x, acc[c4 * 4 + 0]);
+                            acc[c4 * 4 + 1] = fmaf(v, rv.y, acc[c4 * 4 + 1]);
+                            acc[c4 * 4 + 2] = fmaf(v, rv.z, acc[c4 * 4 + 2]);
+                            acc[c4 * 4 + 3] = fmaf(v, rv.w, acc[c4 * 4 + 3]);
+                        }
+                    }
+                }
+            };
+            if (j0 < band_lo || j0 + ST_COLS > band_hi)
+                consume(std::true_type{});
+            else
+                consume(std::false_type{});
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bar_cfree[st]);
+        }
+        if (failed) atomicExch(&fail_flag, 1);
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (!is_ctl_warp) {
+        const int64_t row = r * KM_BLOCK_SIZE + tid;
+        if (row < a.m) {
+            const bool bad = fail_flag != 0;
+            float *orow = a.out.data + (row - a.rb_begin * KM_BLOCK_SIZE) * a.out.s0;
+#pragma unroll
+            for (int c = 0; c < KB; c++)
+                if (c < a.k) orow[c * a.out.s1] = bad ? __int_as_float(0x7fc00000) : acc[c];
+        }
+    }
+    if (is_ctl_warp) tmem_free(tmem_base, ST_TMEM_COLS);
+}
+
+template <int KB>
+static int launch_sum_tc_kb(const SumTcArgs &a, cudaStream_t stream) {
+    const int Bp = ((int)a.batch.count + 7) & ~7;
+    const size_t b_stage = (size_t)2 * (2 * Bp / 8) * ST_COLS * 16;
+    size_t smem = 2 * b_stage + (size_t)ST_IN_STAGES * (ST_COLS + ST_COLS * KB) * sizeof(float);
+    // two CTAs of 256 tensor-memory columns fill an SM: keep a third from being scheduled
+    smem = std::max<size_t>(smem, 80 * 1024);
+    auto kernel = matmul_sum_tc_kernel<KB>;
+    cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(matmul_sum_tc)");
+    kernel<<<(unsigned)a.row_blocks, 160, smem, stream>>>(a);
+    KM_CHECK_LAUNCH("km_matmul_rows_f32 (tensor-core batch sum) launch");
+    return KM_OK;
+}
+
+int launch_matmul_sum_tc(const SumTcArgs &a, cudaStream_t stream) {
+    if (a.row_blocks > 0x7fffffffLL) {
+        set_error("km_matmul_rows_f32: too many row blocks (%lld)", (long long)a.row_blocks);
+        return KM_ERR_UNSUPPORTED;
+    }
+    return a.k <= 8 ? launch_sum_tc_kb<8>(a, stream) : launch_sum_tc_kb<16>(a, stream);
+}
+
+}  // namespace km

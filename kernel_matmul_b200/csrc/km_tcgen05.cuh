@@ -171,4 +171,65 @@ __device__ __forceinline__ void cp_async_mbar_arrive(uint64_t *bar) {
     asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// D (fp32, tensor memory) (+)= A (tensor memory, fp16: row i in lane i, two K values per 32-bit
+// column) . B (smem, fp16); M = 128, N from idesc, K = 16.
+__device__ __forceinline__ void mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}"
+        :
+        : "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+// 16 values and their lo parts -> fp16 pairs [8 hi (truncated) | 8 lo (rounded)] -> 16 consecutive
+// tensor-memory columns of this thread's lane.  One asm block, so that the conversions write
+// straight into the consecutive registers tcgen05.st needs (no register moves in between).
+__device__ __forceinline__ void split_store16(uint32_t taddr, const float (&v)[16], const float (&lo)[16]) {
+    asm volatile(
+        "{\n\t"
+        ".reg .b32 p<16>;\n\t"
+        "cvt.rz.f16x2.f32 p0, %2, %1;\n\t"
+        "cvt.rz.f16x2.f32 p1, %4, %3;\n\t"
+        "cvt.rz.f16x2.f32 p2, %6, %5;\n\t"
+        "cvt.rz.f16x2.f32 p3, %8, %7;\n\t"
+        "cvt.rz.f16x2.f32 p4, %10, %9;\n\t"
+        "cvt.rz.f16x2.f32 p5, %12, %11;\n\t"
+        "cvt.rz.f16x2.f32 p6, %14, %13;\n\t"
+        "cvt.rz.f16x2.f32 p7, %16, %15;\n\t"
+        "cvt.rn.f16x2.f32 p8, %18, %17;\n\t"
+        "cvt.rn.f16x2.f32 p9, %20, %19;\n\t"
+        "cvt.rn.f16x2.f32 p10, %22, %21;\n\t"
+        "cvt.rn.f16x2.f32 p11, %24, %23;\n\t"
+        "cvt.rn.f16x2.f32 p12, %26, %25;\n\t"
+        "cvt.rn.f16x2.f32 p13, %28, %27;\n\t"
+        "cvt.rn.f16x2.f32 p14, %30, %29;\n\t"
+        "cvt.rn.f16x2.f32 p15, %32, %31;\n\t"
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {p0, p1, p2, p3, p4, p5, p6, p7, p8, p9, p10, p11, p12, p13, p14, p15};\n\t"
+        "}"
+        :
+        : "r"(taddr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]), "f"(v[8]),
+          "f"(v[9]), "f"(v[10]), "f"(v[11]), "f"(v[12]), "f"(v[13]), "f"(v[14]), "f"(v[15]), "f"(lo[0]), "f"(lo[1]),
+          "f"(lo[2]), "f"(lo[3]), "f"(lo[4]), "f"(lo[5]), "f"(lo[6]), "f"(lo[7]), "f"(lo[8]), "f"(lo[9]), "f"(lo[10]),
+          "f"(lo[11]), "f"(lo[12]), "f"(lo[13]), "f"(lo[14]), "f"(lo[15])
+        : "memory");
+}
+
+
+// Batch sum of spectral components on the tensor cores (km_matmul_sum_tc.cu): arguments and launcher.
+struct SumTcArgs {
+    Batch batch;                // the components
+    int64_t m, n, k;
+    int64_t row_blocks, rb_begin;
+    View<const float> x1, x2, rhs, params;  // x1, x2, rhs: one copy shared by all components
+    View<const int> start, end;
+    View<float> out;            // (rows_in_window, k)
+};
+constexpr int SUM_TC_MAX_COMPONENTS = 64;
+constexpr int SUM_TC_MAX_K = 16;
+int launch_matmul_sum_tc(const SumTcArgs &a, cudaStream_t stream);
+
 }  // namespace km

@@ -161,3 +161,36 @@ def test_marginal_likelihood_gradient_matches_dense_fp64(kt):
     est = -0.5 * (u @ K @ u) + (0.5 / t) * (w * (K @ probes.double())).sum()
     (g_exact,) = torch.autograd.grad(est, theta)
     assert torch.allclose(g, g_exact, rtol=5e-2, atol=5e-2 * float(g_exact.abs().max())), (g, g_exact)
+
+
+@pytest.mark.parametrize("B,k", [(2, 1), (7, 8), (64, 8), (33, 11), (64, 16)])
+def test_batch_sum_on_tensor_cores(B, k):
+    """Spectral components with one lengthscale: the batch sum as a tensor-core dot product of
+    per-point phase vectors (km_matmul_sum_tc.cu) against the fp64 oracle, incl. row windows."""
+    from kernel_matmul_b200 import ops
+    from oracle import oracle as O
+
+    n = 1400  # ragged last row block
+    x = torch.sort(torch.rand(n) * 300 + 5000)[0]  # large offsets: phases are taken relative to the row block
+    params = torch.stack([torch.full((B,), 1.3), torch.rand(B) * 1.5, (torch.rand(B) + 0.5) / B], dim=-1)
+    params[0, 1] = 0.0
+    start, end = O.make_ranges(5.0, x)
+    rhs = torch.randn(n, k)
+    ref = O.matmul("spectral", x.expand(B, n), x.expand(B, n), rhs.expand(B, n, k), params, start.expand(B, -1),
+                   end.expand(B, -1)).sum(0)
+    d = lambda t: t.cuda()  # noqa: E731
+    args = ("spectral", d(x).expand(B, n), d(x).expand(B, n), d(rhs).expand(B, n, k), d(params), d(start).expand(B, -1),
+            d(end).expand(B, -1))
+    out = ops.matmul_rows(*args, sum_batches=True)
+    assert out.shape == (n, k) and bool(torch.isfinite(out).all())
+    assert rel_err(out, ref) <= 1e-5
+    win = ops.matmul_rows(*args, sum_batches=True, row_block_begin=3, row_block_count=5)
+    assert rel_err(win, ref[384:1024]) <= 1e-5
+    assert torch.equal(win, out[384:1024])
+    # different lengthscales: the FMA-pipe kernel computes the sum (the tensor-core CTAs leave at once)
+    params2 = params.clone()
+    params2[-1, 0] = 1.1
+    ref2 = O.matmul("spectral", x.expand(B, n), x.expand(B, n), rhs.expand(B, n, k), params2, start.expand(B, -1),
+                    end.expand(B, -1)).sum(0)
+    out2 = ops.matmul_rows(args[0], args[1], args[2], args[3], d(params2), args[5], args[6], sum_batches=True)
+    assert rel_err(out2, ref2) <= 1e-5
