@@ -110,9 +110,9 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
     const uint32_t tmem_base = tmem_base_slot;
     bool failed = false;
 
-    float acc[KB];
+    f32x2 acc2[KB / 2];  // output columns in packed pairs
 #pragma unroll
-    for (int c = 0; c < KB; c++) acc[c] = 0.0f;
+    for (int c = 0; c < KB / 2; c++) acc2[c] = 0ull;
 
     if (is_ctl_warp) {
         // ------------------------------------------------ input fetches (all lanes) + MMA issue (lane 0)
@@ -262,20 +262,25 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
                     tmem_ld16_nowait(tmem_lane + (uint32_t)(ST_C_COL + st * ST_COLS + p * 16), cv);
                     tmem_ld_wait();
 #pragma unroll
-                    for (int u = 0; u < 16; u++) {
-                        const int jj = p * 16 + u;
-                        const float tau = x1v - xs[jj];
-                        float v = __uint_as_float(cv[u]) * ex2_approx(c0 * tau * tau);
-                        if (MASKED) {
-                            if (j0 + jj < band_lo || j0 + jj >= band_hi) v = 0.0f;
-                        }
+                    for (int h = 0; h < 4; h++) {
+                        const float4 xq = *reinterpret_cast<const float4 *>(xs + p * 16 + h * 4);
+                        const float xj[4] = {xq.x, xq.y, xq.z, xq.w};
 #pragma unroll
-                        for (int c4 = 0; c4 < KB / 4; c4++) {
-                            const float4 rv = *reinterpret_cast<const float4 *>(rs + jj * KB + c4 * 4);
-                            acc[c4 * 4 + 0] = fmaf(v, rv.x, acc[c4 * 4 + 0]);
-                            acc[c4 * 4 + 1] = fmaf(v, rv.y, acc[c4 * 4 + 1]);
-                            acc[c4 * 4 + 2] = fmaf(v, rv.z, acc[c4 * 4 + 2]);
-                            acc[c4 * 4 + 3] = fmaf(v, rv.w, acc[c4 * 4 + 3]);
+                        for (int u = 0; u < 4; u++) {
+                            const int jj = p * 16 + h * 4 + u;
+                            const float tau = x1v - xj[u];
+                            float v = __uint_as_float(cv[h * 4 + u]) * ex2_approx(c0 * tau * tau);
+                            if (MASKED) {
+                                if (j0 + jj < band_lo || j0 + jj >= band_hi) v = 0.0f;
+                            }
+                            // rhs row of column jj (a broadcast read), two columns per packed FMA
+                            const f32x2 v2 = splat2(v);
+#pragma unroll
+                            for (int c4 = 0; c4 < KB / 4; c4++) {
+                                const ulonglong2 rv = *reinterpret_cast<const ulonglong2 *>(rs + jj * KB + c4 * 4);
+                                acc2[c4 * 2 + 0] = fma2(v2, rv.x, acc2[c4 * 2 + 0]);
+                                acc2[c4 * 2 + 1] = fma2(v2, rv.y, acc2[c4 * 2 + 1]);
+                            }
                         }
                     }
                 }
@@ -297,6 +302,9 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
         const int64_t row = r * KM_BLOCK_SIZE + tid;
         if (row < a.m) {
             const bool bad = fail_flag != 0;
+            float acc[KB];
+#pragma unroll
+            for (int c = 0; c < KB / 2; c++) unpack2(acc2[c], acc[2 * c], acc[2 * c + 1]);
             float *orow = a.out.data + (row - a.rb_begin * KM_BLOCK_SIZE) * a.out.s0;
 #pragma unroll
             for (int c = 0; c < KB; c++)
