@@ -497,7 +497,7 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
     import kernel_matmul_b200  # noqa: F401
     from kernel_matmul_b200 import ops, workloads
     from kernel_matmul_b200._lib import check, lib
-    from kernel_matmul_b200.cg import ShardedOperator, conjugate_gradient
+    from kernel_matmul_b200.cg import CGSolver, ShardedOperator, conjugate_gradient
 
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
@@ -525,32 +525,10 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
     fp32_peak = max(flops.value / (cuda_ms(probe) * 1e-3) for _ in range(3)) / 1e12
     sm_clock = fp32_peak * 1e12 / (148 * 128 * 2)
 
-    # state of a running solve: a few iterations are warm-up, then K timed iterations
-    state = {"x": torch.zeros_like(y), "r": y.clone(), "p": y.clone()}
-    state["rs"] = (state["r"] * state["r"]).sum(0)
-    tiny = torch.finfo(torch.float32).tiny
-    mv_ms = []
-
-    def iteration(timed: bool):
-        p, r, xs = state["p"], state["r"], state["x"]
-        if timed:
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-        Ap = op.apply(p)
-        if timed:
-            e1.record()
-        alpha = state["rs"] / (p * Ap).sum(0).clamp_min(tiny)
-        xs.addcmul_(p, alpha)
-        r.addcmul_(Ap, -alpha)
-        rs_new = (r * r).sum(0)
-        p.mul_(rs_new / state["rs"].clamp_min(tiny)).add_(r)
-        state["rs"] = rs_new
-        if timed:
-            return e0, e1
-        return None
-
+    # a running solve: a few iterations are warm-up, then K timed iterations
+    solver = CGSolver(op, y)
     for _ in range(max(args.warmup, 3)):
-        iteration(False)
+        solver.step()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -558,11 +536,13 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
     t0 = torch.cuda.Event(enable_timing=True)
     t1 = torch.cuda.Event(enable_timing=True)
     t0.record()
-    evs = [iteration(True) for _ in range(args.steps)]
+    for _ in range(args.steps):
+        solver.step()
     t1.record()
     t1.synchronize()
     total_ms = t0.elapsed_time(t1)
-    apply_ms = statistics.mean(a.elapsed_time(b) for a, b in evs)
+    # the product alone (this rank's rows, no collective)
+    apply_ms = statistics.mean(cuda_ms(lambda: op.apply_rows(solver.p)) for _ in range(3))
     clocks = sampler.stop()
 
     # end to end: host y in, solution out, full solve of `iters` iterations
@@ -611,13 +591,13 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
             "metric": METRIC, "value": units / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": w.name, "ops": "CG iteration: batch-summed banded product (rows sharded) + all-gather + vector updates",
+            "config": {"workload": w.name, "ops": "CG iteration: batch-summed banded product, vector updates and inner products sharded by rows; all-gather of the search direction and of per-row-block partial inner products",
                        "entries_per_matvec": E, "rhs_cols": k, "components": B, "sigma2": w.extra["sigma2"],
-                       "l2": "operands (134 MB vectors) exceed L2", "collective": "all_gather_into_tensor per iteration" if world > 1 else "none"},
+                       "l2": "operands (134 MB vectors) exceed L2", "collective": "3 all_gather_into_tensor per iteration (search direction 134 MB, two arrays of partial inner products 1 MB)" if world > 1 else "none"},
             "roofline": {
                 "bound": "tensor", "kernel": "matmul_sum_tc_kernel",
                 "achieved": tensor_flops / t_apply / 1e12, "peak": f16_peak, "unit": "TFLOP/s", "frac": frac_tensor,
-                "traffic": None, "frac_sfu": frac_sfu, "frac_fp32": frac_fp32, "apply_ms_incl_allgather": apply_ms,
+                "traffic": None, "frac_sfu": frac_sfu, "frac_fp32": frac_fp32, "product_ms": apply_ms,
                 "peak_source": "MEASURED_PEAKS.json bf16_tflops (burst; kind::f16 MMAs); tensor, SFU and FP32 bounds of this "
                                "kernel lie within 25 % of each other (5.4 / 5.0 / 4.4 ms at config 5 on one GPU); SFU peak = "
                                "148 SMs x 16 ops/clk x SM clock implied by the live FFMA probe.  The metric counts "

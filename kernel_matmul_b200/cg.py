@@ -5,12 +5,18 @@
 components, the reference's ``SumKernel``, kernel_matmul/gpytorch/sum.py), evaluated inside one
 kernel launch (``ops.matmul_rows(..., sum_batches=True)``).
 
-Sharding.  The product has no dependence between 128-row blocks, so every rank computes the row
-blocks of its own contiguous window against the full search direction and the windows are put
-together with one ``all_gather_into_tensor`` per iteration; nothing else is communicated.  All
-vector updates and inner products then run redundantly on the full vectors on every rank, in
-the same order, so the iterates are bit-identical on all ranks and do not depend on the number
-of ranks (a row block is always computed by one CTA in the same order, whichever rank owns it).
+Sharding.  The product has no dependence between 128-row blocks, so every rank owns a contiguous
+window of row blocks: it computes those rows of ``K p`` against the full search direction and
+keeps ITS rows of the iterate, the residual and the search direction.  Per iteration the ranks
+exchange
+  * the new search direction (one ``all_gather_into_tensor`` of the row windows), and
+  * two small arrays of per-row-block partial inner products (``p . Ap`` and ``r . r``), which
+    every rank then adds up in the same fixed order.
+An inner product is always formed as "one partial per 128-row block, then the sum over all row
+blocks in index order", whichever rank owns a block, so the iterates do not depend on the number
+of ranks (bit for bit wherever the per-block sums are computed in a size-independent order, which
+holds for the CPU reductions the tests run; a row block's product is always computed by one CTA
+in the same order).
 
 The reference itself has no CG: it inherits ``LinearOperator.solve`` from the third-party
 ``linear_operator`` package (tests/test_linear_operator.py:9-38).  This is a standard batched
@@ -64,9 +70,9 @@ class ShardedOperator:
         self.R = -(-n // BLOCK_SIZE)
         self.per = -(-self.R // self.world)  # row blocks per rank (padded)
         self.begin, self.count = row_block_window(self.R, self.rank, self.world)
+        self.row0 = self.begin * BLOCK_SIZE
+        self.rows = max(0, min(n, (self.begin + self.count) * BLOCK_SIZE) - self.row0)  # rows of this rank
         self.device = device
-        self._gather: Tensor | None = None
-        self._mine: Tensor | None = None
 
     @classmethod
     def from_kernel(cls, kernel_type: str, x: Tensor, params: Tensor, start: Tensor, end: Tensor, sigma2: float,
@@ -88,47 +94,95 @@ class ShardedOperator:
 
         return cls(n, sigma2, matvec_rows, group=group, device=x.device)
 
+    # ---- pieces of a sharded iteration
+
+    def local(self, v: Tensor) -> Tensor:
+        """This rank's rows of a full vector (a view)."""
+        return v[self.row0 : self.row0 + self.rows]
+
+    def apply_rows(self, v: Tensor) -> Tensor:
+        """This rank's rows of ``(K + sigma^2 I) v`` for a full ``v`` -> ``(rows, k)``."""
+        out = torch.empty(self.rows, v.shape[-1], device=v.device, dtype=v.dtype)
+        if self.rows > 0:
+            self.matvec_rows(v, self.begin, self.count, out)
+            out.add_(self.local(v), alpha=self.sigma2)
+        return out
+
+    def gather_rows(self, mine: Tensor) -> Tensor:
+        """Full ``(n, k)`` vector from every rank's rows (the collective of the solve)."""
+        if self.world == 1:
+            return mine
+        k = mine.shape[-1]
+        rows_per_rank = self.per * BLOCK_SIZE
+        padded = torch.zeros(rows_per_rank, k, device=mine.device, dtype=mine.dtype)
+        padded[: self.rows] = mine
+        full = torch.empty(self.world * rows_per_rank, k, device=mine.device, dtype=mine.dtype)
+        self.dist.all_gather_into_tensor(full, padded, group=self.group)
+        return full[: self.n]
+
+    def dot(self, a: Tensor, b: Tensor) -> Tensor:
+        """Column-wise inner products ``(k,)`` of two row-sharded vectors: one partial per 128-row
+        block, all partials gathered, then added in block order on every rank."""
+        k = a.shape[-1]
+        blocks = self.count
+        prod = torch.zeros(max(blocks, 0) * BLOCK_SIZE, k, device=a.device, dtype=a.dtype)
+        prod[: self.rows] = a * b
+        partial = prod.view(blocks, BLOCK_SIZE, k).sum(dim=1)  # (blocks, k)
+        if self.world > 1:
+            padded = torch.zeros(self.per, k, device=a.device, dtype=a.dtype)
+            padded[:blocks] = partial
+            every = torch.empty(self.world * self.per, k, device=a.device, dtype=a.dtype)
+            self.dist.all_gather_into_tensor(every, padded, group=self.group)
+            partial = every[: self.R]
+        return partial.sum(dim=0)
+
     def apply(self, v: Tensor) -> Tensor:
         """Full ``(K + sigma^2 I) v`` on every rank."""
-        k = v.shape[-1]
-        rows_per_rank = self.per * BLOCK_SIZE
-        if self._gather is None or self._gather.shape != (self.world * rows_per_rank, k) or self._gather.device != v.device:
-            self._gather = torch.zeros(self.world * rows_per_rank, k, device=v.device, dtype=v.dtype)
-            self._mine = torch.zeros(rows_per_rank, k, device=v.device, dtype=v.dtype)
-        rows = max(0, min(self.n, (self.begin + self.count) * BLOCK_SIZE) - self.begin * BLOCK_SIZE)
-        if self.world == 1:
-            self.matvec_rows(v, self.begin, self.count, self._gather[:rows])
-        else:
-            if rows > 0:
-                self.matvec_rows(v, self.begin, self.count, self._mine[:rows])
-            # the only collective of the solve: every rank's window lands at its row offset
-            self.dist.all_gather_into_tensor(self._gather, self._mine, group=self.group)
-        return torch.add(self._gather[: self.n], v, alpha=self.sigma2)
+        return self.gather_rows(self.apply_rows(v))
+
+
+class CGSolver:
+    """State of a running solve; ``step()`` is one CG iteration."""
+
+    def __init__(self, op: ShardedOperator, y: Tensor):
+        self.op = op
+        self.tiny = torch.finfo(y.dtype).tiny
+        self.x = torch.zeros(op.rows, y.shape[-1], device=y.device, dtype=y.dtype)  # this rank's rows
+        self.r = op.local(y).clone()
+        self.p_local = self.r.clone()
+        self.p = y.clone() if op.world > 1 else self.p_local  # full search direction
+        self.rs = op.dot(self.r, self.r)
+        self.y_norm = self.rs.sqrt().clamp_min(self.tiny)
+
+    def step(self) -> Tensor:
+        """One iteration; returns the relative residual norms ``(k,)``."""
+        op = self.op
+        Ap = op.apply_rows(self.p)
+        alpha = self.rs / op.dot(self.p_local, Ap).clamp_min(self.tiny)
+        self.x.addcmul_(self.p_local, alpha)
+        self.r.addcmul_(Ap, -alpha)
+        rs_new = op.dot(self.r, self.r)
+        beta = rs_new / self.rs.clamp_min(self.tiny)
+        self.p_local.mul_(beta).add_(self.r)
+        self.p = op.gather_rows(self.p_local)
+        self.rs = rs_new
+        return rs_new.sqrt() / self.y_norm
+
+    def solution(self) -> Tensor:
+        """The full iterate on every rank."""
+        return self.op.gather_rows(self.x)
 
 
 def conjugate_gradient(op: ShardedOperator, y: Tensor, iterations: int, tol: float = 0.0) -> CGResult:
     """Batched CG from x0 = 0: every column of ``y`` is its own system sharing the operator.
     Stops after ``iterations`` steps (or earlier when every column's relative residual is below
     ``tol``, which costs one host synchronisation per iteration and is off for ``tol == 0``)."""
-    x = torch.zeros_like(y)
-    r = y.clone()
-    p = r.clone()
-    rs = (r * r).sum(dim=0)
-    y_norm = rs.sqrt().clamp_min(torch.finfo(y.dtype).tiny)
-    history = [torch.ones_like(rs)]
+    solver = CGSolver(op, y)
+    history = [torch.ones_like(solver.rs)]
     done = 0
     for _ in range(iterations):
-        Ap = op.apply(p)
-        pAp = (p * Ap).sum(dim=0)
-        alpha = rs / pAp.clamp_min(torch.finfo(y.dtype).tiny)
-        x.addcmul_(p, alpha)
-        r.addcmul_(Ap, -alpha)
-        rs_new = (r * r).sum(dim=0)
-        beta = rs_new / rs.clamp_min(torch.finfo(y.dtype).tiny)
-        p.mul_(beta).add_(r)
-        rs = rs_new
-        history.append(rs.sqrt() / y_norm)
+        history.append(solver.step())
         done += 1
         if tol > 0 and bool((history[-1] <= tol).all()):
             break
-    return CGResult(x, torch.stack(history), done)
+    return CGResult(solver.solution(), torch.stack(history), done)

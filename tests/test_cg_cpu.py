@@ -1,7 +1,7 @@
 """Host logic of the row-sharded CG solve on CPU: world_size-2 gloo ranks against a single
 process and against a dense fp64 solve.  The matvec is a dense torch product here (the CUDA
-kernel needs a GPU); sharding, the all-gather and the replicated vector updates are the code
-under test."""
+kernel needs a GPU); sharding, the all-gathers, the row-sharded vector updates and the
+block-ordered inner products are the code under test."""
 import os
 
 import pytest
@@ -75,7 +75,7 @@ def test_cg_sharded_ranks_agree_with_single_process(tmp_path, world):
     windows = [o["window"] for o in outs]
     assert sum(c for _, c in windows) == -(-K.shape[0] // 128)
     for o in outs:
-        # identical iterates on every rank and for every rank count (same row products, same
-        # replicated vector arithmetic)
+        # identical iterates on every rank and for every rank count (same row products, inner
+        # products added per row block and then in block order)
         assert torch.equal(o["x"], single.solution)
         assert torch.equal(o["hist"], single.residual_norms)
