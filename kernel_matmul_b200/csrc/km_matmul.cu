@@ -611,7 +611,7 @@ static int matmul_entry(const char *name, int kernel_type, const km_batch *batch
         // takes the case of one common lengthscale (checked on the device by every CTA of both
         // kernels, so that exactly one of the two does the work).
         if (kernel_type == KM_KERNEL_SPECTRAL && a.sum_shared_ok && a.batch.count >= 2 &&
-            a.batch.count <= SUM_TC_MAX_COMPONENTS && k <= SUM_TC_MAX_K) {
+            a.batch.count <= SUM_TC_MAX_TOTAL && k <= SUM_TC_MAX_K) {
             SumTcArgs t;
             t.batch = a.batch;
             t.m = m;
@@ -626,6 +626,8 @@ static int matmul_entry(const char *name, int kernel_type, const km_batch *batch
             t.start = a.start;
             t.end = a.end;
             t.out = a.out;
+            t.comp_begin = 0;
+            t.comp_count = 0;
             const int rc = launch_matmul_sum_tc(t, s);
             if (rc != KM_OK) return rc;
             a.sum_tc_launched = 1;

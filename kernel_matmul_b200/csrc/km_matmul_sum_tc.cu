@@ -2,7 +2,7 @@
 //
 //   out[i, :] = sum_{j in band} ( sum_b s_b exp(-tau^2 / 2 l^2) cos(w_b tau) ) rhs[j, :],   tau = x_i - x_j
 //
-// for B <= 64 components that share inputs, band, right-hand side and lengthscale (the
+// for components that share inputs, band, right-hand side and lengthscale (64 per launch; the
 // reference's SumKernel over a batch of spectral kernels, kernel_matmul/gpytorch/sum.py:16-24).
 // The FMA-pipe kernel (km_matmul.cu) evaluates one SFU cosine per entry and component.  Here the
 // sum over the components is turned into a dot product the tensor core can do:
@@ -49,7 +49,7 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
     const int warp = tid >> 5;
     const int lane = tid & 31;
     const bool is_ctl_warp = warp == 4;
-    const int B = (int)a.batch.count;
+    const int B = (int)a.comp_count;  // components of this launch: [comp_begin, comp_begin + B)
     const int Bp = (B + 7) & ~7;  // components padded to whole MMA steps (K = 2 Bp)
     const int ksteps = Bp / 8;
 
@@ -57,11 +57,14 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
     // launched next to this one does the work and this CTA leaves at once
     const float ell0 = a.params.data[0];
     int same = 1;
+    // (the lengthscales of ALL components are compared, so that every launch of a chunked sum and
+    // the FMA-pipe kernel come to the same decision)
+    for (int64_t b = tid; b < a.batch.count; b += blockDim.x)
+        same &= (batch_ptr(a.params, decompose(a.batch, b))[0] == ell0) ? 1 : 0;
     for (int b = tid; b < SUM_TC_MAX_COMPONENTS; b += blockDim.x) {
         float w = 0.0f, s = 0.0f;
         if (b < B) {
-            const float *th = batch_ptr(a.params, decompose(a.batch, b));
-            same &= (th[0] == ell0) ? 1 : 0;
+            const float *th = batch_ptr(a.params, decompose(a.batch, a.comp_begin + b));
             w = 2.0f * KM_PI_F * th[a.params.s0];
             s = th[2 * a.params.s0];
         }
@@ -308,7 +311,11 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
             float *orow = a.out.data + (row - a.rb_begin * KM_BLOCK_SIZE) * a.out.s0;
 #pragma unroll
             for (int c = 0; c < KB; c++)
-                if (c < a.k) orow[c * a.out.s1] = bad ? __int_as_float(0x7fc00000) : acc[c];
+                if (c < a.k) {
+                    // later chunks of a sum over more than 64 components add to the first chunk's result
+                    const float prev = a.comp_begin > 0 ? orow[c * a.out.s1] : 0.0f;
+                    orow[c * a.out.s1] = bad ? __int_as_float(0x7fc00000) : acc[c] + prev;
+                }
         }
     }
     if (is_ctl_warp) tmem_free(tmem_base, ST_TMEM_COLS);
@@ -316,7 +323,7 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
 
 template <int KB>
 static int launch_sum_tc_kb(const SumTcArgs &a, cudaStream_t stream) {
-    const int Bp = ((int)a.batch.count + 7) & ~7;
+    const int Bp = ((int)a.comp_count + 7) & ~7;
     const size_t b_stage = (size_t)2 * (2 * Bp / 8) * ST_COLS * 16;
     size_t smem = 2 * b_stage + (size_t)ST_IN_STAGES * (ST_COLS + ST_COLS * KB) * sizeof(float);
     // two CTAs of 256 tensor-memory columns fill an SM: keep a third from being scheduled
@@ -334,7 +341,16 @@ int launch_matmul_sum_tc(const SumTcArgs &a, cudaStream_t stream) {
         set_error("km_matmul_rows_f32: too many row blocks (%lld)", (long long)a.row_blocks);
         return KM_ERR_UNSUPPORTED;
     }
-    return a.k <= 8 ? launch_sum_tc_kb<8>(a, stream) : launch_sum_tc_kb<16>(a, stream);
+    // more than 64 components: chunks of 64, each launch adding to the result of the previous ones
+    // (launches on one stream run in order)
+    SumTcArgs chunk = a;
+    for (int64_t b0 = 0; b0 < a.batch.count; b0 += SUM_TC_MAX_COMPONENTS) {
+        chunk.comp_begin = b0;
+        chunk.comp_count = std::min<int64_t>(SUM_TC_MAX_COMPONENTS, a.batch.count - b0);
+        const int rc = a.k <= 8 ? launch_sum_tc_kb<8>(chunk, stream) : launch_sum_tc_kb<16>(chunk, stream);
+        if (rc != KM_OK) return rc;
+    }
+    return KM_OK;
 }
 
 }  // namespace km

@@ -227,8 +227,10 @@ struct SumTcArgs {
     View<const float> x1, x2, rhs, params;  // x1, x2, rhs: one copy shared by all components
     View<const int> start, end;
     View<float> out;            // (rows_in_window, k)
+    int64_t comp_begin, comp_count;  // components of one launch (set by the launcher)
 };
-constexpr int SUM_TC_MAX_COMPONENTS = 64;
+constexpr int SUM_TC_MAX_COMPONENTS = 64;    // per launch; more are processed in chunks
+constexpr int SUM_TC_MAX_TOTAL = 1024;       // (the FMA-pipe kernel's shared-envelope table holds this many)
 constexpr int SUM_TC_MAX_K = 16;
 int launch_matmul_sum_tc(const SumTcArgs &a, cudaStream_t stream);
 

@@ -163,7 +163,7 @@ def test_marginal_likelihood_gradient_matches_dense_fp64(kt):
     assert torch.allclose(g, g_exact, rtol=5e-2, atol=5e-2 * float(g_exact.abs().max())), (g, g_exact)
 
 
-@pytest.mark.parametrize("B,k", [(2, 1), (7, 8), (64, 8), (33, 11), (64, 16)])
+@pytest.mark.parametrize("B,k", [(2, 1), (7, 8), (64, 8), (33, 11), (64, 16), (100, 8), (130, 3)])
 def test_batch_sum_on_tensor_cores(B, k):
     """Spectral components with one lengthscale: the batch sum as a tensor-core dot product of
     per-point phase vectors (km_matmul_sum_tc.cu) against the fp64 oracle, incl. row windows."""
