@@ -180,6 +180,18 @@ __device__ __forceinline__ f32x2 sin_approx2(f32x2 x) {
 //   locally periodic  u(tau) = 2^(c0 tau^2 + c1 sin^2(w tau)),    c1 = -p1 log2(e), w = pi p2
 // (values: native/common/kernel_function.cuh:25-58).
 //
+// Separable phases (tensor-core kernels).  cos / sin of a phase difference factor into
+// per-point values, cos(W (a_i - a_j)) = c_i c_j + s_i s_j, sin(W (a_i - a_j)) = s_i c_j - c_i s_j
+// with c = cos(W a), s = sin(W a): a kernel computes c_i, s_i once per row and c_j, s_j once
+// per column of a tile and then needs no SFU sine / cosine per entry.  PHASE says whether the
+// kernel type has such a factor, phase_w() is W (spectral: w; locally periodic: 2 w, because
+// sin^2(w tau) = (1 - cos(2 w tau)) / 2 and sin(w tau) cos(w tau) = sin(2 w tau) / 2), and the
+// *_ph functions take cs = cos(W tau), sn = sin(W tau) from the caller.
+// A row block uses the separable form only while |W (x_i - x0)| <= KM_PHASE_MAX_ROW_ARG for all of
+// its rows (x0: the block's middle row): the fp32 phase and the SFU's range reduction lose
+// about 1e-7 of absolute accuracy per radian of argument.
+#define KM_PHASE_MAX_ROW_ARG 16.0f
+//
 // The gradient code accumulates, per kernel type, NSUMS "raw" sums of coeff * (factor of u);
 // finish_grad() turns them into d/d theta including the chain rule of
 // native/common/kernel_function.cuh:92-163 and :221-251.
@@ -214,6 +226,12 @@ struct KernelFn<KM_KERNEL_RBF> {
     }
     __device__ __forceinline__ f32x2 unscaled2(f32x2 tau) const {
         return ex2_approx2(mul2(splat2(c0), mul2(tau, tau)));
+    }
+    static constexpr bool PHASE = false;
+    __device__ __forceinline__ float phase_w() const { return 0.0f; }
+    __device__ __forceinline__ f32x2 unscaled2_ph(f32x2 tau, f32x2, f32x2) const { return unscaled2(tau); }
+    __device__ __forceinline__ void accumulate2_ph(f32x2 tau, f32x2, f32x2, f32x2 coeff, f32x2 *sums2) const {
+        accumulate2(tau, coeff, sums2);
     }
     __device__ __forceinline__ void finish_grad(const double *sums, float *grad) const {
         const double l = ell;
@@ -261,6 +279,20 @@ struct KernelFn<KM_KERNEL_SPECTRAL> {
     }
     __device__ __forceinline__ f32x2 unscaled2(f32x2 tau) const {
         return mul2(ex2_approx2(mul2(splat2(c0), mul2(tau, tau))), cos_approx2(mul2(splat2(w), tau)));
+    }
+    static constexpr bool PHASE = true;
+    __device__ __forceinline__ float phase_w() const { return w; }
+    __device__ __forceinline__ f32x2 unscaled2_ph(f32x2 tau, f32x2 cs, f32x2) const {
+        return mul2(ex2_approx2(mul2(splat2(c0), mul2(tau, tau))), cs);
+    }
+    __device__ __forceinline__ void accumulate2_ph(f32x2 tau, f32x2 cs, f32x2 sn, f32x2 coeff, f32x2 *sums2) const {
+        const f32x2 t2 = mul2(tau, tau);
+        const f32x2 v = mul2(coeff, ex2_approx2(mul2(splat2(c0), t2)));
+        const f32x2 vc = mul2(v, cs);
+        const f32x2 vs = mul2(v, sn);
+        sums2[0] = fma2(vc, t2, sums2[0]);
+        sums2[1] = fma2(vs, tau, sums2[1]);
+        sums2[2] = add2(vc, sums2[2]);
     }
     __device__ __forceinline__ void finish_grad(const double *sums, float *grad) const {
         const double l = ell;
@@ -319,6 +351,22 @@ struct KernelFn<KM_KERNEL_LOCALLY_PERIODIC> {
     __device__ __forceinline__ f32x2 unscaled2(f32x2 tau) const {
         const f32x2 sn = sin_approx2(mul2(splat2(w), tau));
         return ex2_approx2(fma2(mul2(splat2(c0), tau), tau, mul2(splat2(c1), mul2(sn, sn))));
+    }
+    // with cs = cos(2 w tau), sn = sin(2 w tau): sin^2(w tau) = (1 - cs) / 2, sin cos = sn / 2
+    static constexpr bool PHASE = true;
+    __device__ __forceinline__ float phase_w() const { return 2.0f * w; }
+    __device__ __forceinline__ f32x2 unscaled2_ph(f32x2 tau, f32x2 cs, f32x2) const {
+        const f32x2 sn2 = mul2(splat2(0.5f), sub2(splat2(1.0f), cs));
+        return ex2_approx2(fma2(mul2(splat2(c0), tau), tau, mul2(splat2(c1), sn2)));
+    }
+    __device__ __forceinline__ void accumulate2_ph(f32x2 tau, f32x2 cs, f32x2 sn, f32x2 coeff, f32x2 *sums2) const {
+        const f32x2 t2 = mul2(tau, tau);
+        const f32x2 sn2 = mul2(splat2(0.5f), sub2(splat2(1.0f), cs));
+        const f32x2 v = mul2(coeff, ex2_approx2(fma2(splat2(c0), t2, mul2(splat2(c1), sn2))));
+        sums2[0] = fma2(v, t2, sums2[0]);
+        sums2[1] = fma2(v, sn2, sums2[1]);
+        sums2[2] = fma2(mul2(v, mul2(splat2(0.5f), sn)), tau, sums2[2]);
+        sums2[3] = add2(v, sums2[3]);
     }
     __device__ __forceinline__ void finish_grad(const double *sums, float *grad) const {
         const double l = ell, lp = ell_per, pr = period, s = scale;

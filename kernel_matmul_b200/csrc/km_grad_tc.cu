@@ -10,6 +10,8 @@
 // copies of images laid out by a pre-pass) into a tensor-memory stage, while the 128 * G consumer
 // threads -- one tensor-memory lane = one row each -- read the previous stage with tcgen05.ld,
 // evaluate the factors of d kappa / d p per entry and add coeff * factor to their running sums.
+// Sines and cosines of the phase difference come from per-row and per-column factors (the
+// control warp computes those of a tile's 64 columns), so an entry costs ONE SFU operation.
 // (Up to 64 columns per CTA; wider operands are processed in column blocks of 64, whose partial
 // sums add up because the coefficient is linear in the columns.)
 // Per entry the FP32 pipe runs ~11 operations instead of k + 11, issued as packed f32x2
@@ -111,7 +113,7 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
     float *smem_f = reinterpret_cast<float *>(smem_raw);
     const int left_floats = 2 * kp * 128;
     const int img_floats = 2 * kp * GT_COLS;
-    const int slot_floats = img_floats + GT_COLS;
+    const int slot_floats = img_floats + 3 * GT_COLS;  // image, then per column x2, cos and sin of its phase
     auto slot_img = [&](int sl) { return smem_f + left_floats + sl * slot_floats; };
     auto slot_x2 = [&](int sl) { return smem_f + left_floats + sl * slot_floats + img_floats; };
 
@@ -133,12 +135,15 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
     const int band_hi = max(band_lo, min(batch_ptr(a.end, bi)[r * a.end.s0], n));
     const int tile_lo = band_lo / GT_COLS;
     const int tiles = band_hi > band_lo ? (band_hi + GT_COLS - 1) / GT_COLS - tile_lo : 0;
+    // origin of the separable phases: the middle row of the block (keeps |x - x0| as small as tau)
+    const float x0 = x1[min(r * KM_BLOCK_SIZE + KM_BLOCK_SIZE / 2, a.m - 1) * a.x1.s0];
+    const float phase_w = fn.phase_w();
     const float *images = a.images + (a.image_slot_stride ? b * a.image_slot_stride : 0) +
                           (int64_t)kb * a.tiles_total * (2LL * a.kp * GT_COLS);
 
     if (tid == 0) {
 #pragma unroll
-        for (int s = 0; s < GT_MAX_SLOTS; s++) mbar_init(&bar_full[s], 33);  // 32 cp.async arrivals + expect_tx
+        for (int s = 0; s < GT_MAX_SLOTS; s++) mbar_init(&bar_full[s], 2);  // expect_tx arrival + lane 0 after the warp's stores
 #pragma unroll
         for (int s = 0; s < GT_D_STAGES; s++) {
             mbar_init(&bar_dfull[s], 1);
@@ -168,7 +173,17 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
         fence_async_smem();
     }
     tc_fence_before();
-    __syncthreads();
+    // The separable form evaluates sine / cosine at W (x - x0) instead of W tau.  Entries that
+    // matter have a small tau, but a row of an unsorted block can be far from x0, and the fp32
+    // phase then carries an error no envelope damps: such a block keeps the per-entry evaluation.
+    bool use_ph = false;
+    {
+        const int64_t row = r * KM_BLOCK_SIZE + (tid & 127);
+        const bool far = KernelFn<KT>::PHASE && tid < 128 && row < a.m &&
+                         fabsf(phase_w * (x1[row * a.x1.s0] - x0)) > KM_PHASE_MAX_ROW_ARG;
+        const int any_far = __syncthreads_or(far ? 1 : 0);
+        use_ph = KernelFn<KT>::PHASE && !any_far;
+    }
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
@@ -180,22 +195,40 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
     if (is_ctl_warp) {
         // -------------------------------------------- slot fetches (all lanes) + MMA issue (lane 0)
         const uint32_t img_bytes = (uint32_t)img_floats * sizeof(float);
+        // Tiles are fetched in increasing order: the x2 values of the next fetch wait in registers
+        // (loaded one fetch ahead, so the load latency never stalls the warp that issues the MMAs).
+        float x_ahead[GT_COLS / 32];
+        auto load_ahead = [&](int t) {
+#pragma unroll
+            for (int u = 0; u < GT_COLS / 32; u++) {
+                const int64_t j = (int64_t)(tile_lo + t) * GT_COLS + lane + 32 * u;
+                x_ahead[u] = (t < tiles && j < n) ? __ldg(x2 + j * a.x2.s0) : 0.0f;
+            }
+        };
+        load_ahead(0);
         auto fetch = [&](int t) {
             const int sl = t % ns;
             const int64_t tile = tile_lo + t;
-            float *xs = slot_x2(sl);
-#pragma unroll
-            for (int u = 0; u < GT_COLS / 32; u++) {
-                const int jj = lane + 32 * u;
-                const int64_t j = tile * GT_COLS + jj;
-                const bool valid = j < n;
-                cp_async4_zfill(xs + jj, x2 + (valid ? j : 0) * a.x2.s0, valid);
-            }
-            cp_async_mbar_arrive(&bar_full[sl]);
             if (lane == 0) {
                 mbar_expect_tx(&bar_full[sl], img_bytes);
                 bulk_copy_g2s(slot_img(sl), images + tile * img_floats, img_bytes, &bar_full[sl]);
             }
+            // per column: x2 and the separable phase factors cos / sin(W (x2 - x0)), two columns per lane
+            float *xs = slot_x2(sl);
+#pragma unroll
+            for (int u = 0; u < GT_COLS / 32; u++) {
+                const int jj = lane + 32 * u;
+                const float xv = x_ahead[u];
+                xs[jj] = xv;
+                if (use_ph) {
+                    const float ph = phase_w * (xv - x0);
+                    xs[GT_COLS + jj] = cos_approx(ph);
+                    xs[2 * GT_COLS + jj] = sin_approx(ph);
+                }
+            }
+            load_ahead(t + 1);
+            __syncwarp();  // the stores of all lanes precede lane 0's (releasing) arrival
+            if (lane == 0) mbar_arrive(&bar_full[sl]);
         };
         for (int t = 0; t < min(tiles, ns); t++) fetch(t);
 
@@ -208,6 +241,7 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
         const uint64_t d_a0 = smem_desc(smem_u32(smem_f), lbo_a, sbo);
         const uint64_t d_b0 = smem_desc(smem_u32(slot_img(0)), lbo_b, sbo);
         const int ksteps = kp / 8;
+        static_assert(GT_MAX_KP == 64, "the MMA issue code covers 1 .. 8 k-steps");
         for (int t = 0; t < tiles; t++) {
             const int sl = t % ns;
             const int ds = t & 1;
@@ -225,26 +259,50 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t d_tmem = tmem_base + (uint32_t)(ds * GT_COLS);
+                // The MMAs of a tile are issued from straight-line code chosen by the number of
+                // k-steps.  As a loop with a run-time trip count the compiler unrolled them partially
+                // (by two or four), and that form produced wrong coefficient tiles as soon as the
+                // unrolled body ran; a rolled loop and the fully unrolled form are both correct, the
+                // latter ~15 % faster for wide operands (the MMA issue rate bounds those).
                 const uint64_t ah = d_a0, al = d_a0 + a_part;
                 const uint64_t bh = d_b0 + sl * slot_step, bl = bh + b_part;
-                for (int ks = 0; ks < ksteps; ks++) {
-                    mma_tf32(d_tmem, ah + ks * ks_a, bl + ks * ks_b, idesc, ks > 0 ? 1u : 0u);
-                    mma_tf32(d_tmem, al + ks * ks_a, bh + ks * ks_b, idesc, 1u);
+                auto issue = [&](auto ks_tag) {
+                    constexpr int KS = decltype(ks_tag)::value;
+#pragma unroll
+                    for (int ks = 0; ks < KS; ks++) {
+                        mma_tf32(d_tmem, ah + ks * ks_a, bl + ks * ks_b, idesc, ks > 0 ? 1u : 0u);
+                        mma_tf32(d_tmem, al + ks * ks_a, bh + ks * ks_b, idesc, 1u);
+                    }
+#pragma unroll
+                    for (int ks = 0; ks < KS; ks++) mma_tf32(d_tmem, ah + ks * ks_a, bh + ks * ks_b, idesc, 1u);
+                };
+                switch (ksteps) {  // 1 .. GT_MAX_KP / 8
+                    case 1: issue(std::integral_constant<int, 1>{}); break;
+                    case 2: issue(std::integral_constant<int, 2>{}); break;
+                    case 3: issue(std::integral_constant<int, 3>{}); break;
+                    case 4: issue(std::integral_constant<int, 4>{}); break;
+                    case 5: issue(std::integral_constant<int, 5>{}); break;
+                    case 6: issue(std::integral_constant<int, 6>{}); break;
+                    case 7: issue(std::integral_constant<int, 7>{}); break;
+                    default: issue(std::integral_constant<int, 8>{}); break;
                 }
-                for (int ks = 0; ks < ksteps; ks++) mma_tf32(d_tmem, ah + ks * ks_a, bh + ks * ks_b, idesc, 1u);
                 mma_commit(&bar_dfull[ds]);
             }
             __syncwarp();
         }
         if (failed && lane == 0) atomicExch(&fail_flag, 1);
-        cp_async_wait<0>();  // no copy may be in flight when the CTA exits
         __syncwarp();
     } else {
         // ------------------------------------------------------------------------ consumers
         const int g = tid >> 7;
         const int row_local = tid & 127;
         const int64_t row = r * KM_BLOCK_SIZE + row_local;
-        const f32x2 x1v2 = splat2(row < a.m ? x1[row * a.x1.s0] : 0.0f);
+        const float x1v = row < a.m ? x1[row * a.x1.s0] : x0;
+        const f32x2 x1v2 = splat2(x1v);
+        // separable phase factors of this row
+        const float ph_i = phase_w * (x1v - x0);
+        const float c_i = KernelFn<KT>::PHASE ? cos_approx(ph_i) : 1.0f, s_i = KernelFn<KT>::PHASE ? sin_approx(ph_i) : 0.0f;
+        const f32x2 ci2 = splat2(c_i), si2 = splat2(s_i), nci2 = splat2(-c_i);
         const uint32_t tmem_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(g * CPT);
 
         for (int t = 0; t < tiles; t++) {
@@ -260,11 +318,12 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
             const float *xs = slot_x2(sl) + g * CPT;
             // Two copies of the loop body: the band mask costs ~8 instructions per entry when the
             // compiler turns it into selects, and only the first and last tile of a band need it.
-            auto consume = [&](auto masked_tag) {
+            auto consume = [&](auto masked_tag, auto phase_tag) {
                 constexpr bool MASKED = decltype(masked_tag)::value;
+                constexpr bool SEPARABLE = decltype(phase_tag)::value;
                 uint32_t cbuf[2][16];
                 tmem_ld16_nowait(tmem_lane + (uint32_t)(ds * GT_COLS), cbuf[0]);
-                tmem_ld_wait();
+                tmem_ld_wait16(cbuf[0]);
 #pragma unroll
                 for (int p = 0; p < PIECES; p++) {
                     if (p + 1 < PIECES)
@@ -282,16 +341,39 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
                                 if (j < band_lo || j >= band_hi) cf[u] = 0u;
                             }
                         }
-                        fn.accumulate2(sub2(x1v2, xv.x), (f32x2)cf[0] | ((f32x2)cf[1] << 32), sums2);
-                        fn.accumulate2(sub2(x1v2, xv.y), (f32x2)cf[2] | ((f32x2)cf[3] << 32), sums2);
+                        const f32x2 co[2] = {(f32x2)cf[0] | ((f32x2)cf[1] << 32), (f32x2)cf[2] | ((f32x2)cf[3] << 32)};
+                        if constexpr (SEPARABLE) {
+                            f32x2 cs[2], sn[2];
+                            // cos / sin(W tau) = c_i c_j + s_i s_j,  s_i c_j - c_i s_j
+                            const ulonglong2 cj = *reinterpret_cast<const ulonglong2 *>(xs + GT_COLS + p * 16 + h * 4);
+                            const ulonglong2 sj = *reinterpret_cast<const ulonglong2 *>(xs + 2 * GT_COLS + p * 16 + h * 4);
+                            cs[0] = fma2(ci2, cj.x, mul2(si2, sj.x));
+                            cs[1] = fma2(ci2, cj.y, mul2(si2, sj.y));
+                            sn[0] = fma2(nci2, sj.x, mul2(si2, cj.x));
+                            sn[1] = fma2(nci2, sj.y, mul2(si2, cj.y));
+                            fn.accumulate2_ph(sub2(x1v2, xv.x), cs[0], sn[0], co[0], sums2);
+                            fn.accumulate2_ph(sub2(x1v2, xv.y), cs[1], sn[1], co[1], sums2);
+                        } else {
+                            fn.accumulate2(sub2(x1v2, xv.x), co[0], sums2);
+                            fn.accumulate2(sub2(x1v2, xv.y), co[1], sums2);
+                        }
                     }
-                    if (p + 1 < PIECES) tmem_ld_wait();
+                    if (p + 1 < PIECES) tmem_ld_wait16(cbuf[(p + 1) & 1]);
                 }
             };
-            if (j0 < band_lo || j0 + CPT > band_hi)
-                consume(std::true_type{});
-            else
-                consume(std::false_type{});
+            const bool edge = j0 < band_lo || j0 + CPT > band_hi;
+            if constexpr (KernelFn<KT>::PHASE) {
+                if (use_ph) {
+                    if (edge) consume(std::true_type{}, std::true_type{});
+                    else consume(std::false_type{}, std::true_type{});
+                } else {
+                    if (edge) consume(std::true_type{}, std::false_type{});
+                    else consume(std::false_type{}, std::false_type{});
+                }
+            } else {
+                if (edge) consume(std::true_type{}, std::false_type{});
+                else consume(std::false_type{}, std::false_type{});
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_dfree[ds]);
@@ -339,7 +421,7 @@ static int launch_grad_tc(const GradTcArgs &a, cudaStream_t s) {
         set_error("gradient (tensor cores): too many work items (%lld)", (long long)items);
         return KM_ERR_UNSUPPORTED;
     }
-    size_t smem = ((size_t)2 * a.kp * 128 + (size_t)a.slots * (2 * a.kp * GT_COLS + GT_COLS)) * sizeof(float);
+    size_t smem = ((size_t)2 * a.kp * 128 + (size_t)a.slots * (2 * a.kp * GT_COLS + 3 * GT_COLS)) * sizeof(float);
     // four CTAs of 128 tensor-memory columns fill an SM: keep a fifth from being scheduled
     smem = std::max<size_t>(smem, 46 * 1024);
     auto kernel = grad_tc_kernel<KT, G>;

@@ -52,6 +52,7 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
     const int B = (int)a.comp_count;  // components of this launch: [comp_begin, comp_begin + B)
     const int Bp = (B + 7) & ~7;  // components padded to whole MMA steps (K = 2 Bp)
     const int ksteps = Bp / 8;
+    static_assert(SUM_TC_MAX_COMPONENTS == 64, "the MMA issue code covers 1 .. 8 k-steps");
 
     // every CTA checks that the components share one lengthscale; if not, the FMA-pipe kernel
     // launched next to this one does the work and this CTA leaves at once
@@ -163,13 +164,30 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
             if (lane == 0) {
                 const uint32_t d_tmem = tmem_base + (uint32_t)(ST_C_COL + st * ST_COLS);
                 const uint64_t b_hi = d_b0 + st * stage_step, b_lo = b_hi + part_step;
-                for (int ks = 0; ks < ksteps; ks++) {
-                    const uint32_t a_hi = tmem_base + (uint32_t)(16 * ks), a_lo = a_hi + 8;
-                    mma_f16_ts(d_tmem, a_hi, b_lo + ks * kstep_b, idesc, ks > 0 ? 1u : 0u);
-                    mma_f16_ts(d_tmem, a_lo, b_hi + ks * kstep_b, idesc, 1u);
+                // straight-line code per k-step count (a partially unrolled run-time loop of MMAs gave
+                // wrong tiles in the gradient kernel; see there)
+                auto issue = [&](auto ks_tag) {
+                    constexpr int KS = decltype(ks_tag)::value;
+#pragma unroll
+                    for (int ks = 0; ks < KS; ks++) {
+                        const uint32_t a_hi = tmem_base + (uint32_t)(16 * ks), a_lo = a_hi + 8;
+                        mma_f16_ts(d_tmem, a_hi, b_lo + ks * kstep_b, idesc, ks > 0 ? 1u : 0u);
+                        mma_f16_ts(d_tmem, a_lo, b_hi + ks * kstep_b, idesc, 1u);
+                    }
+#pragma unroll
+                    for (int ks = 0; ks < KS; ks++)
+                        mma_f16_ts(d_tmem, tmem_base + (uint32_t)(16 * ks), b_hi + ks * kstep_b, idesc, 1u);
+                };
+                switch (ksteps) {  // 1 .. SUM_TC_MAX_COMPONENTS / 8
+                    case 1: issue(std::integral_constant<int, 1>{}); break;
+                    case 2: issue(std::integral_constant<int, 2>{}); break;
+                    case 3: issue(std::integral_constant<int, 3>{}); break;
+                    case 4: issue(std::integral_constant<int, 4>{}); break;
+                    case 5: issue(std::integral_constant<int, 5>{}); break;
+                    case 6: issue(std::integral_constant<int, 6>{}); break;
+                    case 7: issue(std::integral_constant<int, 7>{}); break;
+                    default: issue(std::integral_constant<int, 8>{}); break;
                 }
-                for (int ks = 0; ks < ksteps; ks++)
-                    mma_f16_ts(d_tmem, tmem_base + (uint32_t)(16 * ks), b_hi + ks * kstep_b, idesc, 1u);
                 mma_commit(&bar_cfull[st]);
             }
             __syncwarp();
@@ -263,7 +281,7 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
                 for (int p = 0; p < ST_COLS / 16; p++) {
                     uint32_t cv[16];
                     tmem_ld16_nowait(tmem_lane + (uint32_t)(ST_C_COL + st * ST_COLS + p * 16), cv);
-                    tmem_ld_wait();
+                    tmem_ld_wait16(cv);
 #pragma unroll
                     for (int h = 0; h < 4; h++) {
                         const float4 xq = *reinterpret_cast<const float4 *>(xs + p * 16 + h * 4);

@@ -70,7 +70,7 @@ struct TcCfg {
     static constexpr int MIN_CTAS = N == 16 ? 4 : (N == 32 ? 3 : (N == 64 ? 2 : 1));
     static constexpr int IMG_HALFS = 2 * TC_SCOLS * N;  // hi + lo image of one slot (fp16 values)
     static constexpr int IMG_BYTES = IMG_HALFS * 2;
-    static constexpr int SLOT_BYTES = IMG_BYTES + TC_SCOLS * 4;  // image + x2 values
+    static constexpr int SLOT_BYTES = IMG_BYTES + 3 * TC_SCOLS * 4;  // image + x2 values + separable phase factors (cos, sin)
     // dynamic shared memory: the slots, padded so that no more CTAs fit an SM than its 512
     // tensor-memory columns can serve
     static constexpr size_t SMEM_BYTES = N <= 32 ? 48 * 1024 : (N == 64 ? 80 * 1024 : 136 * 1024);
@@ -209,7 +209,9 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
     if (tid == 0) {
 #pragma unroll
         for (int s = 0; s < TC_SLOTS; s++) {
-            mbar_init(&bar_full[s], 33);  // 32 lanes' cp.async arrivals + the bulk copy's expect_tx arrival
+            // kernels without a phase: 32 lanes' cp.async arrivals + the bulk copy's expect_tx arrival;
+            // with one: the expect_tx arrival + lane 0's arrival after the warp's stores
+            mbar_init(&bar_full[s], KernelFn<KT>::PHASE ? 2 : 33);
             mbar_init(&bar_sfree[s], 1);
         }
 #pragma unroll
@@ -227,7 +229,18 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
     }
     if (is_ctl_warp) tmem_alloc(&tmem_base_slot, TC_TMEM_COLS);
     tc_fence_before();
-    __syncthreads();
+    // Separable phases: origin x0 = the block's middle row; a block with a row too far from x0
+    // (unsorted inputs) keeps the per-entry sine / cosine.
+    const float x0 = KernelFn<KT>::PHASE ? x1[min(r * KM_BLOCK_SIZE + KM_BLOCK_SIZE / 2, a.m - 1) * a.x1.s0] : 0.0f;
+    const float phase_w = fn.phase_w();
+    bool use_ph = false;
+    {
+        const int64_t row = r * KM_BLOCK_SIZE + row_local;
+        const bool far = KernelFn<KT>::PHASE && tid < 128 && row < a.m &&
+                         fabsf(phase_w * (x1[row * a.x1.s0] - x0)) > KM_PHASE_MAX_ROW_ARG;
+        const int any_far = __syncthreads_or(far ? 1 : 0);
+        use_ph = KernelFn<KT>::PHASE && !any_far;
+    }
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_slot;
 
@@ -241,21 +254,49 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
 
     if (is_ctl_warp) {
         // ------------------------------------------- slot fetches (all lanes) + MMA issue (lane 0)
+        // Slots are fetched in increasing order, so a phase kernel keeps the x2 values of the
+        // next fetch in registers (loaded one fetch ahead: the load latency never stalls the warp).
+        float x_ahead[TC_SCOLS / 32];
+        auto load_ahead = [&](int sr) {
+#pragma unroll
+            for (int u = 0; u < TC_SCOLS / 32; u++) {
+                const int64_t j = (int64_t)(super_lo + sr) * TC_SCOLS + lane + 32 * u;
+                x_ahead[u] = (sr < supers && j < n) ? __ldg(x2 + j * a.x2.s0) : 0.0f;
+            }
+        };
+        if constexpr (KernelFn<KT>::PHASE) load_ahead(0);
         auto fetch = [&](int sr) {
             const int sl = sr % TC_SLOTS;
             const int64_t sup = super_lo + sr;
             float *xs = slot_x2(sl);
-#pragma unroll
-            for (int u = 0; u < TC_SCOLS / 32; u++) {
-                const int jj = lane + 32 * u;
-                const int64_t j = sup * TC_SCOLS + jj;
-                const bool valid = j < n;
-                cp_async4_zfill(xs + jj, x2 + (valid ? j : 0) * a.x2.s0, valid);
-            }
-            cp_async_mbar_arrive(&bar_full[sl]);
             if (lane == 0) {
                 mbar_expect_tx(&bar_full[sl], TC_IMG_BYTES);
                 bulk_copy_g2s(slot_img(sl), images + sup * TC_IMG_BYTES, TC_IMG_BYTES, &bar_full[sl]);
+            }
+            if constexpr (KernelFn<KT>::PHASE) {
+#pragma unroll
+                for (int u = 0; u < TC_SCOLS / 32; u++) {
+                    const int jj = lane + 32 * u;
+                    const float xv = x_ahead[u];
+                    xs[jj] = xv;
+                    if (use_ph) {
+                        const float ph = phase_w * (xv - x0);
+                        xs[TC_SCOLS + jj] = cos_approx(ph);
+                        xs[2 * TC_SCOLS + jj] = sin_approx(ph);
+                    }
+                }
+                load_ahead(sr + 1);
+                __syncwarp();  // every lane's stores precede lane 0's (releasing) arrival
+                if (lane == 0) mbar_arrive(&bar_full[sl]);
+            } else {
+#pragma unroll
+                for (int u = 0; u < TC_SCOLS / 32; u++) {
+                    const int jj = lane + 32 * u;
+                    const int64_t j = sup * TC_SCOLS + jj;
+                    const bool valid = j < n;
+                    cp_async4_zfill(xs + jj, x2 + (valid ? j : 0) * a.x2.s0, valid);
+                }
+                cp_async_mbar_arrive(&bar_full[sl]);
             }
         };
         for (int sr = 0; sr < min(supers, TC_SLOTS); sr++) fetch(sr);
@@ -330,7 +371,10 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
     } else {
         // ----------------------------------------------------------------------- generators
         const int64_t row = r * KM_BLOCK_SIZE + row_local;
-        const float x1v = row < a.m ? x1[row * a.x1.s0] : 0.0f;
+        const float x1v = row < a.m ? x1[row * a.x1.s0] : x0;
+        // separable phase factors of this row
+        const float ph_i = phase_w * (x1v - x0);
+        const f32x2 ci2 = splat2(use_ph ? cos_approx(ph_i) : 1.0f), si2 = splat2(use_ph ? sin_approx(ph_i) : 0.0f);
         const uint32_t tmem_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
 
         auto collect = [&](int ai) {
@@ -339,7 +383,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             for (int q = 0; q < NPT / 16; q++) {
                 uint32_t v[16];
                 tmem_ld16_nowait(tmem_lane + (uint32_t)(TC_ACC_COL + ai * N + g * NPT + q * 16), v);
-                tmem_ld_wait();
+                tmem_ld_wait16(v);
 #pragma unroll
                 for (int u = 0; u < 16; u++) acc[q * 16 + u] += __uint_as_float(v[u]);
             }
@@ -390,11 +434,22 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
                     const ulonglong2 *xs2 = reinterpret_cast<const ulonglong2 *>(xs);
                     const f32x2 x1v2 = splat2(x1v);
                     f32x2 kv2[8];
+                    if (use_ph) {
+                        // cos(W tau) = c_i c_j + s_i s_j from the slot's per-column factors
+                        const ulonglong2 *cj2 = xs2 + TC_SCOLS / 4, *sj2 = xs2 + 2 * (TC_SCOLS / 4);
 #pragma unroll
-                    for (int h = 0; h < 4; h++) {
-                        const ulonglong2 xv = xs2[half * 4 + h];
-                        kv2[2 * h] = fn.unscaled2(sub2(x1v2, xv.x));
-                        kv2[2 * h + 1] = fn.unscaled2(sub2(x1v2, xv.y));
+                        for (int h = 0; h < 4; h++) {
+                            const ulonglong2 xv = xs2[half * 4 + h], cj = cj2[half * 4 + h], sj = sj2[half * 4 + h];
+                            kv2[2 * h] = fn.unscaled2_ph(sub2(x1v2, xv.x), fma2(ci2, cj.x, mul2(si2, sj.x)), 0ull);
+                            kv2[2 * h + 1] = fn.unscaled2_ph(sub2(x1v2, xv.y), fma2(ci2, cj.y, mul2(si2, sj.y)), 0ull);
+                        }
+                    } else {
+#pragma unroll
+                        for (int h = 0; h < 4; h++) {
+                            const ulonglong2 xv = xs2[half * 4 + h];
+                            kv2[2 * h] = fn.unscaled2(sub2(x1v2, xv.x));
+                            kv2[2 * h + 1] = fn.unscaled2(sub2(x1v2, xv.y));
+                        }
                     }
 #pragma unroll
                     for (int u = 0; u < 8; u++) {

@@ -164,7 +164,7 @@ def test_tc_gradient_unbanded_long_bands():
 
 
 @pytest.mark.parametrize("kt", KERNEL_TYPES)
-@pytest.mark.parametrize("k", [33, 40, 64, 65, 100, 130])
+@pytest.mark.parametrize("k", [33, 40, 48, 56, 64, 65, 100, 130])
 def test_tc_gradient_wide_operands(kt, k):
     # up to 64 columns: four consumer groups; beyond: column blocks of 64
     _run_grad(kt, 400, 500, k)
@@ -243,3 +243,37 @@ def test_tc_product_row_window(k):
     assert rel_err(tail, ref[:, 1280:]) <= 1e-5
     full = ops.matmul(*args, path="tc")
     assert torch.equal(out, full[:, 384:896])
+
+
+# ------------------------------------------------------------------ separable phases and their guard
+
+
+@pytest.mark.parametrize("kt", ["spectral", "locally_periodic"])
+@pytest.mark.parametrize("rows", ["unsorted", "sorted"])
+def test_tc_phase_factors_far_rows_and_offsets(kt, rows):
+    # The tensor-core kernels factor cos / sin(W (x1_i - x2_j)) into per-row and per-column values
+    # around the row block's middle point.  Unsorted rows spread a block over the whole range (the
+    # kernels must then keep the per-entry evaluation); sorted rows far from zero keep the factored
+    # form, whose arguments are differences to a nearby origin.
+    from conftest import assert_grad_close
+    from kernel_matmul_b200 import ops
+    from oracle import oracle as O
+
+    m, n, k = 500, 700, 16
+    x1 = torch.rand(m) * 60 + 300
+    if rows == "sorted":
+        x1 = torch.sort(x1)[0]
+    x2 = torch.sort(torch.rand(n) * 60 + 300)[0]
+    params = make_params(kt, ())
+    start, end = O.make_ranges(None if rows == "unsorted" else 4.0, x1, x2)
+    rhs, og = torch.randn(n, k), torch.randn(m, k)
+    d = lambda t: t.cuda()  # noqa: E731
+    args = (kt, d(x1), d(x2), d(rhs), d(params), d(start), d(end))
+    out = ops.matmul(*args, path="tc")
+    assert ops.tc_status(out) == 0
+    assert rel_err(out, O.matmul(kt, x1, x2, rhs, params, start, end)) <= 1e-5
+    grad = ops.matmul_bwd(*args, d(og), path="tc")
+    assert ops.tc_status(grad) == 0
+    ref = O.matmul_bwd(kt, x1, x2, rhs, params, start, end, og)
+    scale = O.matmul_bwd(kt, x1, x2, rhs, params, start, end, og, absolute=True)
+    assert_grad_close(grad, ref, scale)
