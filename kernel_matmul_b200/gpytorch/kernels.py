@@ -20,7 +20,7 @@ from gpytorch.priors import Prior
 from torch import Size, Tensor, nn
 
 from ..linear_operator import KernelMatmulLinearOperator
-from ..ranges import make_ranges
+from ..ranges import make_ranges, make_ranges_symmetric_cutoffs
 
 
 class KernelMatmulKernel(Kernel):
@@ -92,15 +92,29 @@ class KernelMatmulKernel(Kernel):
             return z * self._get_largest_lengthscale()
         return self._cutoff
 
+    def _cutoff_on_device(self) -> Tensor:
+        """The dynamic cutoff of ``_cutoff_now`` as a 0-dim fp32 tensor on the parameters' device,
+        computed without a host synchronisation (kernel_matmul/gpytorch/base.py:59-64 reads the
+        largest lengthscale back with ``.item()`` on every forward)."""
+        z = math.sqrt(2.0) * torch.special.erfinv(torch.tensor(1.0 - self._epsilon)).item()
+        largest = torch.stack([getattr(self, name).detach().max() for name in self._LENGTHSCALES]).max()
+        return (largest.double() * z).float()
+
     def forward(self, x1: Tensor, x2: Tensor, diag: bool = False, last_dim_is_batch: bool = False, **params):
         if last_dim_is_batch:
             raise NotImplementedError("last_dim_is_batch not supported for KernelMatmulKernel")
         symmetric = x1.shape == x2.shape and torch.equal(x1, x2)
-        cutoff = self._cutoff_now()
-        if symmetric:
-            start, end = make_ranges(cutoff, x1.squeeze(-1), align=True)
+        xs = x1.squeeze(-1)
+        if symmetric and self._epsilon is not None and xs.is_cuda and xs.dim() == 1:
+            # dynamic cutoff without reading the lengthscale back to the host: the band is built on
+            # the device from a device-resident cutoff (same value: double product, rounded to fp32)
+            start, end = make_ranges_symmetric_cutoffs(self._cutoff_on_device().reshape(1), xs)
+            start, end = start[0], end[0]
+        elif symmetric:
+            cutoff = self._cutoff_now()
+            start, end = make_ranges(cutoff, xs, align=True)
         else:
-            start, end = make_ranges(cutoff, x1.squeeze(-1), x2.squeeze(-1), align=True)
+            start, end = make_ranges(self._cutoff_now(), xs, x2.squeeze(-1), align=True)
         operator = KernelMatmulLinearOperator(
             x1, x2, self._get_params(), start, end,
             kernel_type=self._KERNEL_TYPE, symmetric=symmetric, compile_pool=self._compile_pool,

@@ -83,3 +83,22 @@ def test_symmetric_ranges_with_per_batch_cutoffs():
     for b, c in enumerate(cutoffs.tolist()):
         rs, re_ = ranges.make_ranges(c, xb[b].cuda())
         assert torch.equal(s[b], rs) and torch.equal(e[b], re_)
+
+
+def test_dynamic_cutoff_from_a_device_resident_lengthscale():
+    # The GPyTorch-facing kernels derive the cutoff from the largest lengthscale
+    # (kernel_matmul/gpytorch/base.py:59-64).  Computed on the device (double product, rounded to
+    # fp32) and fed to the batched band construction it must give the band of the host-side value.
+    import math
+
+    from kernel_matmul_b200 import ranges
+
+    torch.manual_seed(3)
+    x = torch.sort(torch.rand(5000) * 40)[0].cuda()
+    for eps in (1e-3, 1e-5, 1e-7):
+        z = math.sqrt(2.0) * torch.special.erfinv(torch.tensor(1.0 - eps)).item()
+        lengthscales = (0.3 + torch.rand(4) * 2).cuda()
+        on_device = (lengthscales.max().double() * z).float()
+        start_d, end_d = ranges.make_ranges_symmetric_cutoffs(on_device.reshape(1), x)
+        start_h, end_h = ranges.make_ranges(z * lengthscales.max().item(), x, align=True)
+        assert torch.equal(start_d[0], start_h) and torch.equal(end_d[0], end_h)
