@@ -65,8 +65,8 @@ NPARAMS = {"rbf": 2, "spectral": 3, "locally_periodic": 4}
 #   forward   tau, its envelope exponent, cos(W tau) = c_i c_j + s_i s_j, the product, + 2 for the
 #             fp16 hi / lo split;
 #   gradient  the same plus sin(W tau), the coefficient and one accumulation per parameter.
-TC_FWD = {"rbf": (5, 1), "spectral": (8, 1), "locally_periodic": (10, 1)}
-TC_BWD = {"rbf": (6, 1), "spectral": (13, 1), "locally_periodic": (16, 1)}
+TC_FWD = {"rbf": (5, 1), "spectral": (8, 1), "locally_periodic": (9, 1)}
+TC_BWD = {"rbf": (6, 1), "spectral": (13, 1), "locally_periodic": (15, 1)}
 
 
 def fp32_instr_fwd(kt: str, k: int) -> int:

@@ -233,6 +233,7 @@ struct KernelFn<KM_KERNEL_RBF> {
     __device__ __forceinline__ void accumulate2_ph(f32x2 tau, f32x2, f32x2, f32x2 coeff, f32x2 *sums2) const {
         accumulate2(tau, coeff, sums2);
     }
+    __device__ __forceinline__ void rescale_ph(f32x2 *) const {}
     __device__ __forceinline__ void finish_grad(const double *sums, float *grad) const {
         const double l = ell;
         // d kappa / d p0 = -s e tau^2 ; d p0 / d l = -1 / l^3
@@ -294,6 +295,7 @@ struct KernelFn<KM_KERNEL_SPECTRAL> {
         sums2[1] = fma2(vs, tau, sums2[1]);
         sums2[2] = add2(vc, sums2[2]);
     }
+    __device__ __forceinline__ void rescale_ph(f32x2 *) const {}
     __device__ __forceinline__ void finish_grad(const double *sums, float *grad) const {
         const double l = ell;
         const double pi = 3.14159265358979323846;
@@ -355,18 +357,24 @@ struct KernelFn<KM_KERNEL_LOCALLY_PERIODIC> {
     // with cs = cos(2 w tau), sn = sin(2 w tau): sin^2(w tau) = (1 - cs) / 2, sin cos = sn / 2
     static constexpr bool PHASE = true;
     __device__ __forceinline__ float phase_w() const { return 2.0f * w; }
+    // (the halves are folded into constants: c1 sin^2 = (c1 / 2) q with q = 1 - cs; the sums [1] and
+    // [2] are accumulated as sum v q and sum v sn tau and halved once by rescale_ph)
     __device__ __forceinline__ f32x2 unscaled2_ph(f32x2 tau, f32x2 cs, f32x2) const {
-        const f32x2 sn2 = mul2(splat2(0.5f), sub2(splat2(1.0f), cs));
-        return ex2_approx2(fma2(mul2(splat2(c0), tau), tau, mul2(splat2(c1), sn2)));
+        const f32x2 q = sub2(splat2(1.0f), cs);
+        return ex2_approx2(fma2(mul2(splat2(c0), tau), tau, mul2(splat2(0.5f * c1), q)));
     }
     __device__ __forceinline__ void accumulate2_ph(f32x2 tau, f32x2 cs, f32x2 sn, f32x2 coeff, f32x2 *sums2) const {
         const f32x2 t2 = mul2(tau, tau);
-        const f32x2 sn2 = mul2(splat2(0.5f), sub2(splat2(1.0f), cs));
-        const f32x2 v = mul2(coeff, ex2_approx2(fma2(splat2(c0), t2, mul2(splat2(c1), sn2))));
+        const f32x2 q = sub2(splat2(1.0f), cs);
+        const f32x2 v = mul2(coeff, ex2_approx2(fma2(splat2(c0), t2, mul2(splat2(0.5f * c1), q))));
         sums2[0] = fma2(v, t2, sums2[0]);
-        sums2[1] = fma2(v, sn2, sums2[1]);
-        sums2[2] = fma2(mul2(v, mul2(splat2(0.5f), sn)), tau, sums2[2]);
+        sums2[1] = fma2(v, q, sums2[1]);
+        sums2[2] = fma2(mul2(v, sn), tau, sums2[2]);
         sums2[3] = add2(v, sums2[3]);
+    }
+    __device__ __forceinline__ void rescale_ph(f32x2 *sums2) const {
+        sums2[1] = mul2(splat2(0.5f), sums2[1]);
+        sums2[2] = mul2(splat2(0.5f), sums2[2]);
     }
     __device__ __forceinline__ void finish_grad(const double *sums, float *grad) const {
         const double l = ell, lp = ell_per, pr = period, s = scale;

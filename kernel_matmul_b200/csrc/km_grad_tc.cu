@@ -379,6 +379,7 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
             if (lane == 0) mbar_arrive(&bar_dfree[ds]);
         }
         if (failed) atomicExch(&fail_flag, 1);
+        if (use_ph) fn.rescale_ph(sums2);  // constant factors the factored form left out of the loop
 
         // warp part of the CTA reduction
 #pragma unroll
