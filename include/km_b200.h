@@ -88,11 +88,14 @@ KM_API int km_matmul_f32(int kernel_type, const km_batch *batch, int64_t m, int6
                   const km_view *out, void *stream);
 
 /* ---------------------------------------------------------------------------------------
- * The same product on the tensor cores (tcgen05.mma, fp32 accumulators in tensor memory), for
- * right-hand sides wide enough to make the contraction a dense GEMM.  Same arguments and
- * result as km_matmul_f32 (to fp32 accuracy: 3xTF32 split operands), plus a workspace of
+ * The same product on the tensor cores (tcgen05.mma, fp32 accumulators in tensor memory): any
+ * number of columns, GEMM width 16 / 32 / 64 / 128.  Same arguments and result as km_matmul_f32
+ * (to fp32 accuracy: kernel entries and rhs as fp16 hi + lo pairs, 22 significant bits each, rhs
+ * columns scaled by a power of two; sine and cosine of a phase difference from per-row and
+ * per-column factors around the row block's middle point, per-entry evaluation for row blocks
+ * that span too wide a range), plus a workspace of
  * km_matmul_tc_workspace_bytes(...) bytes, 256-byte aligned, contents irrelevant on entry: a
- * pre-pass writes the rhs there as hi / lo TF32 tile images in the tensor core's shared-memory
+ * pre-pass writes the rhs there as hi / lo fp16 tile images in the tensor core's shared-memory
  * layout, preceded by a 4-byte status word (0 = ok, non-zero = a bounded wait inside the
  * kernel gave up and the output is invalid; read it with km_workspace_status, which
  * synchronises the stream).  Replaces the same reference call as km_matmul_f32.
@@ -166,8 +169,9 @@ KM_API int km_matmul_bwd_f32(int kernel_type, const km_batch *batch, int64_t m, 
 /* ---------------------------------------------------------------------------------------
  * The same gradients with the coefficients <left[i, :], right[j, :]> computed on the tensor
  * cores (tcgen05.mma, 3xTF32 = fp32-level accuracy) while the threads evaluate the factors of
- * d kappa / d p: the FP32 pipe no longer pays k FMAs per entry.  Up to 64 columns per pass; wider
- * operands are processed in column blocks of 64.  Replaces the same reference calls as
+ * d kappa / d p: the FP32 pipe no longer pays k FMAs per entry.  Sine and cosine of a phase
+ * difference come from per-row and per-column factors, as in km_matmul_tc_f32.  Up to 64 columns
+ * per pass; wider operands are processed in column blocks of 64.  Replaces the same reference calls as
  * km_bilinear_derivative_f32 / km_matmul_bwd_f32.
  * workspace: km_grad_tc_workspace_bytes(...) bytes of device memory, 256-byte aligned: a 4-byte
  * status word (0 = ok, non-zero = a bounded wait inside the kernel gave up and the gradient is
