@@ -42,6 +42,7 @@ import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 import torch
@@ -88,57 +89,64 @@ def dist_env():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    """Samples the SM clock and the clock-event (throttle) reasons of one GPU while the timed region
+    runs: a thread reading NVML every 10 ms (read-only queries; short timed regions still get
+    samples, which a freshly spawned nvidia-smi would miss)."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
+    REASONS = {  # NVML clocks-event-reason bits
+        0x0000000000000008: "hw_slowdown",
+        0x0000000000000040: "hw_thermal_slowdown",
+        0x0000000000000020: "sw_thermal_slowdown",
+        0x0000000000000004: "sw_power_cap",
+    }
 
     def __init__(self, device_index: int):
-        self.proc = None
-        self.path = None
+        self.samples, self.max_mhz, self.reasons = [], None, set()
+        self.stop_flag = threading.Event()
+        self.thread = None
         try:
+            import pynvml
+
+            pynvml.nvmlInit()
             uuid = str(torch.cuda.get_device_properties(device_index).uuid)
             if not uuid.startswith("GPU-"):
                 uuid = "GPU-" + uuid
-            fd, self.path = tempfile.mkstemp(suffix=".csv")
-            os.close(fd)
-            self.out = open(self.path, "w")
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", uuid, f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=self.out, stderr=subprocess.DEVNULL)
-        except Exception:  # noqa: BLE001 - no nvidia-smi: report empty clocks
-            self.proc = None
+            try:
+                handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            except TypeError:
+                handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            reasons_fn = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+
+            def run():
+                while not self.stop_flag.is_set():
+                    try:
+                        self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                        bits = int(reasons_fn(handle))
+                        for bit, name in self.REASONS.items():
+                            if bits & bit:
+                                self.reasons.add(name)
+                    except Exception:  # noqa: BLE001 - a failed read is a missing sample
+                        pass
+                    self.stop_flag.wait(0.01)
+
+            self.thread = threading.Thread(target=run, daemon=True)
+            self.thread.start()
+        except Exception:  # noqa: BLE001 - no NVML: report empty clocks
+            self.thread = None
 
     def stop(self) -> dict:
-        if self.proc is None:
+        if self.thread is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:  # noqa: BLE001
-            self.proc.kill()
-        self.out.close()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in open(self.path):
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 7:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[3:7]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        os.unlink(self.path)
-        busy = [s for s in sm if s > 0.5 * max(sm)] if sm else []
+        self.stop_flag.set()
+        self.thread.join(timeout=2)
+        sm = list(self.samples)
+        busy = [v for v in sm if v > 0.5 * max(sm)] if sm else []
         return {
             "sm_mhz": statistics.median(busy) if busy else None,
-            "sm_max_mhz": max(mx) if mx else None,
-            "reasons": sorted(reasons),
+            "sm_max_mhz": self.max_mhz,
+            "reasons": sorted(self.reasons),
             "samples": len(sm),
         }
 
