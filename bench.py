@@ -152,10 +152,10 @@ class ClockSampler:
 
 
 def device_delay() -> None:
-    """Keep the GPU busy for ~0.2 ms (touching no memory) so that the launches of the timed region
+    """Keep the GPU busy for ~1 ms (touching no memory) so that the launches of the timed region
     are already queued when its first event is reached: the events then measure device time, not
     the host's enqueue latency (which the end-to-end figure covers)."""
-    torch.cuda._sleep(400_000)
+    torch.cuda._sleep(2_000_000)
 
 
 def cuda_ms(fn, stream=None) -> float:
