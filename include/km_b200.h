@@ -16,7 +16,9 @@
  *    stride of 0 broadcasts the same data to every batch (the reference receives such views
  *    from `Tensor.expand`, kernel_matmul/linear_operator.py:170-183).
  *  - Inputs are borrowed and never written.  Outputs and workspaces are caller-allocated; the
- *    library never allocates device memory and holds no device state.
+ *    library never calls an allocator.  The only device state it holds is the fixed scratch
+ *    array of km_bilinear_derivative_static_f32 (compiled into the library, 4 MiB per device)
+ *    and the cached device address of that array; every other entry point is stateless.
  *  - Launches are asynchronous on the `stream` argument (a cudaStream_t passed as void*).
  *    The band-construction calls do not synchronise either.
  *  - Return value: KM_OK or an error code; km_last_error() gives a message for the calling
@@ -44,6 +46,8 @@ extern "C" {
 #define KM_BLOCK_SIZE 128
 #define KM_MAX_BATCH_DIMS 4
 #define KM_MAX_PARAMS 4
+/* the product of the batch sizes of a call may not exceed this (refused with KM_ERR_UNSUPPORTED) */
+#define KM_MAX_BATCH_COUNT (1LL << 40)
 
 /* status codes */
 #define KM_OK 0
@@ -98,7 +102,9 @@ KM_API int km_matmul_f32(int kernel_type, const km_batch *batch, int64_t m, int6
  * pre-pass writes the rhs there as hi / lo fp16 tile images in the tensor core's shared-memory
  * layout, preceded by a 4-byte status word (0 = ok, non-zero = a bounded wait inside the
  * kernel gave up and the output is invalid; read it with km_workspace_status, which
- * synchronises the stream).  Replaces the same reference call as km_matmul_f32.
+ * synchronises the stream).  A CTA whose wait gave up also writes NaN to its rows of `out`, so a
+ * failure shows in everything computed from the result even if nobody reads the status word.
+ * Replaces the same reference call as km_matmul_f32.
  * ------------------------------------------------------------------------------------- */
 KM_API size_t km_matmul_tc_workspace_bytes(const km_batch *batch, int64_t n, int64_t k,
                                            const km_view *rhs);
@@ -175,8 +181,9 @@ KM_API int km_matmul_bwd_f32(int kernel_type, const km_batch *batch, int64_t m, 
  * km_bilinear_derivative_f32 / km_matmul_bwd_f32.
  * workspace: km_grad_tc_workspace_bytes(...) bytes of device memory, 256-byte aligned: a 4-byte
  * status word (0 = ok, non-zero = a bounded wait inside the kernel gave up and the gradient is
- * invalid; read it with km_workspace_status), the per-row-block partial sums, and the hi / lo
- * TF32 images of `right` written by a pre-pass.
+ * invalid; read it with km_workspace_status; the gradient of the affected batch is NaN as
+ * well), the per-row-block partial sums, and the hi / lo TF32 images of `right` written by a
+ * pre-pass.
  * ------------------------------------------------------------------------------------- */
 KM_API size_t km_grad_tc_workspace_bytes(const km_batch *batch, int64_t m, int64_t n, int64_t k,
                                          const km_view *right);
@@ -218,6 +225,14 @@ KM_API int km_matmul_bwd_tc_f32(int kernel_type, const km_batch *batch, int64_t 
  *    (cudaGetSymbolAddress, with that device current) and keeps it.  Make that first call
  *    before starting any stream capture on that device.  Device ordinals up to
  *    KM_STATIC_MAX_DEVICES - 1.
+ *  - The array is part of the library's device code: the CUDA runtime places it in device
+ *    memory when that code is first loaded on a device (with the default lazy loading: at the
+ *    first use of any gradient entry point there).  A host that hands all of HBM to its own
+ *    pool must make one gradient call on each device BEFORE doing so, or the load fails with
+ *    an out-of-memory error.
+ *  - The cached address belongs to the device's primary context.  After cudaDeviceReset, or
+ *    under another context, it is stale: this entry point supports the primary context of a
+ *    process that does not reset its devices.
  * ------------------------------------------------------------------------------------- */
 #define KM_STATIC_GRAD_UNITS 262144
 #define KM_STATIC_MAX_DEVICES 64
@@ -314,6 +329,10 @@ KM_API int km_transpose_ranges_i32(int64_t B, int64_t R, const int32_t *start, c
 KM_API int km_count_entries(const km_batch *batch, int64_t m, int64_t n, const km_view *start,
                      const km_view *end, int64_t *count, void *stream);
 
+/* `iters` of the two calibration calls below may not exceed this (a mistaken argument must not
+ * become a kernel that never ends on a shared GPU). */
+#define KM_PROBE_MAX_ITERS (1LL << 24)
+
 /* FP32-pipe calibration: runs `iters` dependent-chain-free FFMA rounds on every SM and writes a
  * checksum to *sink (device float, may be NULL).  flops = 2 * threads * iters * 64 are returned
  * in *flops_out (host).  No reference counterpart; bench.py times it to obtain the measured
@@ -325,6 +344,78 @@ KM_API int km_probe_fp32_peak(int64_t iters, float *sink, double *flops_out, voi
  * counterpart; bench.py times it to obtain the measured SFU rate, which bounds the tensor-core
  * kernels (their FP32-pipe work per entry is small; kappa costs 1-3 SFU operations per entry). */
 KM_API int km_probe_sfu_peak(int64_t iters, float *sink, double *ops_out, void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Vector kernels of the row-sharded conjugate-gradient solve (K + sigma^2 I) X = Y.  No reference
+ * counterpart: the reference has no CG, it inherits LinearOperator.solve from the third-party
+ * linear_operator package (tests/test_linear_operator.py:9-38).  One iteration is
+ *     km_matmul_rows_f32 (K p on the rank's rows)  ->  km_cg_q_dots_f32  ->  km_cg_segment_sums_f32
+ *     -> [all-gather]  ->  km_cg_update_xr_f32  ->  km_cg_segment_sums_f32  ->  [all-gather]
+ *     ->  km_cg_update_p_f32.
+ * All vectors are fp32, (n, k) row-major with row stride k, indexed by GLOBAL row; a rank owns
+ * the rows [row0, row1) (row0 a multiple of 128) and keeps r and p valid on [lo, hi), the columns
+ * its band reads.  Inner products: one fp32 partial per 128-row block, fp64 sums per segment of
+ * `seg_blocks` consecutive row blocks, and the gathered segment sums (seg_ranks records,
+ * seg_rank_stride_bytes apart, of seg_slots x k doubles each; unused slots zero) added in record
+ * order -- the same numbers for any number of ranks whose windows are whole segments.
+ * ------------------------------------------------------------------------------------- */
+
+/* block_partials[(row - row0) / 128][c] = sum over the block's rows of a[row, c] * b[row, c] */
+KM_API int km_cg_block_dots_f32(int64_t k, const float *a, const float *b, int64_t row0, int64_t row1,
+                                float *block_partials, void *stream);
+
+/* kp[row, :] (in: K p) becomes q = K p + sigma2 * p on the own rows; block partials of p . q; the
+ * first top_rows and the last bottom_rows rows of q are also copied to send_top / send_bottom
+ * (what the neighbouring ranks need of q). */
+KM_API int km_cg_q_dots_f32(int64_t k, float *kp, const float *p, float sigma2, int64_t row0, int64_t row1,
+                            float *block_partials, float *send_top, int64_t top_rows, float *send_bottom,
+                            int64_t bottom_rows, void *stream);
+
+/* seg_sums[s][c] = sum of block_partials[blk][c] over the blocks [s * seg_blocks, (s + 1) * seg_blocks) */
+KM_API int km_cg_segment_sums_f32(int64_t k, const float *block_partials, int64_t blocks, int64_t seg_blocks,
+                                  double *seg_sums, void *stream);
+
+/* start of a solve: rs[c] = total of the gathered segment sums of y . y, ynorm[c] = sqrt(rs[c]) */
+KM_API int km_cg_init_scalars_f32(int64_t k, const void *seg_sums, int64_t seg_rank_stride_bytes, int32_t seg_ranks,
+                                  int32_t seg_slots, float *rs, float *ynorm, void *stream);
+
+/* alpha = rs / (p . q) from the gathered sums; x += alpha p on the own rows; r -= alpha q on
+ * [lo, hi), with q of a row below / above the own window read from
+ * q_below[(row - below_origin) * k + c] / q_above[(row - above_origin) * k + c]; block partials of
+ * the new r . r over the own rows. */
+KM_API int km_cg_update_xr_f32(int64_t k, float *x, float *r, const float *p, const float *q_own,
+                               const float *q_below, int64_t below_origin, const float *q_above,
+                               int64_t above_origin, int64_t row0, int64_t row1, int64_t lo, int64_t hi,
+                               const void *pq_seg_sums, int64_t seg_rank_stride_bytes, int32_t seg_ranks,
+                               int32_t seg_slots, const float *rs, float *block_partials, void *stream);
+
+/* rs_new = total of the gathered sums of r . r; beta = rs_new / rs_old; p = r + beta p on [lo, hi);
+ * rs_new[k] is stored (rs_old and rs_new must be different buffers) and, if history_row is not
+ * NULL, history_row[c] = sqrt(rs_new[c]) / ynorm[c]. */
+KM_API int km_cg_update_p_f32(int64_t k, float *p, const float *r, int64_t lo, int64_t hi, const void *rr_seg_sums,
+                              int64_t seg_rank_stride_bytes, int32_t seg_ranks, int32_t seg_slots,
+                              const float *rs_old, float *rs_new, const float *ynorm, float *history_row,
+                              void *stream);
+
+/* ---------------------------------------------------------------------------------------
+ * Self-tests of the give-up path of the tensor-core kernels.  No reference counterpart (the
+ * reference's debug build synchronises and throws on a CUDA error,
+ * native/common/gpu_assert.cuh:6-23; its kernels have no hand-offs that could stall).
+ *
+ * Every hand-off inside km_matmul_tc_f32, the *_tc_f32 gradients and the tensor-core batch sum
+ * of km_matmul_rows_f32 is an mbarrier wait with a poll limit.  When the limit runs out the CTA
+ * stops, waits for its own copies and MMAs in flight, releases its tensor memory, sets the
+ * status word and writes NaN results; it never spins for ever and never traps.
+ *
+ * km_selftest_bounded_wait launches one warp that waits, with `polls` polls, on a barrier nobody
+ * arrives at and writes 1 to *status (device int32) when the wait gave up, 0 if it did not.
+ * km_selftest_set_wait_polls(polls) sets the poll limit that later launches of the tensor-core
+ * kernels of this process use: 0 makes every wait that is not complete at its first test give
+ * up at once, -1 restores the default.  A process-wide setting for tests; not thread-safe with
+ * respect to launches in flight on other host threads.
+ * ------------------------------------------------------------------------------------- */
+KM_API int km_selftest_bounded_wait(int64_t polls, int32_t *status, void *stream);
+KM_API int km_selftest_set_wait_polls(int64_t polls);
 
 #ifdef __cplusplus
 }

@@ -100,6 +100,23 @@ def _load() -> ctypes.CDLL:
     lib.km_probe_fp32_peak.argtypes = [i64, vp, ctypes.POINTER(ctypes.c_double), vp]
     lib.km_probe_sfu_peak.restype = ctypes.c_int
     lib.km_probe_sfu_peak.argtypes = [i64, vp, ctypes.POINTER(ctypes.c_double), vp]
+    f32 = ctypes.c_float
+    lib.km_cg_block_dots_f32.restype = ctypes.c_int
+    lib.km_cg_block_dots_f32.argtypes = [i64, vp, vp, i64, i64, vp, vp]
+    lib.km_cg_q_dots_f32.restype = ctypes.c_int
+    lib.km_cg_q_dots_f32.argtypes = [i64, vp, vp, f32, i64, i64, vp, vp, i64, vp, i64, vp]
+    lib.km_cg_segment_sums_f32.restype = ctypes.c_int
+    lib.km_cg_segment_sums_f32.argtypes = [i64, vp, i64, i64, vp, vp]
+    lib.km_cg_init_scalars_f32.restype = ctypes.c_int
+    lib.km_cg_init_scalars_f32.argtypes = [i64, vp, i64, i32, i32, vp, vp, vp]
+    lib.km_cg_update_xr_f32.restype = ctypes.c_int
+    lib.km_cg_update_xr_f32.argtypes = [i64, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, vp, i64, i32, i32, vp, vp, vp]
+    lib.km_cg_update_p_f32.restype = ctypes.c_int
+    lib.km_cg_update_p_f32.argtypes = [i64, vp, vp, i64, i64, vp, i64, i32, i32, vp, vp, vp, vp, vp]
+    lib.km_selftest_bounded_wait.restype = ctypes.c_int
+    lib.km_selftest_bounded_wait.argtypes = [i64, vp, vp]
+    lib.km_selftest_set_wait_polls.restype = ctypes.c_int
+    lib.km_selftest_set_wait_polls.argtypes = [i64]
     return lib
 
 
@@ -112,7 +129,9 @@ EXPORTED = [
     "km_bilinear_derivative_f32", "km_bilinear_derivative_static_f32", "km_matmul_bwd_f32", "km_dense_f32", "km_dense_bwd_f32",
     "km_index_f32", "km_index_bwd_workspace_bytes", "km_index_bwd_f32", "km_make_ranges_f32",
     "km_make_ranges_symmetric_f32", "km_make_ranges_symmetric_cutoffs_f32", "km_transpose_ranges_i32", "km_count_entries",
-    "km_probe_fp32_peak", "km_probe_sfu_peak",
+    "km_probe_fp32_peak", "km_probe_sfu_peak", "km_selftest_bounded_wait", "km_selftest_set_wait_polls",
+    "km_cg_block_dots_f32", "km_cg_q_dots_f32", "km_cg_segment_sums_f32", "km_cg_init_scalars_f32", "km_cg_update_xr_f32",
+    "km_cg_update_p_f32",
 ]
 
 

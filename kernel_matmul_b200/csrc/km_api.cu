@@ -1,9 +1,10 @@
 // Library-wide pieces of the C ABI: error reporting, batch validation, the entry counter and
 // the FP32-pipe calibration kernel.
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 
-#include "km_common.cuh"
+#include "km_tcgen05.cuh"
 
 namespace km {
 
@@ -29,9 +30,30 @@ int make_batch(const km_batch *in, Batch *out) {
     for (int d = 0; d < KM_MAX_BATCH_DIMS; d++) {
         out->size[d] = d < in->ndim ? in->size[d] : 1;
         KM_REQUIRE(out->size[d] >= 0, KM_ERR_INVALID_ARGUMENT, "negative batch size");
+        // the product of the sizes must stay far inside int64: every launcher multiplies it by row
+        // blocks and record sizes
+        KM_REQUIRE(out->size[d] == 0 || out->count <= (int64_t)KM_MAX_BATCH_COUNT / out->size[d], KM_ERR_UNSUPPORTED,
+                   "batch of more than %lld kernels", (long long)KM_MAX_BATCH_COUNT);
         out->count *= out->size[d];
     }
     return KM_OK;
+}
+
+static std::atomic<unsigned> g_wait_polls{TC_WAIT_POLLS};
+
+unsigned current_wait_polls() { return g_wait_polls.load(std::memory_order_relaxed); }
+
+// One CTA of one warp waits, with the given poll limit, on an mbarrier that nobody arrives at and
+// records whether the wait gave up: the hand-off failure of the tensor-core kernels in isolation.
+__global__ void selftest_wait_kernel(unsigned polls, int *status) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    const bool ok = mbar_wait_warp(&bar, 0u, polls);
+    if (threadIdx.x == 0) *status = ok ? 0 : 1;
 }
 
 __global__ void count_entries_kernel(Batch batch, int64_t m, int n, int64_t row_blocks,
@@ -115,7 +137,8 @@ extern "C" int km_count_entries(const km_batch *batch, int64_t m, int64_t n, con
 
 extern "C" int km_probe_fp32_peak(int64_t iters, float *sink, double *flops_out, void *stream) {
     using namespace km;
-    KM_REQUIRE(iters > 0, KM_ERR_INVALID_ARGUMENT, "km_probe_fp32_peak: iters must be positive");
+    KM_REQUIRE(iters > 0 && iters <= KM_PROBE_MAX_ITERS, KM_ERR_INVALID_ARGUMENT,
+               "km_probe_fp32_peak: iters must be in [1, %lld]", (long long)KM_PROBE_MAX_ITERS);
     int dev = 0, sms = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return cuda_fail(err, "cudaGetDevice");
@@ -130,7 +153,8 @@ extern "C" int km_probe_fp32_peak(int64_t iters, float *sink, double *flops_out,
 
 extern "C" int km_probe_sfu_peak(int64_t iters, float *sink, double *ops_out, void *stream) {
     using namespace km;
-    KM_REQUIRE(iters > 0, KM_ERR_INVALID_ARGUMENT, "km_probe_sfu_peak: iters must be positive");
+    KM_REQUIRE(iters > 0 && iters <= KM_PROBE_MAX_ITERS, KM_ERR_INVALID_ARGUMENT,
+               "km_probe_sfu_peak: iters must be in [1, %lld]", (long long)KM_PROBE_MAX_ITERS);
     int dev = 0, sms = 0;
     cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return cuda_fail(err, "cudaGetDevice");
@@ -140,5 +164,23 @@ extern "C" int km_probe_sfu_peak(int64_t iters, float *sink, double *ops_out, vo
     sfu_peak_kernel<<<blocks, threads, 0, static_cast<cudaStream_t>(stream)>>>(iters, sink);
     KM_CHECK_LAUNCH("km_probe_sfu_peak launch");
     if (ops_out) *ops_out = (double)blocks * threads * (double)iters * 8.0;
+    return KM_OK;
+}
+
+extern "C" int km_selftest_set_wait_polls(int64_t polls) {
+    using namespace km;
+    KM_REQUIRE(polls >= -1 && polls <= (int64_t)TC_WAIT_POLLS, KM_ERR_INVALID_ARGUMENT,
+               "km_selftest_set_wait_polls: polls must be -1 (default) or in [0, %u]", TC_WAIT_POLLS);
+    g_wait_polls.store(polls < 0 ? TC_WAIT_POLLS : (unsigned)polls, std::memory_order_relaxed);
+    return KM_OK;
+}
+
+extern "C" int km_selftest_bounded_wait(int64_t polls, int32_t *status, void *stream) {
+    using namespace km;
+    KM_REQUIRE(status != nullptr, KM_ERR_INVALID_ARGUMENT, "km_selftest_bounded_wait: null status pointer");
+    KM_REQUIRE(polls >= 0 && polls <= 1 << 16, KM_ERR_INVALID_ARGUMENT,
+               "km_selftest_bounded_wait: polls must be in [0, 65536]");
+    selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>((unsigned)polls, status);
+    KM_CHECK_LAUNCH("km_selftest_bounded_wait launch");
     return KM_OK;
 }

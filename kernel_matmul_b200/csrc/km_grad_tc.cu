@@ -20,7 +20,8 @@
 //
 // Reduction and chain rule are those of km_grad.cu: one partial record per (batch, row block),
 // then the fixed-order fp64 sum of launch_grad_finish.  Every mbarrier wait is bounded; a
-// give-up is reported through the status word of the workspace.
+// give-up is reported through the status word of the workspace and makes the CTA's partial
+// record, and so the gradient of its batch, NaN.
 #include <type_traits>
 
 #include "km_tcgen05.cuh"
@@ -47,6 +48,7 @@ struct GradTcArgs {
     int64_t image_slot_stride;  // floats between batch slots (0: right shared by all batches)
     float *partials;            // [batch.count][row_blocks][kblocks][KM_MAX_PARAMS]
     int *status;
+    unsigned wait_polls;        // poll limit of every hand-off wait
 };
 
 // Pre-pass: right -> per (image slot, 64-column tile) the K-major core-matrix layout of a B
@@ -98,6 +100,7 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
     __shared__ __align__(8) uint64_t bar_full[GT_MAX_SLOTS];   // right image + x2 of a slot landed
     __shared__ __align__(8) uint64_t bar_dfull[GT_D_STAGES];   // coefficient tile complete (tcgen05.commit)
     __shared__ __align__(8) uint64_t bar_dfree[GT_D_STAGES];   // coefficient tile consumed
+    __shared__ __align__(8) uint64_t bar_drain;                // give-up path: every issued MMA has completed
     __shared__ uint32_t tmem_base_slot;
     __shared__ int fail_flag;
     __shared__ float warp_sums[WARPS][KM_MAX_PARAMS];
@@ -149,6 +152,7 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
             mbar_init(&bar_dfull[s], 1);
             mbar_init(&bar_dfree[s], WARPS);
         }
+        mbar_init(&bar_drain, 1);
         fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -206,7 +210,9 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
             }
         };
         load_ahead(0);
+        int fetched = 0, landed = 0;  // tiles whose copies were issued / (set when a wait gives up) were seen complete
         auto fetch = [&](int t) {
+            fetched = t + 1;
             const int sl = t % ns;
             const int64_t tile = tile_lo + t;
             if (lane == 0) {
@@ -248,12 +254,13 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
             bool ok = true;
             // the stage is free once tile t - 2 has been consumed; that also frees its slot
             if (t >= GT_D_STAGES) {
-                ok = mbar_wait(&bar_dfree[ds], (unsigned)(((t >> 1) - 1) & 1));
+                ok = mbar_wait(&bar_dfree[ds], (unsigned)(((t >> 1) - 1) & 1), a.wait_polls);
                 if (__all_sync(0xffffffffu, ok) && t - GT_D_STAGES + ns < tiles) fetch(t - GT_D_STAGES + ns);
             }
-            if (ok) ok = mbar_wait(&bar_full[sl], (unsigned)((t / ns) & 1));
+            if (ok) ok = mbar_wait(&bar_full[sl], (unsigned)((t / ns) & 1), a.wait_polls);
             if (!__all_sync(0xffffffffu, ok)) {
                 failed = true;
+                landed = t;
                 break;
             }
             tc_fence_after();
@@ -290,7 +297,12 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
             }
             __syncwarp();
         }
-        if (failed && lane == 0) atomicExch(&fail_flag, 1);
+        if (failed) {
+            // give-up path: the bulk copies that were issued and not yet seen complete are awaited
+            // (with the full poll limit: they do arrive) before the CTA's shared memory is given up
+            for (int t = landed; t < fetched; t++) mbar_wait(&bar_full[t % ns], (unsigned)((t / ns) & 1), TC_WAIT_POLLS);
+            if (lane == 0) atomicExch(&fail_flag, 1);
+        }
         __syncwarp();
     } else {
         // ------------------------------------------------------------------------ consumers
@@ -308,8 +320,8 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
         for (int t = 0; t < tiles; t++) {
             const int sl = t % ns;
             const int ds = t & 1;
-            if (!mbar_wait_warp(&bar_dfull[ds], (unsigned)((t >> 1) & 1)) ||
-                !mbar_wait_warp(&bar_full[sl], (unsigned)((t / ns) & 1))) {
+            if (!mbar_wait_warp(&bar_dfull[ds], (unsigned)((t >> 1) & 1), a.wait_polls) ||
+                !mbar_wait_warp(&bar_full[sl], (unsigned)((t / ns) & 1), a.wait_polls)) {
                 failed = true;
                 break;
             }
@@ -401,10 +413,23 @@ __global__ void __launch_bounds__(128 * G + 32, G == 4 ? 2 : GT_MIN_CTAS) grad_t
         if (tid < NS) {
 #pragma unroll
             for (int w = 0; w < WARPS; w++) v += warp_sums[w][tid];
+            // a wait gave up: the record becomes NaN, and with it the gradient of this batch
+            if (fail_flag) v = __int_as_float(0x7fc00000);
         }
         a.partials[((b * a.row_blocks + r) * a.kblocks + kb) * KM_MAX_PARAMS + tid] = v;
     }
-    if (is_ctl_warp) tmem_free(tmem_base, GT_TMEM_COLS);
+    if (is_ctl_warp) {
+        if (fail_flag) {
+            // after a give-up MMAs may still be running: one commit covers everything this thread
+            // has issued; tensor memory is released only when it has completed
+            if (lane == 0) {
+                mma_commit(&bar_drain);
+                mbar_wait(&bar_drain, 0u, TC_WAIT_POLLS);
+            }
+            __syncwarp();
+        }
+        tmem_free(tmem_base, GT_TMEM_COLS);
+    }
 }
 
 static int64_t grad_tc_kblocks(int64_t k) { return std::max<int64_t>(1, ceil_div(k, GT_MAX_KP)); }
@@ -469,6 +494,7 @@ static int grad_tc_entry(const char *name, int kernel_type, const km_batch *batc
     a.kp = grad_tc_kp(k);
     a.kblocks = (int)grad_tc_kblocks(k);
     a.slots = a.kp <= 16 ? 4 : 3;
+    a.wait_polls = current_wait_polls();
     a.row_blocks = ceil_div(m, KM_BLOCK_SIZE);
     a.x1 = make_view<const float>(x1, a.batch);
     a.x2 = make_view<const float>(x2, a.batch);

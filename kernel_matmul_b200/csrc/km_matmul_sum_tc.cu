@@ -41,6 +41,7 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
     __shared__ __align__(8) uint64_t bar_bready[2];         // psi tile written
     __shared__ __align__(8) uint64_t bar_cfull[2];          // C tile complete (tcgen05.commit)
     __shared__ __align__(8) uint64_t bar_cfree[2];          // C tile consumed
+    __shared__ __align__(8) uint64_t bar_drain;             // give-up path: every issued MMA has completed
     __shared__ uint32_t tmem_base_slot;
     __shared__ int fail_flag;
     __shared__ float w_tab[SUM_TC_MAX_COMPONENTS], s_tab[SUM_TC_MAX_COMPONENTS];
@@ -105,6 +106,7 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
             mbar_init(&bar_cfull[s], 1);
             mbar_init(&bar_cfree[s], 4);
         }
+        mbar_init(&bar_drain, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (is_ctl_warp) tmem_alloc(&tmem_base_slot, ST_TMEM_COLS);
@@ -152,10 +154,10 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
             bool ok = true;
             if (t >= 2) {
                 // C stage free = tile t - 2 consumed, which also frees its input stage
-                ok = mbar_wait(&bar_cfree[st], (unsigned)(((t >> 1) - 1) & 1));
+                ok = mbar_wait(&bar_cfree[st], (unsigned)(((t >> 1) - 1) & 1), a.wait_polls);
                 if (__all_sync(0xffffffffu, ok) && t + 2 < tiles) fetch(t + 2);
             }
-            if (ok) ok = mbar_wait(&bar_bready[st], (unsigned)((t >> 1) & 1));
+            if (ok) ok = mbar_wait(&bar_bready[st], (unsigned)((t >> 1) & 1), a.wait_polls);
             if (!__all_sync(0xffffffffu, ok)) {
                 failed = true;
                 break;
@@ -253,7 +255,7 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
         };
 
         if (tiles > 0) {
-            if (!mbar_wait_warp(&bar_in[0], 0u)) failed = true;
+            if (!mbar_wait_warp(&bar_in[0], 0u, a.wait_polls)) failed = true;
             if (!failed) generate(0);
         }
         for (int t = 0; t < tiles && !failed; t++) {
@@ -261,13 +263,13 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
             if (t + 1 < tiles) {
                 // (the psi stage of tile t + 1 was read by the MMAs of tile t - 1, whose completion
                 // this thread has seen when it consumed tile t - 1)
-                if (!mbar_wait_warp(&bar_in[(t + 1) % ST_IN_STAGES], (unsigned)(((t + 1) / ST_IN_STAGES) & 1))) {
+                if (!mbar_wait_warp(&bar_in[(t + 1) % ST_IN_STAGES], (unsigned)(((t + 1) / ST_IN_STAGES) & 1), a.wait_polls)) {
                     failed = true;
                     break;
                 }
                 generate(t + 1);
             }
-            if (!mbar_wait_warp(&bar_cfull[st], (unsigned)((t >> 1) & 1))) {
+            if (!mbar_wait_warp(&bar_cfull[st], (unsigned)((t >> 1) & 1), a.wait_polls)) {
                 failed = true;
                 break;
             }
@@ -336,7 +338,18 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
                 }
         }
     }
-    if (is_ctl_warp) tmem_free(tmem_base, ST_TMEM_COLS);
+    if (is_ctl_warp) {
+        if (fail_flag) {
+            // after a give-up MMAs may still be running: one commit covers everything this thread
+            // has issued; tensor memory is released only when it has completed
+            if (lane == 0) {
+                mma_commit(&bar_drain);
+                mbar_wait(&bar_drain, 0u, TC_WAIT_POLLS);
+            }
+            __syncwarp();
+        }
+        tmem_free(tmem_base, ST_TMEM_COLS);
+    }
 }
 
 template <int KB>
@@ -362,6 +375,7 @@ int launch_matmul_sum_tc(const SumTcArgs &a, cudaStream_t stream) {
     // more than 64 components: chunks of 64, each launch adding to the result of the previous ones
     // (launches on one stream run in order)
     SumTcArgs chunk = a;
+    chunk.wait_polls = current_wait_polls();
     for (int64_t b0 = 0; b0 < a.batch.count; b0 += SUM_TC_MAX_COMPONENTS) {
         chunk.comp_begin = b0;
         chunk.comp_count = std::min<int64_t>(SUM_TC_MAX_COMPONENTS, a.batch.count - b0);

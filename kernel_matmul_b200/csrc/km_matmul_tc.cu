@@ -32,7 +32,8 @@
 //
 // Four CTAs share an SM at N = 16 (128 tensor-memory columns each; three at N = 32, two at
 // N = 64, one with 512 generator threads at N = 128).  All hand-offs are mbarriers; every
-// wait is bounded and a give-up is reported through the status word of the workspace.
+// wait is bounded; a give-up is reported through the status word of the workspace and turns the
+// CTA's output rows into NaN.
 #include <cuda_fp16.h>
 
 #include "km_tcgen05.cuh"
@@ -167,6 +168,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
     __shared__ __align__(8) uint64_t bar_empty[TC_A_STAGES];  // MMAs reading an A stage are done
     __shared__ __align__(8) uint64_t bar_acc[2];              // accumulator group complete
     __shared__ __align__(8) uint64_t bar_free[2];             // accumulators added to the registers
+    __shared__ __align__(8) uint64_t bar_drain;               // give-up path: every issued MMA has completed
     __shared__ uint32_t tmem_base_slot;
     __shared__ int fail_flag;
 
@@ -224,6 +226,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             mbar_init(&bar_acc[i], 1);
             mbar_init(&bar_free[i], 4 * G);
         }
+        mbar_init(&bar_drain, 1);
         fail_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -265,7 +268,9 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             }
         };
         if constexpr (KernelFn<KT>::PHASE) load_ahead(0);
+        int fetched = 0, landed = 0;  // slots whose copies were issued / (set when a wait gives up) were seen complete
         auto fetch = [&](int sr) {
+            fetched = sr + 1;
             const int sl = sr % TC_SLOTS;
             const int64_t sup = super_lo + sr;
             float *xs = slot_x2(sl);
@@ -319,12 +324,13 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             const bool slot_first = t == 0 || q == 0;
             const bool slot_last = q == TC_SUPER - 1 || t == tiles - 1;
             bool ok = true;
-            if (slot_first) ok = mbar_wait(&bar_full[sl], (unsigned)((sr / TC_SLOTS) & 1));
+            if (slot_first) ok = mbar_wait(&bar_full[sl], (unsigned)((sr / TC_SLOTS) & 1), a.wait_polls);
             // the accumulator must have been collected by every generator warp
-            if (ok && grp_first && grp >= 2) ok = mbar_wait(&bar_free[ai], (unsigned)(((grp >> 1) - 1) & 1));
-            if (ok) ok = mbar_wait(&bar_ready[s], (unsigned)(use & 1));
+            if (ok && grp_first && grp >= 2) ok = mbar_wait(&bar_free[ai], (unsigned)(((grp >> 1) - 1) & 1), a.wait_polls);
+            if (ok) ok = mbar_wait(&bar_ready[s], (unsigned)(use & 1), a.wait_polls);
             if (!__all_sync(0xffffffffu, ok)) {
                 failed = true;
+                landed = sr;
                 break;
             }
             tc_fence_after();
@@ -348,9 +354,10 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             // after the first tile of a slot: the previous slot is re-filled once its MMAs are done
             if (slot_first && sr >= 1 && sr - 1 + TC_SLOTS < supers) {
                 const int prev = sr - 1;
-                ok = mbar_wait(&bar_sfree[prev % TC_SLOTS], (unsigned)((prev / TC_SLOTS) & 1));
+                ok = mbar_wait(&bar_sfree[prev % TC_SLOTS], (unsigned)((prev / TC_SLOTS) & 1), a.wait_polls);
                 if (!__all_sync(0xffffffffu, ok)) {
                     failed = true;
+                    landed = sr;
                     break;
                 }
                 fetch(prev + TC_SLOTS);
@@ -364,7 +371,14 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
                 grp++;
             }
         }
-        if (failed && lane == 0) atomicExch(&fail_flag, 1);
+        if (failed) {
+            // Give-up path: nothing asynchronous may still be running when the CTA exits and its
+            // shared memory goes to the next CTA.  The bulk copies that were issued and not yet
+            // seen complete are awaited (with the full poll limit: they do arrive).
+            for (int sr = landed; sr < fetched; sr++)
+                mbar_wait(&bar_full[sr % TC_SLOTS], (unsigned)((sr / TC_SLOTS) & 1), TC_WAIT_POLLS);
+            if (lane == 0) atomicExch(&fail_flag, 1);
+        }
         // no cp.async may be in flight when the CTA exits
         cp_async_wait<0>();
         __syncwarp();
@@ -397,13 +411,13 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             const int sl = sr % TC_SLOTS;
             const int s = t % TC_A_STAGES, use = t / TC_A_STAGES;
             const int grp = t / TC_PROMO, ai = grp & 1;
-            if ((t == 0 || q == 0) && !mbar_wait_warp(&bar_full[sl], (unsigned)((sr / TC_SLOTS) & 1))) {
+            if ((t == 0 || q == 0) && !mbar_wait_warp(&bar_full[sl], (unsigned)((sr / TC_SLOTS) & 1), a.wait_polls)) {
                 failed = true;
                 break;
             }
             // an accumulator that is about to be reused is first added to the registers
             if ((t % TC_PROMO) == 0 && grp >= 2) {
-                if (!mbar_wait_warp(&bar_acc[ai], (unsigned)((grp / 2 - 1) & 1))) {
+                if (!mbar_wait_warp(&bar_acc[ai], (unsigned)((grp / 2 - 1) & 1), a.wait_polls)) {
                     failed = true;
                     break;
                 }
@@ -413,7 +427,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             }
             // stage s must have been read by the MMAs of tile t - TC_A_STAGES
             if (use > 0) {
-                if (!mbar_wait_warp(&bar_empty[s], (unsigned)((use - 1) & 1))) {
+                if (!mbar_wait_warp(&bar_empty[s], (unsigned)((use - 1) & 1), a.wait_polls)) {
                     failed = true;
                     break;
                 }
@@ -476,7 +490,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
         // drain: the last two groups still sit in tensor memory
         const int groups = (tiles + TC_PROMO - 1) / TC_PROMO;
         for (int grp = max(0, groups - 2); grp < groups && !failed; grp++) {
-            if (!mbar_wait_warp(&bar_acc[grp & 1], (unsigned)((grp / 2) & 1))) {
+            if (!mbar_wait_warp(&bar_acc[grp & 1], (unsigned)((grp / 2) & 1), a.wait_polls)) {
                 failed = true;
                 break;
             }
@@ -488,7 +502,14 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
     tc_fence_before();
     __syncthreads();
     if (fail_flag) {
+        // a wait gave up: the status word says so, and the rows of this CTA become NaN so that the
+        // failure also shows in whatever is computed from the result, without a host synchronisation
         if (tid == 0) atomicExch(a.status, 1);
+        const int64_t row = r * KM_BLOCK_SIZE + row_local;
+        if (!is_ctl_warp && g == 0 && row < a.m) {
+            float *orow = out + (row - a.rb_begin * KM_BLOCK_SIZE) * a.out.s0 + (int64_t)kb * N * a.out.s1;
+            for (int c = 0; c < (int)k_here; c++) orow[c * a.out.s1] = __int_as_float(0x7fc00000);
+        }
     } else if (!is_ctl_warp) {
         const int64_t row = r * KM_BLOCK_SIZE + row_local;
         if (row < a.m) {
@@ -516,7 +537,18 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             }
         }
     }
-    if (is_ctl_warp) tmem_free(tmem_base, TC_TMEM_COLS);
+    if (is_ctl_warp) {
+        if (fail_flag) {
+            // after a give-up MMAs may still be running: one commit covers everything this thread
+            // has issued; tensor memory is released only when it has completed
+            if (lane == 0) {
+                mma_commit(&bar_drain);
+                mbar_wait(&bar_drain, 0u, TC_WAIT_POLLS);
+            }
+            __syncwarp();
+        }
+        tmem_free(tmem_base, TC_TMEM_COLS);
+    }
 }
 
 // workspace: [status, 256 B][per (image slot, column block): column maxima and inverse scales][images]
@@ -572,6 +604,7 @@ static int tc_matmul(int kernel_type, TcArgs a, const View<const float> &rhs, vo
     a.tiles = supers;                         // 64-column groups per image
     a.n_pad = n_pad;
     a.col_inv_scale = reinterpret_cast<const float *>(scales) + TC_MAX_N;
+    a.wait_polls = current_wait_polls();
     cudaError_t err = cudaMemsetAsync(scales, 0, tc_scale_bytes(slots, kblocks), s);
     if (err != cudaSuccess) return cuda_fail(err, "km_matmul_tc_f32 cudaMemsetAsync");
     const unsigned max_blocks = (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(a.n, 16), 148 * 8));

@@ -257,6 +257,8 @@ __global__ void __launch_bounds__(1024) transpose_fix_kernel(int64_t C, int x1_s
     }
 }
 
+// One thread per item on at most 2^20 blocks of 256 threads: callers refuse more items.
+constexpr int64_t KM_RANGES_MAX_ITEMS = (1LL << 20) * 256;
 static inline unsigned grid_for(int64_t total, int threads) {
     return (unsigned)std::max<int64_t>(1, std::min<int64_t>(ceil_div(total, threads), 1 << 20));
 }
@@ -271,6 +273,9 @@ static int make_ranges_common(const char *name, int64_t B, int64_t m, int64_t n,
     if (B == 0 || R == 0) return KM_OK;
     KM_REQUIRE(x1 && x2 && start && end && flags, KM_ERR_INVALID_ARGUMENT, "%s: null pointer", name);
     KM_REQUIRE(B <= 0x7fffffffLL, KM_ERR_UNSUPPORTED, "%s: too many batch rows", name);
+    // (the per-element kernels run one thread per (batch row, row block) on grids of at most 2^20 blocks)
+    KM_REQUIRE(B <= KM_RANGES_MAX_ITEMS / R, KM_ERR_UNSUPPORTED, "%s: more than %lld (batch row, row block) pairs", name,
+               (long long)KM_RANGES_MAX_ITEMS);
     fill_flags_kernel<<<grid_for(B, 256), 256, 0, s>>>(B, flags);
     if (n > 1) check_sorted_kernel<<<(unsigned)std::min<int64_t>(ceil_div(B * n, 256), 148 * 16), 256, 0, s>>>(B, n, x2, x2s, flags);
     range_bounds_kernel<<<grid_for(B * R, 256), 256, 0, s>>>(B, m, n, R, x1, x1s, x2, x2s, cutoff, cutoffs, block, step,
@@ -326,6 +331,8 @@ extern "C" int km_transpose_ranges_i32(int64_t B, int64_t R, const int32_t *star
     KM_REQUIRE(start_t && end_t && (R == 0 || (start && end)), KM_ERR_INVALID_ARGUMENT,
                "km_transpose_ranges_i32: null pointer");
     KM_REQUIRE(B <= 0x7fffffffLL, KM_ERR_UNSUPPORTED, "km_transpose_ranges_i32: too many batch rows");
+    KM_REQUIRE(B <= KM_RANGES_MAX_ITEMS / C && (R == 0 || B <= KM_RANGES_MAX_ITEMS / R), KM_ERR_UNSUPPORTED,
+               "km_transpose_ranges_i32: more than %lld (batch row, block) pairs", (long long)KM_RANGES_MAX_ITEMS);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     transpose_init_kernel<<<grid_for(B * C, 256), 256, 0, s>>>(B * C, (int)x1_size, start_t, end_t);
     if (R > 0)

@@ -23,6 +23,7 @@ struct TcArgs {
     int64_t image_slot_stride;   // non-zero: every batch has its own images (0: rhs shared by all batches)
     const float *col_inv_scale;  // per (image slot, column block): inverse of the per-column rhs scales
     int *status;
+    unsigned wait_polls;         // poll limit of every hand-off wait (TC_WAIT_POLLS unless a self-test lowered it)
 };
 
 // Number of distinct rhs images: 1 when every batch shares one rhs (all batch strides 0).
@@ -33,6 +34,9 @@ inline int64_t tc_slots(const Batch &b, const View<const float> &rhs) {
 }
 
 constexpr unsigned TC_WAIT_POLLS = 1u << 18;  // each poll may block for a short, system-defined time
+// Poll limit the launchers put into the kernel arguments: TC_WAIT_POLLS, or what
+// km_selftest_set_wait_polls() set (km_api.cu).
+unsigned current_wait_polls();
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -48,7 +52,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
 // Bounded wait for the phase with the given parity.  false = gave up.  A non-blocking test comes
 // first (the phase is usually complete already); then try_wait, which suspends the thread for a
 // short, system-defined time per poll (an explicit suspend-time hint only added instructions).
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity, unsigned polls) {
     const uint32_t addr = smem_u32(bar);
     {
         // the phase is usually complete already: a non-blocking test first
@@ -64,7 +68,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
             : "memory");
         if (done) return true;
     }
-    for (unsigned poll = 0; poll < TC_WAIT_POLLS; poll++) {
+    for (unsigned poll = 0; poll < polls; poll++) {
         uint32_t done;
         asm volatile(
             "{\n\t"
@@ -81,8 +85,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, unsigned parity) {
 }
 // The same wait with a warp-uniform outcome (all 32 lanes must call it): false if any lane gave
 // up, so that a warp leaves its loop as a whole and .aligned instructions stay warp-wide.
-__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, unsigned parity) {
-    return __all_sync(0xffffffffu, mbar_wait(bar, parity));
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t *bar, unsigned parity, unsigned polls) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, polls));
 }
 __device__ __forceinline__ void bulk_copy_g2s(void *dst, const void *src, unsigned bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
@@ -242,6 +246,7 @@ struct SumTcArgs {
     View<const int> start, end;
     View<float> out;            // (rows_in_window, k)
     int64_t comp_begin, comp_count;  // components of one launch (set by the launcher)
+    unsigned wait_polls;        // poll limit of every hand-off wait
 };
 constexpr int SUM_TC_MAX_COMPONENTS = 64;    // per launch; more are processed in chunks
 constexpr int SUM_TC_MAX_TOTAL = 1024;       // (the FMA-pipe kernel's shared-envelope table holds this many)

@@ -18,7 +18,8 @@ import torch
 from torch import Tensor
 
 from . import _lib
-from ._lib import KM_MAX_BATCH_DIMS, KERNEL_TYPES, KmBatch, KmView, check, lib
+from ._lib import KM_MAX_BATCH_DIMS, KERNEL_TYPES, KmBatch, KmView, lib
+from ._lib import check as _check
 
 BLOCK_SIZE = 128
 NUM_PARAMS = {"rbf": 2, "spectral": 3, "locally_periodic": 4}
@@ -118,6 +119,7 @@ def _prep(kernel_type: str, x1, x2, params, start, end, extra: Sequence[tuple[Te
     for t, _ in extra:
         _check_f32(t)
     dev = _same_device(x1, x2, params, start, end, *(t for t, _ in extra))
+    _state(dev).poll(wait=False)  # a tensor-core launch that gave up since the last call raises here
     P = NUM_PARAMS[kernel_type]
     if params.shape[-1] != P:
         raise RuntimeError(f"params must have {P} entries in the last dim for kernel '{kernel_type}', got {params.shape[-1]}")
@@ -131,8 +133,84 @@ def _prep(kernel_type: str, x1, x2, params, start, end, extra: Sequence[tuple[Te
     return kid, dev, batch, m, n, expanded
 
 
-def _out_batch(batch: tuple[int, ...]) -> tuple[int, ...]:
-    return batch
+class KernelGaveUpError(RuntimeError):
+    """A tensor-core kernel stopped at a hand-off wait that ran out (status word != 0).  The
+    results of that launch are invalid (and NaN where the failing CTAs would have written)."""
+
+
+class _DeviceState:
+    """Per device and stream: one cached workspace for the tensor-core kernels and the status
+    words of the launches whose outcome has not been looked at yet.
+
+    Every tensor-core launch is followed by an asynchronous 4-byte copy of its status word into
+    pinned host memory and an event.  The next op call on the device looks at the copies whose
+    events have completed (no synchronisation) and raises ``KernelGaveUpError`` if one is
+    non-zero; ``check()`` synchronises first, so that it covers everything launched so far.
+    """
+
+    def __init__(self) -> None:
+        self.workspaces: dict[int, Tensor] = {}  # stream id -> uint8 workspace
+        self.pending: list[tuple[torch.cuda.Event, Tensor, str]] = []
+        self.free_words: list[Tensor] = []
+
+    def workspace(self, dev: torch.device, nbytes: int) -> Tensor:
+        key = torch.cuda.current_stream(dev).cuda_stream
+        ws = self.workspaces.get(key)
+        if ws is None or ws.numel() < nbytes:
+            # grows geometrically; launches that still use the old buffer keep it alive through
+            # the stream-ordered allocator
+            ws = torch.empty(max(nbytes, 2 * (ws.numel() if ws is not None else 0), 256), device=dev, dtype=torch.uint8)
+            self.workspaces[key] = ws
+        return ws
+
+    def track(self, ws: Tensor, what: str) -> None:
+        word = self.free_words.pop() if self.free_words else torch.zeros(1, dtype=torch.int32).pin_memory()
+        word.copy_(ws[:4].view(torch.int32), non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(ws.device))
+        self.pending.append((ev, word, what))
+
+    def poll(self, wait: bool) -> None:
+        failed = None
+        keep = []
+        for ev, word, what in self.pending:
+            if wait:
+                ev.synchronize()
+            if wait or ev.query():
+                if int(word[0]) != 0 and failed is None:
+                    failed = what
+                self.free_words.append(word)
+            else:
+                keep.append((ev, word, what))
+        self.pending = keep
+        if failed is not None:
+            raise KernelGaveUpError(
+                f"{failed}: a bounded wait inside the tensor-core kernel gave up (status word != 0); "
+                "the results of that call are invalid")
+
+
+_device_state: dict[int, _DeviceState] = {}
+
+
+def _state(dev: torch.device) -> _DeviceState:
+    idx = dev.index if dev.index is not None else torch.cuda.current_device()
+    st = _device_state.get(idx)
+    if st is None:
+        st = _device_state[idx] = _DeviceState()
+    return st
+
+
+def check(device: torch.device | int | None = None) -> None:
+    """Wait for every tensor-core launch made so far (on ``device``, default: all devices used)
+    and raise ``KernelGaveUpError`` if one of them gave up at a hand-off wait.  Op calls do the
+    same check, without waiting, for the launches that have already finished."""
+    if device is None:
+        states = list(_device_state.values())
+    else:
+        d = torch.device("cuda", device) if isinstance(device, int) else torch.device(device)
+        states = [_state(d)]
+    for st in states:
+        st.poll(wait=True)
 
 
 #: rhs widths from which ``matmul`` runs the contraction on the tensor cores (tcgen05; fp16
@@ -172,29 +250,36 @@ def matmul(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor
         kb = _km_batch(batch)
         rv = _view(re, 2)
         ws_bytes = lib.km_matmul_tc_workspace_bytes(kb, n, k, rv)
-        ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
+        st = _state(dev)
+        ws = st.workspace(dev, ws_bytes)
         with torch.cuda.device(dev):
-            check(lib.km_matmul_tc_f32(
+            _check(lib.km_matmul_tc_f32(
                 kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), rv, _view(pe, 1), _view(se, 1), _view(ee, 1),
-                _view(oute, 2), ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
-        out._km_workspace = ws  # keeps the status word reachable for tc_status()
+                _view(oute, 2), ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream(dev)))
+            st.track(ws, "matmul")
+        out._km_tensor_cores = True
         return out
     with torch.cuda.device(dev):
-        check(lib.km_matmul_f32(
+        _check(lib.km_matmul_f32(
             kid, _km_batch(batch), m, n, k, _view(x1e, 1), _view(x2e, 1), _view(re, 2), _view(pe, 1),
             _view(se, 1), _view(ee, 1), _view(oute, 2), _stream(dev)))
     return out
 
 
+def used_tensor_cores(result: Tensor) -> bool:
+    """Whether the op call that returned ``result`` ran its tensor-core kernel."""
+    return bool(getattr(result, "_km_tensor_cores", False))
+
+
 def tc_status(out: Tensor) -> int:
-    """Status word of the tensor-core product that produced ``out`` (synchronises): 0 = ok."""
-    ws = getattr(out, "_km_workspace", None)
-    if ws is None:
-        return 0
-    status = ctypes.c_int32(-1)
-    with torch.cuda.device(ws.device):
-        check(lib.km_workspace_status(ctypes.c_void_p(ws.data_ptr()), ctypes.byref(status), _stream(ws.device)))
-    return int(status.value)
+    """1 if a tensor-core launch on ``out``'s device has given up since the last check, else 0
+    (synchronises the device's launches; kept for callers that poll instead of catching
+    ``KernelGaveUpError`` from ``check``)."""
+    try:
+        check(out.device)
+    except KernelGaveUpError:
+        return 1
+    return 0
 
 
 def matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor, start: Tensor, end: Tensor,
@@ -235,15 +320,18 @@ def matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: T
         kb = _km_batch(batch)
         rv = _view(re, 2)
         ws_bytes = lib.km_matmul_tc_workspace_bytes(kb, n, k, rv)
-        ws = torch.empty(ws_bytes, device=dev, dtype=torch.uint8)
+        st = _state(dev)
+        ws = st.workspace(dev, ws_bytes)
         with torch.cuda.device(dev):
-            check(lib.km_matmul_tc_rows_f32(
+            _check(lib.km_matmul_tc_rows_f32(
                 kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), rv, _view(pe, 1), _view(se, 1), _view(ee, 1),
-                _view(oute, 2), row_block_begin, row_block_count, ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
-        out._km_workspace = ws
+                _view(oute, 2), row_block_begin, row_block_count, ctypes.c_void_p(ws.data_ptr()), ws.numel(),
+                _stream(dev)))
+            st.track(ws, "matmul_rows")
+        out._km_tensor_cores = True
         return out
     with torch.cuda.device(dev):
-        check(lib.km_matmul_rows_f32(
+        _check(lib.km_matmul_rows_f32(
             kid, _km_batch(batch), m, n, k, _view(x1e, 1), _view(x2e, 1), _view(re, 2), _view(pe, 1),
             _view(se, 1), _view(ee, 1), _view(oute, 2), row_block_begin, row_block_count,
             1 if sum_batches else 0, _stream(dev)))
@@ -276,16 +364,19 @@ def _grad_call(which: str, kernel_type, x1, x2, left, right, params, start, end,
     else:
         ws_bytes = lib.km_grad_workspace_bytes(kid, kb, m)
         fn = lib.km_matmul_bwd_f32 if which == "matmul_bwd" else lib.km_bilinear_derivative_f32
-    ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
+    st = _state(dev)
+    ws = st.workspace(dev, max(ws_bytes, 16))
     with torch.cuda.device(dev):
         if which == "matmul_bwd":  # argument order: rhs ... out_grad
-            check(fn(kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), rv, _view(pe, 1), _view(se, 1), _view(ee, 1),
-                     lv, _view(grade, 1), ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
+            _check(fn(kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), rv, _view(pe, 1), _view(se, 1), _view(ee, 1),
+                      lv, _view(grade, 1), ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream(dev)))
         else:
-            check(fn(kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), lv, rv, _view(pe, 1), _view(se, 1), _view(ee, 1),
-                     _view(grade, 1), ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
+            _check(fn(kid, kb, m, n, k, _view(x1e, 1), _view(x2e, 1), lv, rv, _view(pe, 1), _view(se, 1), _view(ee, 1),
+                      _view(grade, 1), ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream(dev)))
+        if tc:
+            st.track(ws, which)
     if tc:
-        grad._km_workspace = ws  # keeps the status word reachable for tc_status()
+        grad._km_tensor_cores = True
     return grad
 
 
@@ -314,7 +405,7 @@ def dense(kernel_type: str, x1, x2, params, start, end) -> Tensor:
     out = torch.empty(*batch, m, n, device=dev, dtype=torch.float32)
     oute = out.reshape(-1, m, n) if len(batch) > KM_MAX_BATCH_DIMS else out
     with torch.cuda.device(dev):
-        check(lib.km_dense_f32(kid, _km_batch(batch), m, n, _view(x1e, 1), _view(x2e, 1), _view(pe, 1),
+        _check(lib.km_dense_f32(kid, _km_batch(batch), m, n, _view(x1e, 1), _view(x2e, 1), _view(pe, 1),
                                _view(se, 1), _view(ee, 1), _view(oute, 2), _stream(dev)))
     return out
 
@@ -332,7 +423,7 @@ def dense_bwd(kernel_type: str, x1, x2, params, start, end, out_grad) -> Tensor:
     ws_bytes = lib.km_grad_workspace_bytes(kid, kb, m)
     ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev):
-        check(lib.km_dense_bwd_f32(kid, kb, m, n, _view(x1e, 1), _view(x2e, 1), _view(pe, 1), _view(se, 1),
+        _check(lib.km_dense_bwd_f32(kid, kb, m, n, _view(x1e, 1), _view(x2e, 1), _view(pe, 1), _view(se, 1),
                                    _view(ee, 1), _view(ge, 2), _view(grade, 1), ctypes.c_void_p(ws.data_ptr()),
                                    ws_bytes, _stream(dev)))
     return grad
@@ -368,7 +459,7 @@ def index(kernel_type: str, x1, x2, params, start, end, batch_indices, row_index
     L = row.numel()
     out = torch.empty(L, device=dev, dtype=torch.float32)
     with torch.cuda.device(dev):
-        check(lib.km_index_f32(kid, _km_batch(batch), m, n, L, _view(x1e, 1), _view(x2e, 1), _view(pe, 1),
+        _check(lib.km_index_f32(kid, _km_batch(batch), m, n, L, _view(x1e, 1), _view(x2e, 1), _view(pe, 1),
                                _view(se, 1), _view(ee, 1), _bidx_array(bidx, batch), ctypes.c_void_p(row.data_ptr()),
                                ctypes.c_void_p(col.data_ptr()), ctypes.c_void_p(out.data_ptr()), _stream(dev)))
     return out.reshape(shape)
@@ -390,7 +481,7 @@ def index_bwd(kernel_type: str, x1, x2, params, start, end, batch_indices, row_i
     ws_bytes = lib.km_index_bwd_workspace_bytes(kid, kb)
     ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev):
-        check(lib.km_index_bwd_f32(kid, kb, m, n, L, _view(x1e, 1), _view(x2e, 1), _view(pe, 1), _view(se, 1),
+        _check(lib.km_index_bwd_f32(kid, kb, m, n, L, _view(x1e, 1), _view(x2e, 1), _view(pe, 1), _view(se, 1),
                                    _view(ee, 1), _bidx_array(bidx, batch), ctypes.c_void_p(row.data_ptr()),
                                    ctypes.c_void_p(col.data_ptr()), ctypes.c_void_p(og.data_ptr()), _view(grad, 1),
                                    ctypes.c_void_p(ws.data_ptr()), ws_bytes, _stream(dev)))
@@ -406,12 +497,12 @@ def count_entries(m: int, n: int, start: Tensor, end: Tensor) -> Tensor:
     se, ee = _expand(start, batch, 1), _expand(end, batch, 1)
     out = torch.empty((), device=dev, dtype=torch.int64)
     with torch.cuda.device(dev):
-        check(lib.km_count_entries(_km_batch(batch), m, n, _view(se, 1), _view(ee, 1),
+        _check(lib.km_count_entries(_km_batch(batch), m, n, _view(se, 1), _view(ee, 1),
                                    ctypes.c_void_p(out.data_ptr()), _stream(dev)))
     return out
 
 
 __all__ = [
-    "matmul", "matmul_rows", "tc_status", "matmul_bwd", "bilinear_derivative", "dense", "dense_bwd", "index", "index_bwd",
+    "matmul", "matmul_rows", "tc_status", "check", "used_tensor_cores", "KernelGaveUpError", "matmul_bwd", "bilinear_derivative", "dense", "dense_bwd", "index", "index_bwd",
     "count_entries", "BLOCK_SIZE", "NUM_PARAMS",
 ]

@@ -69,7 +69,7 @@ def test_tc_product_unbanded_and_empty_bands():
 
 def test_tc_product_reports_its_workspace():
     out = _run("rbf", 300, 300, 64, square=True)
-    assert hasattr(out, "_km_workspace")
+    assert ops.used_tensor_cores(out)
 
 
 # ------------------------------------------------------------------ GEMM widths 16 / 32 / 64 / 128
@@ -205,21 +205,21 @@ def test_auto_path_selection_for_narrow_operands():
     for k, expect_tc in [(16, True), (9, True), (4, False)]:
         rhs = torch.randn(8192, k).cuda()
         out = ops.matmul("spectral", xd.expand(4, -1), xd.expand(4, -1), rhs.expand(4, -1, -1), pd, sd, ed)
-        assert hasattr(out, "_km_workspace") == expect_tc
+        assert ops.used_tensor_cores(out) == expect_tc
         assert ops.tc_status(out) == 0
         fma = ops.matmul("spectral", xd.expand(4, -1), xd.expand(4, -1), rhs.expand(4, -1, -1), pd, sd, ed, path="fma")
         assert rel_err(out, fma) <= 1e-5
     left = torch.randn(4, 8192, 16).cuda()
     right = torch.randn(4, 8192, 16).cuda()
     g = ops.bilinear_derivative("spectral", xd.expand(4, -1), xd.expand(4, -1), left, right, pd, sd, ed)
-    assert hasattr(g, "_km_workspace") and ops.tc_status(g) == 0
+    assert ops.used_tensor_cores(g) and ops.tc_status(g) == 0
     g4 = ops.bilinear_derivative("spectral", xd.expand(4, -1), xd.expand(4, -1), left[..., :4], right[..., :4], pd, sd, ed)
-    assert not hasattr(g4, "_km_workspace")
+    assert not ops.used_tensor_cores(g4)
     # small problems stay on the FMA pipe whatever the width
     xs = xd[:300]
     ss, es = O.make_ranges(2.0, x[:300])
     small = ops.matmul("spectral", xs, xs, torch.randn(300, 16).cuda(), pd[0], ss.cuda(), es.cuda())
-    assert not hasattr(small, "_km_workspace")
+    assert not ops.used_tensor_cores(small)
 
 
 @pytest.mark.parametrize("k", [13, 40])
