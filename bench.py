@@ -1,47 +1,50 @@
 """Benchmark of the kernel-matmul hot path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
-                    [--path auto|fma|tc]
+                    [--exchange auto|halo|allgather] [--path auto|fma|tc] [--no-cpu] [--no-secondary]
 
-Workload at the default settings: the spectral-mixture configuration (16 components sharing
-x and rhs, m = n = 65536 sorted U[0, 500], l ~ LogUniform[0.5, 5], f ~ U[0, 2], cutoff 4 l,
-rhs 65536 x 16; seeded synthetic inputs, ``kernel_matmul_b200/workloads.py``).  One step is one
-pass of the hot path over that batch: the forward product ``K . rhs`` and the hyper-parameter
-gradients ``matmul_bwd`` of all 16 components.  The metric is kernel entries x rhs columns per
-second: a step processes ``2 * E * k`` units (E visited entries, once forward and once in the
-gradient).
+Default workload (every N): the conjugate-gradient solve ``(K + sigma^2 I) V = Y`` with K the sum
+of 64 spectral components that share inputs, band and lengthscale (n = 2^22 sorted U[0, 20000],
+l = 1.5, f ~ U[0, 1] with f_0 = 0, cutoff 6, sigma^2 = 0.01, Y 2^22 x 8; seeded synthetic inputs,
+``kernel_matmul_b200/workloads.py``).  One step is one CG iteration: the banded product
+``sum_b K_b p`` (all 64 components inside one kernel), the inner products and the vector updates.
+With N > 1 (torchrun) the rows are sharded over the ranks -- total work is fixed, ``scaling`` is
+"strong" -- and an iteration contains two NCCL all-gathers (``--exchange halo``, the default
+for a banded operator: the neighbours' halo rows of q and the partial inner products;
+``--exchange allgather``: all of q, 134 MB).  The metric is kernel entries x rhs columns per
+second: a matvec visits E component entries, a step processes ``E * k`` units.
 
 Printed keys (one JSON line, rank 0):
-  value      whole-job units/s with inputs resident in HBM, CUDA-event time per step summed over
-             K steps, L2 flushed between steps, max over ranks;
-  e2e        the same metric through ``kernel_matmul_b200.host.matmul_and_grad_from_host`` with
-             HOST (pinned) buffers: every step copies x, rhs, params and out_grad to the device,
-             builds the band on the device, runs forward + gradient and copies out and grad back
-             (copies on two extra streams, overlapping the kernels);
-  roofline   the dominant kernel against the pipe that bounds it, measured live with the library's
-             calibration kernels: the SFU rate for the tensor-core kernels (the contraction runs as
-             tcgen05.mma; generating kappa costs 2-3 SFU operations per entry), the FP32 FFMA rate
-             for the FMA-pipe kernels (FMA-equivalent TFLOP/s = 2 x FP32-pipe instructions);
-  cpu_baseline  the dense PyTorch formulation (materialise K, mask by ranges, matmul, autograd)
-             in fp32 on all host cores, on a bounded sample of the same workload.
+  value      whole-job units/s with operands resident in HBM: the sum of the CUDA-event times of
+             K iterations (L2 flushed between them), max over ranks;
+  e2e        the same metric for whole solves (``iterations`` steps) through
+             ``kernel_matmul_b200.host.cg_solve_from_host`` with HOST (pinned) buffers: every rank
+             copies x, params and its rows of Y to the device, builds the band, iterates, and copies
+             its rows of the solution back;
+  roofline   the dominant kernel (``matmul_sum_tc_kernel``) against the measured dense bf16 rate
+             (its three fp16 MMAs per 16 phase values are what bounds it), its time taken with CUDA
+             events around the product inside the timed iterations;
+  cpu_baseline  the dense PyTorch formulation (materialise every K_b, mask by ranges, matmul, sum)
+             in fp32 on all host cores, on a seeded sample of row blocks of the same product,
+             extrapolated linearly in entries;
+  secondary  (N = 1) the other benchmark configurations, each timed the same way: forward +
+             ``matmul_bwd`` of the 16-component spectral mixture with their roofline fractions,
+             the locally periodic ``bilinear_derivative``, the unbanded k = 128 product, the 2^24
+             gathers, the small RBF product; and the reference's own CUDA kernels (best of its
+             autotune candidates, compiled unmodified) on the same GPU where they can run.
 
-With N > 1 (torchrun) every rank runs its own batch of 16 components with the same seeded
-parameters (the same work per GPU at every N): independent work, no data-path collective, weak
-scaling.
-
-``--impl reference`` times only the CPU dense formulation (the reference has no CPU kernel of
-its own for this path; the dense formulation is what its tests define as the expected result).
+``--impl reference`` times only the CPU dense formulation of the chosen workload (the reference
+has no CPU kernel of its own for this path; the dense formulation is what its tests define as
+the expected result).  Under torchrun rank 0 alone runs it.
 """
 from __future__ import annotations
 
 import argparse
+import importlib.util
 import json
-import math
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
 import threading
 import time
 
@@ -53,6 +56,7 @@ if ROOT not in sys.path:
 
 METRIC = "kernel_entries_x_rhs_cols_per_s"
 UNIT = "entry-cols/s"
+DEFAULT_WORKLOAD = "cg_sum"
 
 # Algorithmic per-entry instruction budget of the FMA path (FP32-pipe instructions, SFU ops):
 # generation + contraction.  Forward: k FFMA per entry; gradient: k FFMA for the coefficient
@@ -86,6 +90,21 @@ def dist_env():
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     return rank, world, local
+
+
+def load_workloads():
+    """The workload generators, loaded by path: they need PyTorch only, and the reference arm must
+    not import the package (which maps the product's library)."""
+    spec = importlib.util.spec_from_file_location("km_b200_workloads", os.path.join(ROOT, "kernel_matmul_b200", "workloads.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[spec.name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measured_peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    return json.load(open(path)) if os.path.exists(path) else {}
 
 
 class ClockSampler:
@@ -158,7 +177,7 @@ def device_delay() -> None:
     torch.cuda._sleep(2_000_000)
 
 
-def cuda_ms(fn, stream=None) -> float:
+def cuda_ms(fn) -> float:
     a = torch.cuda.Event(enable_timing=True)
     b = torch.cuda.Event(enable_timing=True)
     a.record()
@@ -168,42 +187,80 @@ def cuda_ms(fn, stream=None) -> float:
     return a.elapsed_time(b)
 
 
-# ----------------------------------------------------------------------------------- workload
+def live_peaks(dev) -> tuple[float, float]:
+    """(FP32 FFMA TFLOP/s, SFU Tops/s) measured with the library's calibration kernels."""
+    import ctypes
+
+    from kernel_matmul_b200._lib import check, lib
+
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    flops, sfu_ops = ctypes.c_double(), ctypes.c_double()
+
+    def probe():
+        check(lib.km_probe_fp32_peak(20000, None, ctypes.byref(flops), stream))
+
+    def probe_sfu():
+        check(lib.km_probe_sfu_peak(20000, None, ctypes.byref(sfu_ops), stream))
+
+    probe()
+    fp32_peak = max(flops.value / (cuda_ms(probe) * 1e-3) for _ in range(3)) / 1e12
+    probe_sfu()
+    sfu_peak = max(sfu_ops.value / (cuda_ms(probe_sfu) * 1e-3) for _ in range(3)) / 1e12
+    return fp32_peak, sfu_peak
 
 
-def make_workload(name: str, rank: int):
-    from kernel_matmul_b200 import workloads
+def dram_traffic(workload: str, kernel: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch, copied by hand from the ncu captures
+    summarised under profiles/ into profiles/dram_traffic.json."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    if not os.path.exists(path):
+        return None
+    return json.load(open(path)).get(workload, {}).get(kernel)
 
+
+# ----------------------------------------------------------------------------------- workloads
+
+
+def make_workload(W, name: str):
+    if name == "cg_sum":
+        return W.cg_sum_kernel()
+    if name == "cg_sum_small":
+        return W.cg_sum_kernel(n=1 << 17, components=8, span=625.0)
     if name == "spectral_mixture":
-        w = workloads.spectral_mixture()
-    elif name == "spectral_mixture_small":
-        w = workloads.spectral_mixture(n=8192, components=4, k=16, span=62.5)
-    else:
-        raise SystemExit(f"unknown workload {name}")
-    return w
+        return W.spectral_mixture()
+    if name == "spectral_mixture_small":
+        return W.spectral_mixture(n=8192, components=4, k=16, span=62.5)
+    raise SystemExit(f"unknown workload {name}")
 
 
-# -------------------------------------------------------------------------------- CPU baseline
+def config_of(w, entries: int) -> dict:
+    """The ``config`` key: the same in both arms."""
+    k = w.rhs.shape[-1]
+    B = w.params.shape[0] if w.params.dim() > 1 else 1
+    if w.name.startswith("cg_sum"):
+        return {"workload": w.name, "ops": "CG iteration: batch-summed banded product + inner products + vector updates",
+                "n": w.n, "components": B, "rhs_cols": k, "entries_per_matvec": entries, "units_per_step": float(entries) * k,
+                "sigma2": w.extra["sigma2"], "iterations_per_solve": int(w.extra["iterations"])}
+    return {"workload": w.name, "ops": "matmul fwd + matmul_bwd", "n": w.n, "components": B, "rhs_cols": k,
+            "entries_per_pass": entries, "units_per_step": 2.0 * entries * k}
 
 
-def cpu_dense_sample(w, seconds: float = 12.0, max_seconds: float = 30.0) -> dict:
+# -------------------------------------------------------------------------------- CPU baselines
+
+
+def cpu_dense_sample_mixture(w, seconds: float = 12.0, max_seconds: float = 30.0) -> dict:
     """Dense formulation (oracle/dense_reference.py) in fp32 on all host cores: forward slab
-    product + autograd gradient for row-block slabs of the workload, drawn round-robin over the
-    components, until ``seconds`` of work are done.  Returns units/s."""
+    product + autograd gradient for row-block slabs of the spectral-mixture workload, drawn
+    round-robin over the components, until ``seconds`` of work are done.  Returns units/s."""
     from oracle import dense_reference as D
     from oracle import oracle as O
 
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
-    x = w.x
-    n = w.n
-    k = w.rhs.shape[-1]
-    B = w.params.shape[0]
+    x, n, k, B = w.x, w.n, w.rhs.shape[-1], w.params.shape[0]
     R = -(-n // 128)
     bands = [O.make_ranges(c, x) for c in w.cutoffs]
-    units = 0
-    entries = 0
-    slabs = 0
+    units = entries = slabs = 0
     t0 = time.perf_counter()
     group = 8  # row blocks per slab
     order = [(b, r0) for p in range(16) for r0 in range(p * group, R, group * 16) for b in range(B)]
@@ -228,38 +285,85 @@ def cpu_dense_sample(w, seconds: float = 12.0, max_seconds: float = 30.0) -> dic
             break
     el = time.perf_counter() - t0
     return {
-        "value": units / el,
-        "unit": UNIT,
-        "cores": cores,
-        "kind": "port",
+        "value": units / el, "unit": UNIT, "cores": cores, "kind": "port",
         "sample": f"{slabs} slabs of {group} row blocks ({entries} entries, fwd + autograd bwd, fp32) in {el:.1f} s",
         "seconds": el,
     }
 
 
-# --------------------------------------------------------------------------------------- main
+def cpu_dense_sample_cg(w, seconds: float = 12.0, min_blocks: int = 64, max_seconds: float = 40.0) -> dict:
+    """Dense formulation of the CG workload's product in fp32 on all host cores: for a seeded random
+    sample of row blocks, every component's K_b is materialised over the block's band, masked and
+    multiplied with the right-hand side, and the results are added (what the reference's
+    SumKernel operator does, kernel_matmul/gpytorch/sum.py:16-24).  At least ``min_blocks`` row blocks
+    and ``seconds`` of work; the rate is per entry, so it extrapolates linearly to the full product
+    (7.4e11 entries would take most of an hour).  The vector updates of the iteration (~1 % of the
+    product's memory traffic) are not part of the sample."""
+    from oracle import dense_reference as D
+    from oracle import oracle as O
+
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    x, n, k, B = w.x, w.n, w.rhs.shape[-1], w.params.shape[0]
+    R = -(-n // 128)
+    start, end = O.make_ranges(w.cutoffs[0], x)
+    g = torch.Generator().manual_seed(0)
+    order = torch.randperm(R, generator=g).tolist()
+    entries = blocks = 0
+    t0 = time.perf_counter()
+    with torch.no_grad():
+        for r in order:
+            c0, c1 = int(start[r]), min(int(end[r]), n)
+            rows = slice(r * 128, min((r + 1) * 128, n))
+            acc = torch.zeros(rows.stop - rows.start, k)
+            xr, xc, rhs = x[rows], x[c0:c1], w.rhs[c0:c1]
+            for b in range(B):
+                acc += D.kernel_matrix(w.kernel_type, xr, xc, w.params[b]) @ rhs
+            entries += B * (rows.stop - rows.start) * (c1 - c0)
+            blocks += 1
+            el = time.perf_counter() - t0
+            if (blocks >= min_blocks and el >= seconds) or el >= max_seconds:
+                break
+    el = time.perf_counter() - t0
+    return {
+        "value": entries * k / el, "unit": UNIT, "cores": cores, "kind": "port",
+        "sample": f"{blocks} random row blocks x {B} components ({entries} entries, fp32 dense product per component, "
+                  f"summed) in {el:.1f} s; extrapolated linearly in entries",
+        "seconds": el,
+    }
 
 
 def run_reference(args, rank: int, world: int) -> None:
     if rank != 0:
         return
-    w = make_workload(args.workload, 0)
+    W = load_workloads()
+    from oracle import oracle as O
+
+    w = make_workload(W, args.workload)
+    cg = w.name.startswith("cg_sum")
+    sample = cpu_dense_sample_cg if cg else cpu_dense_sample_mixture
+    entries = sum(O.count_entries(w.n, w.n, *O.make_ranges(c, w.x)) for c in w.cutoffs)
+    if cg:
+        entries *= w.params.shape[0]
     per_step = max(2.0, min(10.0, 60.0 / max(1, args.steps + args.warmup)))
+    extra = {"min_blocks": 4} if cg else {}
     for _ in range(args.warmup):
-        cpu_dense_sample(w, seconds=per_step / 4, max_seconds=per_step)
-    vals, secs = [], []
-    base = None
+        sample(w, seconds=per_step / 4, max_seconds=per_step, **extra)
+    vals, secs, base = [], [], None
+    extra = {"min_blocks": 8} if cg else {}
     for _ in range(args.steps):
-        base = cpu_dense_sample(w, seconds=per_step, max_seconds=2 * per_step)
+        base = sample(w, seconds=per_step, max_seconds=3 * per_step, **extra)
         vals.append(base["value"])
         secs.append(base["seconds"])
     value = statistics.mean(vals)
     base["value"] = value
+    base["sample"] = f"per step: {base['sample']}; {args.steps} steps"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(secs),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w.name, "what": "dense PyTorch formulation on host cores, bounded sample per step"},
+        "higher_is_better": True, "scaling": "strong" if cg else "weak", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": config_of(w, entries),
+        "what": "dense PyTorch formulation on host cores, bounded sample per step",
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -267,58 +371,61 @@ def run_reference(args, rank: int, world: int) -> None:
     print(json.dumps(line), flush=True)
 
 
-def reference_cuda_timing(w, dev, xb, rhs, params, start, end, og) -> dict | None:
-    """Times the reference's own CUDA kernels (compiled unmodified into oracle/_ref) on the same
-    inputs, when those modules are present.  Informational: the generic-SIMT bar on this GPU."""
-    import importlib.util
+# ------------------------------------------------------------- the reference's CUDA kernels, same GPU
 
-    out = {}
-    try:
-        k = rhs.shape[-1]
-        for op, modname in (("fwd", f"km_ref_matmul_{w.kernel_type}_k{k}"), ("bwd", f"km_ref_matmul_bwd_{w.kernel_type}")):
-            path = os.path.join(ROOT, "oracle", "_ref", modname, modname + ".so")
-            if not os.path.exists(path):
-                return None
-            spec = importlib.util.spec_from_file_location(modname, path)
+
+def reference_cuda_timing(kind: str, kernel_type: str, k: int, call_args: tuple, reps: int = 3) -> dict | None:
+    """Times the reference's own CUDA kernels (compiled unmodified into oracle/_ref by
+    oracle/build_ref.py) on the same inputs: every autotune candidate that was built for this op,
+    kernel type and width (kernel_matmul/configurations.py:94-118), the fastest one reported.
+    The reference launches on the legacy default stream, so each call is timed between device
+    synchronisations.  None when no module was built."""
+    import glob
+
+    base = os.path.join(ROOT, "oracle", "_ref")
+    stem = f"km_ref_matmul_{kernel_type}_k{k}" if kind == "matmul" else f"km_ref_{kind}_{kernel_type}"
+    best, tried, errors = None, 0, []
+    for d in sorted(glob.glob(os.path.join(base, stem + "*"))):
+        name = os.path.basename(d)
+        if name != stem and not name.startswith(stem + "_"):
+            continue  # e.g. ..._k1 must not pick up ..._k16
+        so = os.path.join(d, name + ".so")
+        if not os.path.exists(so):
+            continue
+        try:
+            spec = importlib.util.spec_from_file_location(name, so)
             mod = importlib.util.module_from_spec(spec)
             spec.loader.exec_module(mod)
-            fn = (lambda m=mod: m.call(xb, xb, rhs, params, start, end)) if op == "fwd" else (
-                lambda m=mod: m.call(xb, xb, rhs, params, start, end, og))
-            fn()
+            mod.call(*call_args)
             torch.cuda.synchronize()
-            # the reference launches on the legacy default stream: time with full device syncs
             ts = []
-            for _ in range(3):
+            for _ in range(reps):
                 torch.cuda.synchronize()
                 t0 = time.perf_counter()
-                fn()
+                mod.call(*call_args)
                 torch.cuda.synchronize()
                 ts.append(1e3 * (time.perf_counter() - t0))
-            out[f"{op}_ms"] = min(ts)
-        return out
-    except Exception as exc:  # noqa: BLE001 - informational only
-        return {"error": str(exc)[:200]}
+            tried += 1
+            if best is None or min(ts) < best[0]:
+                best = (min(ts), name)
+        except Exception as exc:  # noqa: BLE001 - informational only
+            errors.append(f"{name}: {str(exc)[:120]}")
+    if best is None:
+        return {"error": "; ".join(errors)[:400]} if errors else None
+    return {"ms": best[0], "module": best[1], "candidates_timed": tried}
 
 
-def run_ours(args, rank: int, world: int, local: int) -> None:
-    import kernel_matmul_b200 as km  # raises if libkm_b200.so is missing: no fallback
-    from kernel_matmul_b200 import ops, ranges, workloads
-    from kernel_matmul_b200._lib import check, lib
-    import ctypes
+# ------------------------------------------------------------------------ spectral mixture (config 2)
 
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        import torch.distributed as dist
 
-        dist.init_process_group("nccl", device_id=dev)
+def measure_mixture(w, dev, steps: int, path: str, fp32_peak: float, sfu_peak: float, with_e2e: bool, with_ref: bool) -> dict:
+    """Forward product + matmul_bwd of the spectral mixture: resident inputs, CUDA events, L2 flushed
+    between steps.  Returns times, roofline fractions per kernel and (optionally) the end-to-end
+    figure from host buffers and the reference's CUDA kernels on the same GPU."""
+    from kernel_matmul_b200 import host, ops, workloads
 
-    w = make_workload(args.workload, rank)
     kt = w.kernel_type
-    n, k = w.n, w.rhs.shape[-1]
-    B = w.params.shape[0]
-
-    # ---- resident inputs
+    n, k, B = w.n, w.rhs.shape[-1], w.params.shape[0]
     x = w.x.to(dev)
     xb = x.expand(B, -1)
     rhs = w.rhs.to(dev).expand(B, -1, -1)
@@ -326,52 +433,14 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
     og = w.extra["out_grad"].to(dev)
     start, end = workloads.band(w, x)
     E = int(ops.count_entries(n, n, start, end))
-    units_per_step = 2 * E * k
-
-    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)  # > 126 MB of L2
-
-    path = args.path
-
-    def step():
-        out = ops.matmul(kt, xb, xb, rhs, params, start, end, path=path)
-        g = ops.matmul_bwd(kt, xb, xb, rhs, params, start, end, og, path=path)
-        return out, g
-
-    for _ in range(max(args.warmup, 3)):
-        out_w, g_w = step()
-    torch.cuda.synchronize()
-    # which kernels the ops chose (tensor cores for this width and size, else the FMA pipe);
-    # a tensor-core kernel reports a bounded wait that gave up through its status word
-    tc_fwd, tc_bwd = hasattr(out_w, "_km_workspace"), hasattr(g_w, "_km_workspace")
-    if ops.tc_status(out_w) != 0 or ops.tc_status(g_w) != 0:
-        raise RuntimeError("a tensor-core kernel reported a failed wait")
-
-    # ---- live FP32 and SFU peaks (calibration kernels of the library)
-    flops = ctypes.c_double()
-    sfu_ops = ctypes.c_double()
-    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
-
-    def probe():
-        check(lib.km_probe_fp32_peak(20000, None, ctypes.byref(flops), stream))
-
-    def probe_sfu():
-        check(lib.km_probe_sfu_peak(20000, None, ctypes.byref(sfu_ops), stream))
-
-    probe()
-    fp32_peak = max(flops.value / (cuda_ms(probe) * 1e-3) for _ in range(3)) / 1e12
-    probe_sfu()
-    sfu_peak = max(sfu_ops.value / (cuda_ms(probe_sfu) * 1e-3) for _ in range(3)) / 1e12
-
-    # ---- timed region
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.barrier()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(local)
-    wall0 = time.perf_counter()
-    step_ms, fwd_ms, bwd_ms = [], [], []
-    for _ in range(args.steps):
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    for _ in range(3):
+        out_w = ops.matmul(kt, xb, xb, rhs, params, start, end, path=path)
+        g_w = ops.matmul_bwd(kt, xb, xb, rhs, params, start, end, og, path=path)
+    ops.check(dev)
+    tc_fwd, tc_bwd = ops.used_tensor_cores(out_w), ops.used_tensor_cores(g_w)
+    fwd_ms, bwd_ms, step_ms = [], [], []
+    for _ in range(steps):
         flush.fill_(1)
         device_delay()
         e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
@@ -384,301 +453,75 @@ def run_ours(args, rank: int, world: int, local: int) -> None:
         fwd_ms.append(e0.elapsed_time(e1))
         bwd_ms.append(e1.elapsed_time(e2))
         step_ms.append(e0.elapsed_time(e2))
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    wall = time.perf_counter() - wall0
-    total_ms = sum(step_ms)
+    ops.check(dev)
+    fwd, bwd = statistics.mean(fwd_ms), statistics.mean(bwd_ms)
+    fwd_name = "matmul_tc_kernel" if tc_fwd else "matmul_fma_kernel"
+    bwd_name = "grad_tc_kernel" if tc_bwd else "grad_band_kernel"
+    kernels = {
+        fwd_name: {"ms": fwd, "sfu_per_entry": TC_FWD[kt][1] if tc_fwd else GEN_FWD[kt][1],
+                   "contraction": "tcgen05.mma kind::f16 (fp16 hi/lo split)" if tc_fwd else "fma.rn.f32x2",
+                   "fp32_instr_per_entry": TC_FWD[kt][0] if tc_fwd else fp32_instr_fwd(kt, k)},
+        bwd_name: {"ms": bwd, "sfu_per_entry": TC_BWD[kt][1] if tc_bwd else GEN_BWD[kt][1],
+                   "contraction": "tcgen05.mma kind::tf32 (3xTF32)" if tc_bwd else "fma.rn.f32x2",
+                   "fp32_instr_per_entry": TC_BWD[kt][0] if tc_bwd else fp32_instr_bwd(kt, k)},
+    }
+    for kname, kd in kernels.items():
+        kd["achieved_tflops"] = 2.0 * E * kd["fp32_instr_per_entry"] / (kd["ms"] * 1e-3) / 1e12
+        kd["frac_fp32"] = kd["achieved_tflops"] / fp32_peak
+        kd["achieved_sfu_tops"] = E * kd["sfu_per_entry"] / (kd["ms"] * 1e-3) / 1e12
+        kd["frac_sfu"] = kd["achieved_sfu_tops"] / sfu_peak
+        kd["traffic"] = dram_traffic("spectral_mixture", kname) if w.n == 65536 else None
+    ms_per_step = statistics.mean(step_ms)
+    res = {
+        "config": config_of(w, E), "path": path, "ms_per_step": ms_per_step, "value": 2.0 * E * k / (ms_per_step * 1e-3),
+        "unit": UNIT, "steps": steps, "l2": "flushed between steps (256 MB write)", "kernels": kernels,
+        "fp32_peak_tflops": fp32_peak, "sfu_peak_tops": sfu_peak,
+        "bound": "fp32 (FFMA issue rate measured live; the contraction runs on the tensor cores at a few % of their peak, "
+                 "what bounds the kernels is generating the kernel entries)",
+        "gpu_launches_per_step": (3 if tc_fwd else 1) + (3 if tc_bwd else 2),
+    }
+    if with_e2e:
+        hx, hrhs = w.x.pin_memory(), w.rhs.contiguous().pin_memory()
+        hp, hog = w.params.contiguous().pin_memory(), w.extra["out_grad"].contiguous().pin_memory()
+        hout, hgrad = torch.empty(B, n, k).pin_memory(), torch.empty(B, w.params.shape[-1]).pin_memory()
+        streams = host.HostStreams(dev)
 
-    # ---- end to end with host buffers (pinned), copies inside the timed region
-    hx = w.x.pin_memory()
-    hrhs = w.rhs.contiguous().pin_memory()
-    hp = w.params.contiguous().pin_memory()
-    hog = w.extra["out_grad"].contiguous().pin_memory()
-    hout = torch.empty(B, n, k).pin_memory()
-    hgrad = torch.empty(B, w.params.shape[-1]).pin_memory()
-    h2d = sum(t.numel() * t.element_size() for t in (hx, hrhs, hp, hog))
-    d2h = sum(t.numel() * t.element_size() for t in (hout, hgrad))
+        def e2e_step():
+            host.matmul_and_grad_from_host(kt, hx, hrhs, hp, hog, lambda dx: workloads.band(w, dx), hout, hgrad, streams, path=path)
 
-    from kernel_matmul_b200 import host
-
-    host_streams = host.HostStreams(dev)
-
-    def e2e_step():
-        # copies in, band construction, product, gradient and copies out, overlapped on three streams
-        host.matmul_and_grad_from_host(kt, hx, hrhs, hp, hog, lambda dx: workloads.band(w, dx), hout, hgrad,
-                                       host_streams, path=path)
-
-    for _ in range(2):
-        e2e_step()
-    torch.cuda.synchronize()
-    e2e_ms = []
-    for _ in range(args.steps):
-        flush.fill_(1)
-        e2e_ms.append(cuda_ms(e2e_step))
-    clocks = sampler.stop()
-    e2e_total = sum(e2e_ms)
-
-    # ---- max over ranks
-    if world > 1:
-        t = torch.tensor([total_ms, e2e_total], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_total = float(t[0]), float(t[1])
-        u = torch.tensor([float(units_per_step)], device=dev, dtype=torch.float64)
-        dist.all_reduce(u, op=dist.ReduceOp.SUM)
-        units_all = float(u[0])
-    else:
-        units_all = float(units_per_step)
-
-    if rank == 0:
-        ms_per_step = total_ms / args.steps
-        value = units_all / (ms_per_step * 1e-3)
-        e2e_value = units_all / (e2e_total / args.steps * 1e-3)
-        fwd = statistics.mean(fwd_ms)
-        bwd = statistics.mean(bwd_ms)
-        # Per-entry budgets.  FMA-pipe kernels: generation + k FMAs (+ P in the gradient).
-        # Tensor-core kernels: the contraction runs as tcgen05.mma, the threads only generate
-        # (forward: + 2 operations for the hi / lo split; gradient: + one FMA per parameter).
-        fwd_name = "matmul_tc_kernel" if tc_fwd else "matmul_fma_kernel"
-        bwd_name = "grad_tc_kernel" if tc_bwd else "grad_band_kernel"
-        kernels = {
-            fwd_name: {"ms": fwd, "sfu_per_entry": TC_FWD[kt][1] if tc_fwd else GEN_FWD[kt][1],
-                       "contraction": "tcgen05.mma kind::f16 (fp16 hi/lo split)" if tc_fwd else "fma.rn.f32x2",
-                       "fp32_instr_per_entry": TC_FWD[kt][0] if tc_fwd else fp32_instr_fwd(kt, k)},
-            bwd_name: {"ms": bwd, "sfu_per_entry": TC_BWD[kt][1] if tc_bwd else GEN_BWD[kt][1],
-                       "contraction": "tcgen05.mma kind::tf32 (3xTF32)" if tc_bwd else "fma.rn.f32x2",
-                       "fp32_instr_per_entry": TC_BWD[kt][0] if tc_bwd else fp32_instr_bwd(kt, k)},
-        }
-        traffic = None
-        tpath = os.path.join(ROOT, "profiles", "dram_traffic.json")
-        dom = max(kernels, key=lambda kname: kernels[kname]["ms"])
-        if os.path.exists(tpath):
-            traffic = json.load(open(tpath)).get(args.workload, {}).get(dom)
-        for kname, kd in kernels.items():
-            kd["achieved_tflops"] = 2.0 * E * kd["fp32_instr_per_entry"] / (kd["ms"] * 1e-3) / 1e12
-            kd["frac_fp32"] = kd["achieved_tflops"] / fp32_peak
-            kd["achieved_sfu_tops"] = E * kd["sfu_per_entry"] / (kd["ms"] * 1e-3) / 1e12
-            kd["frac_sfu"] = kd["achieved_sfu_tops"] / sfu_peak
-        d = kernels[dom]
-        dom_tc = (dom == fwd_name and tc_fwd) or (dom == bwd_name and tc_bwd)
-        if dom_tc and d["frac_sfu"] > d["frac_fp32"]:
-            roof = {"bound": "sfu", "kernel": dom, "achieved": d["achieved_sfu_tops"], "peak": sfu_peak,
-                    "unit": "Tops/s (special-function operations)", "frac": d["frac_sfu"], "traffic": traffic,
-                    "peak_source": "measured live: km_probe_sfu_peak (ex2.approx issue rate of all SMs); achieved = "
-                                   "algorithmic SFU operations per launch / CUDA-event time.  The contraction runs on "
-                                   "the tensor cores (a few % of their peak at this width); what bounds the kernel is "
-                                   "generating the kernel entries"}
-        else:
-            roof = {"bound": "fp32", "kernel": dom, "achieved": d["achieved_tflops"], "peak": fp32_peak,
-                    "unit": "TFLOP/s", "frac": d["frac_fp32"], "traffic": traffic,
-                    "peak_source": "measured live: km_probe_fp32_peak (FFMA issue rate of all SMs); achieved = 2 x "
-                                   "algorithmic FP32-pipe instructions per launch / CUDA-event time"
-                                   + (".  The contraction runs on the tensor cores (a few % of their peak at this "
-                                      "width); what bounds the kernel is generating the kernel entries" if dom_tc else "")}
-        peaks = {}
-        ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        if os.path.exists(ppath):
-            peaks = json.load(open(ppath))
-        hbm_bytes = 4 * (n * k + B * n * k * 2 + n + 2 * B * (n // 128))
-        line = {
-            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {
-                "workload": w.name, "ops": "matmul fwd + matmul_bwd", "path": path, "entries_per_rank": E, "rhs_cols": k,
-                "units_per_step": units_all, "l2": "flushed between steps (256 MB write)",
-                "per_rank": "own batch of 16 components (same seeded parameters on every rank), no collective",
-            },
-            "roofline": {
-                **roof,
-                "fp32_peak_tflops": fp32_peak, "sfu_peak_tops": sfu_peak,
-                "hbm": {"algorithmic_bytes_per_step": hbm_bytes,
-                        "frac_of_measured_hbm": (hbm_bytes / (ms_per_step * 1e-3)) / (peaks.get("hbm_gbs", 6650.0) * 1e9)},
-                "kernels": kernels,
-            },
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "ms_per_step": e2e_total / args.steps},
-            # forward: product kernel (+ column-maximum and image pre-passes on the tensor-core path);
-            # gradient: band kernel + finish kernel (+ image pre-pass on the tensor-core path)
-            "gpu_launches": ((3 if tc_fwd else 1) + (3 if tc_bwd else 2)) * args.steps,
-            "clocks": clocks,
-            "wall_s": wall,
-        }
-        if not args.no_cpu and world == 1:
-            line["cpu_baseline"] = cpu_dense_sample(w)
-        ref_cuda = reference_cuda_timing(w, dev, xb, rhs, params, start, end, og)
-        if ref_cuda is not None:
-            line["reference_cuda_kernels_same_gpu"] = ref_cuda
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        for _ in range(2):
+            e2e_step()
+        torch.cuda.synchronize()
+        e2e_ms = []
+        for _ in range(steps):
+            flush.fill_(1)
+            e2e_ms.append(cuda_ms(e2e_step))
+        res["e2e"] = {"value": 2.0 * E * k / (statistics.mean(e2e_ms) * 1e-3), "unit": UNIT,
+                      "h2d_bytes_per_step": sum(t.numel() * 4 for t in (hx, hrhs, hp, hog)),
+                      "d2h_bytes_per_step": sum(t.numel() * 4 for t in (hout, hgrad)), "ms_per_step": statistics.mean(e2e_ms)}
+    if with_ref:
+        ref_f = reference_cuda_timing("matmul", kt, k, (xb, xb, rhs, params, start, end))
+        ref_b = reference_cuda_timing("matmul_bwd", kt, k, (xb, xb, rhs, params, start, end, og))
+        if ref_f or ref_b:
+            res["reference_cuda_kernels_same_gpu"] = {"matmul": ref_f, "matmul_bwd": ref_b}
+    return res
 
 
-def run_cg(args, rank: int, world: int, local: int) -> None:
-    """Config-5 style workload: (K + sigma^2 I) V = Y by CG, K the sum of 64 spectral components
-    (shared band), rows sharded over the ranks, one NCCL all-gather per iteration.  One step =
-    one CG iteration (sharded product + all-gather + replicated vector updates); total work is
-    fixed, so scaling is strong."""
-    import ctypes
-
-    import kernel_matmul_b200  # noqa: F401
-    from kernel_matmul_b200 import ops, workloads
-    from kernel_matmul_b200._lib import check, lib
-    from kernel_matmul_b200.cg import CGSolver, ShardedOperator, conjugate_gradient
-
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=dev)
-    w = workloads.cg_sum_kernel() if args.workload == "cg_sum" else workloads.cg_sum_kernel(n=1 << 17, components=8, span=625.0)
-    kt, n, k, B = w.kernel_type, w.n, w.rhs.shape[-1], w.params.shape[0]
-    x = w.x.to(dev)
-    params = w.params.to(dev)
-    y = w.rhs.to(dev)
-    start, end = workloads.band(w, x)
-    E = int(ops.count_entries(n, n, start, end))  # over all components
-    units = float(E) * k
-    op = ShardedOperator.from_kernel(kt, x, params, start[0], end[0], w.extra["sigma2"])
-
-    flops = ctypes.c_double()
-    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
-
-    def probe():
-        check(lib.km_probe_fp32_peak(20000, None, ctypes.byref(flops), stream))
-
-    probe()
-    fp32_peak = max(flops.value / (cuda_ms(probe) * 1e-3) for _ in range(3)) / 1e12
-    sm_clock = fp32_peak * 1e12 / (148 * 128 * 2)
-
-    # a running solve: a few iterations are warm-up, then K timed iterations
-    solver = CGSolver(op, y)
-    for _ in range(max(args.warmup, 3)):
-        solver.step()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    sampler = ClockSampler(local)
-    t0 = torch.cuda.Event(enable_timing=True)
-    t1 = torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(args.steps):
-        solver.step()
-    t1.record()
-    t1.synchronize()
-    total_ms = t0.elapsed_time(t1)
-    # the product alone (this rank's rows, no collective)
-    apply_ms = statistics.mean(cuda_ms(lambda: op.apply_rows(solver.p)) for _ in range(3))
-    clocks = sampler.stop()
-
-    # end to end: host y in, solution out, full solve of `iters` iterations
-    iters = int(w.extra["iterations"]) if args.workload == "cg_sum" and world > 1 else min(int(w.extra["iterations"]), 10)
-    hy = w.rhs.contiguous().pin_memory()
-    hx = w.x.pin_memory()
-    hp = w.params.contiguous().pin_memory()
-    hsol = torch.empty(n, k).pin_memory()
-
-    def solve_e2e():
-        dx = hx.to(dev, non_blocking=True)
-        dp = hp.to(dev, non_blocking=True)
-        dy = hy.to(dev, non_blocking=True)
-        st, en = workloads.band(w, dx)
-        o = ShardedOperator.from_kernel(kt, dx, dp, st[0], en[0], w.extra["sigma2"])
-        res = conjugate_gradient(o, dy, iterations=iters)
-        hsol.copy_(res.solution, non_blocking=True)
-
-    e2e_ms = cuda_ms(solve_e2e)
-    if world > 1:
-        t = torch.tensor([total_ms, e2e_ms, apply_ms], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms, e2e_ms, apply_ms = (float(v) for v in t)
-    if rank == 0:
-        ms_per_step = total_ms / args.steps
-        # All components share inputs, band and lengthscale, so the batch sum runs on the tensor
-        # cores (matmul_sum_tc_kernel): sum_b s_b cos(w_b tau) = <phi(x_i), psi(x_j)> with 2B-vectors
-        # of per-point phases.  Per UNIQUE (row, column) entry: one envelope exponential + 2B / 128
-        # SFU operations for the column's phase vector (shared by the 128 rows of the block), three
-        # fp16 MMAs of 2B multiply-adds, and k + ~6 FP32 operations.
-        e_unique = E / B / world  # row windows are equal
-        t_apply = apply_ms * 1e-3
-        tensor_flops = e_unique * 3 * 2 * (2 * B)
-        sfu_ops = e_unique * (1 + 2 * B / 128)
-        fp32_ops = e_unique * (k + 6)
-        peaks = {}
-        ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
-        if os.path.exists(ppath):
-            peaks = json.load(open(ppath))
-        f16_peak = peaks.get("bf16_tflops", 1590.0)
-        sfu_peak = 148 * 16 * sm_clock
-        frac_tensor = tensor_flops / t_apply / 1e12 / f16_peak
-        frac_sfu = sfu_ops / t_apply / sfu_peak
-        frac_fp32 = 2.0 * fp32_ops / t_apply / 1e12 / fp32_peak
-        line = {
-            "metric": METRIC, "value": units / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": w.name, "ops": "CG iteration: batch-summed banded product, vector updates and inner products sharded by rows; all-gather of the search direction and of per-row-block partial inner products",
-                       "entries_per_matvec": E, "rhs_cols": k, "components": B, "sigma2": w.extra["sigma2"],
-                       "l2": "operands (134 MB vectors) exceed L2", "collective": "3 all_gather_into_tensor per iteration (search direction 134 MB, two arrays of partial inner products 1 MB)" if world > 1 else "none"},
-            "roofline": {
-                "bound": "tensor", "kernel": "matmul_sum_tc_kernel",
-                "achieved": tensor_flops / t_apply / 1e12, "peak": f16_peak, "unit": "TFLOP/s", "frac": frac_tensor,
-                "traffic": None, "frac_sfu": frac_sfu, "frac_fp32": frac_fp32, "product_ms": apply_ms,
-                "peak_source": "MEASURED_PEAKS.json bf16_tflops (burst; kind::f16 MMAs); tensor, SFU and FP32 bounds of this "
-                               "kernel lie within 25 % of each other (5.4 / 5.0 / 4.4 ms at config 5 on one GPU); SFU peak = "
-                               "148 SMs x 16 ops/clk x SM clock implied by the live FFMA probe.  The metric counts "
-                               "component entries (B per unique entry), as the reference would evaluate them",
-            },
-            "e2e": {"value": units * iters / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": (hy.numel() + hx.numel() + hp.numel()) * 4 // iters,
-                    "d2h_bytes_per_step": hsol.numel() * 4 // iters, "solve_ms": e2e_ms, "iterations": iters},
-            "gpu_launches": args.steps,
-            "clocks": clocks,
-        }
-        print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+# ------------------------------------------------------------------------------ single ops (configs 1, 3, 4)
 
 
-def run_single_op(args, local: int) -> None:
+def measure_single_op(name: str, dev, steps: int, fp32_peak: float, sfu_peak: float, with_ref: bool = True) -> dict:
     """The other benchmark configurations, one op each, on one GPU (inputs resident in HBM, CUDA
     events, L2 flushed between steps).  Workloads:
-      rbf_small                  config 1: RBF forward, n = 4096, k = 1 (launch-latency bound)
-      locally_periodic_bilinear  config 3: bilinear_derivative, batch 4, n = 262144, k = 32
-      rbf_unbanded               config 4: unbanded RBF forward, n = 131072, k = 128 (tensor cores)
-      rbf_unbanded_index         config 4: 2^24 random (row, col) gathers
+      rbf_small                  RBF forward, n = 4096, k = 1 (launch-latency bound)
+      locally_periodic_bilinear  bilinear_derivative, batch 4, n = 262144, k = 32
+      rbf_unbanded               unbanded RBF forward, n = 131072, k = 128 (tensor cores)
+      rbf_unbanded_index         2^24 random (row, col) gathers
     """
-    import ctypes
-
-    import kernel_matmul_b200  # noqa: F401
     from kernel_matmul_b200 import ops, ranges, workloads
-    from kernel_matmul_b200._lib import check, lib
 
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    name = args.workload
-    peaks = {}
-    ppath = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(ppath):
-        peaks = json.load(open(ppath))
-    flops = ctypes.c_double()
-    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
-
-    def probe():
-        check(lib.km_probe_fp32_peak(20000, None, ctypes.byref(flops), stream))
-
-    probe()
-    fp32_peak = max(flops.value / (cuda_ms(probe) * 1e-3) for _ in range(3)) / 1e12
-    sfu_ops = ctypes.c_double()
-
-    def probe_sfu():
-        check(lib.km_probe_sfu_peak(20000, None, ctypes.byref(sfu_ops), stream))
-
-    probe_sfu()
-    sfu_peak = max(sfu_ops.value / (cuda_ms(probe_sfu) * 1e-3) for _ in range(3)) / 1e12
-
+    peaks = measured_peaks()
+    ref = None
     if name == "rbf_small":
         w = workloads.rbf_small()
         x = w.x.to(dev)
@@ -688,6 +531,8 @@ def run_single_op(args, local: int) -> None:
         fn = lambda: ops.matmul(kt, x, x, rhs, params, start, end)  # noqa: E731
         model = {"bound": "launch latency", "fp32_instr": fp32_instr_fwd(kt, k), "sfu": GEN_FWD[kt][1]}
         units, kernel = E * k, "matmul_fma_cluster_kernel"
+        if with_ref:
+            ref = reference_cuda_timing("matmul", kt, k, (x, x, rhs, params, start, end))
     elif name == "locally_periodic_bilinear":
         w = workloads.locally_periodic_bilinear()
         B = w.params.shape[0]
@@ -698,9 +543,10 @@ def run_single_op(args, local: int) -> None:
         kt, k = "locally_periodic", w.rhs.shape[-1]
         E = int(ops.count_entries(w.n, w.n, start, end))
         fn = lambda: ops.bilinear_derivative(kt, xb, xb, lhs, rhs, params, start, end)  # noqa: E731
-        # tensor-core gradient (k <= 32): threads only evaluate the factors of d kappa / d p
         model = {"bound": "fp32", "fp32_instr": TC_BWD[kt][0], "sfu": TC_BWD[kt][1]}
         units, kernel = E * k, "grad_tc_kernel"
+        if with_ref:
+            ref = reference_cuda_timing("bilinear_derivative", kt, k, (xb, xb, lhs, rhs, params.contiguous(), start, end), reps=1)
     elif name == "rbf_unbanded":
         w = workloads.rbf_unbanded(lookups=16)
         x = w.x.to(dev)
@@ -708,9 +554,10 @@ def run_single_op(args, local: int) -> None:
         rhs, params = w.rhs.to(dev), w.params.to(dev)
         kt, k, E = "rbf", w.rhs.shape[-1], w.n * w.n
         fn = lambda: ops.matmul(kt, x, x, rhs, params, start, end)  # noqa: E731
-        # three fp16 MMAs (hi*lo, lo*hi, hi*hi) per product
         model = {"bound": "tensor", "tensor_flops": 3 * 2.0 * E * k, "fp32_instr": TC_FWD[kt][0], "sfu": TC_FWD[kt][1]}
         units, kernel = E * k, "matmul_tc_kernel"
+        if with_ref:
+            ref = reference_cuda_timing("matmul", kt, k, (x, x, rhs, params, start, end), reps=1)
     elif name == "rbf_unbanded_index":
         w = workloads.rbf_unbanded()
         x = w.x.to(dev)
@@ -725,20 +572,18 @@ def run_single_op(args, local: int) -> None:
         raise SystemExit(f"unknown workload {name}")
 
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(3):
         fn()
-    torch.cuda.synchronize()
-    sampler = ClockSampler(local)
+    ops.check(dev)
     ms = []
-    for _ in range(args.steps):
+    for _ in range(steps):
         flush.fill_(1)
         device_delay()
         ms.append(cuda_ms(fn))
-    clocks = sampler.stop()
+    ops.check(dev)
     t = statistics.mean(ms) * 1e-3
-    roof = {"bound": model["bound"], "kernel": kernel, "traffic": None}
+    roof = {"bound": model["bound"], "kernel": kernel, "traffic": dram_traffic(name, kernel)}
     if model["bound"] == "tensor":
-        # peak: the measured dense bf16 rate (kind::f16 MMAs run at the same rate)
         f16_peak = peaks.get("bf16_tflops", 1590.0)
         roof.update(achieved=model["tensor_flops"] / t / 1e12, peak=f16_peak, unit="TFLOP/s",
                     peak_source="MEASURED_PEAKS.json bf16_tflops (burst); achieved counts the 3 fp16 MMAs per product",
@@ -746,23 +591,262 @@ def run_single_op(args, local: int) -> None:
     elif model["bound"] == "hbm":
         roof.update(achieved=model["bytes"] / t / 1e9, peak=peaks.get("hbm_gbs", 6650.0), unit="GB/s",
                     peak_source="MEASURED_PEAKS.json hbm_gbs; algorithmic bytes = row + col + out per lookup")
-    elif model["bound"] == "sfu":
-        roof.update(achieved=E * model["sfu"] / t / 1e12, peak=sfu_peak, unit="Tops/s (special-function operations)",
-                    peak_source="live SFU probe (km_probe_sfu_peak); the coefficients run as tcgen05.mma",
-                    frac_fp32=2.0 * E * model["fp32_instr"] / t / 1e12 / fp32_peak)
     else:
         roof.update(achieved=2.0 * E * model["fp32_instr"] / t / 1e12, peak=fp32_peak, unit="TFLOP/s",
                     peak_source="live FFMA probe", frac_sfu=E * model["sfu"] / t / 1e12 / sfu_peak)
     roof["frac"] = roof["achieved"] / roof["peak"]
-    print(json.dumps({
+    res = {
         "metric": METRIC if name != "rbf_unbanded_index" else "gathered_kernel_entries_per_s",
-        "value": units / t, "unit": UNIT if name != "rbf_unbanded_index" else "entries/s", "n_gpus": 1,
-        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": t * 1e3, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "value": units / t, "unit": UNIT if name != "rbf_unbanded_index" else "entries/s", "steps": steps,
+        "ms_per_step": t * 1e3,
         "config": {"workload": w.name if name != "rbf_unbanded_index" else w.name + "_index", "entries": E, "rhs_cols": k,
                    "l2": "flushed between steps (256 MB write)"},
-        "roofline": roof, "gpu_launches": args.steps, "clocks": clocks,
-    }), flush=True)
+        "roofline": roof,
+    }
+    if ref is not None:
+        res["reference_cuda_kernels_same_gpu"] = ref
+    del flush
+    torch.cuda.empty_cache()
+    return res
+
+
+# ------------------------------------------------------------------------------------ CG (config 5)
+
+
+def run_cg(args, rank: int, world: int, local: int) -> None:
+    import kernel_matmul_b200  # noqa: F401  (raises if libkm_b200.so is missing: no fallback)
+    from kernel_matmul_b200 import host, ops, workloads
+    from kernel_matmul_b200.cg import CGSolver, ShardedOperator
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    w = make_workload(workloads, args.workload)
+    kt, n, k, B = w.kernel_type, w.n, w.rhs.shape[-1], w.params.shape[0]
+    x = w.x.to(dev)
+    params = w.params.to(dev)
+    y = w.rhs.to(dev)
+    start, end = workloads.band(w, x)
+    E = int(ops.count_entries(n, n, start, end))  # over all components
+    units = float(E) * k
+    op = ShardedOperator.from_kernel(kt, x, params, start[0], end[0], w.extra["sigma2"], mode=args.exchange)
+    fp32_peak, sfu_peak = live_peaks(dev)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+
+    # a running solve: the first iterations are warm-up, then K timed iterations
+    warm = max(args.warmup, 3)
+    solver = CGSolver(op, y, max_iterations=warm + args.steps + 8)
+    matvec = op.matvec_rows
+    product_events = []
+
+    def timed_matvec(v, b, c, out):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        matvec(v, b, c, out)
+        e1.record()
+        product_events.append((e0, e1))
+
+    for _ in range(warm):
+        solver.step()
+    solver.check_finite()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    op.matvec_rows = timed_matvec
+    sampler = ClockSampler(local)
+    wall0 = time.perf_counter()
+    step_events = []
+    for _ in range(args.steps):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        solver.step()
+        e1.record()
+        step_events.append((e0, e1))
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - wall0
+    clocks = sampler.stop()
+    op.matvec_rows = matvec
+    total_ms = sum(a.elapsed_time(b) for a, b in step_events)
+    product_ms = statistics.mean(a.elapsed_time(b) for a, b in product_events) if product_events else 0.0
+    solver.check_finite()
+    residual = float(solver.residual_norms()[-1].max())
+    del solver
+
+    # end to end: whole solves from host buffers (x, params, this rank's rows of Y in; its rows of V out)
+    iters = int(w.extra["iterations"])
+    hy, hx, hp = w.rhs.contiguous().pin_memory(), w.x.pin_memory(), w.params.contiguous().pin_memory()
+    hsol = torch.empty(n, k).pin_memory()
+
+    def solve_e2e():
+        return host.cg_solve_from_host(kt, hx, hp, hy, w.cutoffs[0], w.extra["sigma2"], iters, hsol, dev, mode=args.exchange)
+
+    solve_e2e()  # warm-up (allocator, NCCL buffers)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e2e_runs = []
+    for _ in range(2):
+        e2e_runs.append(cuda_ms(solve_e2e))
+    e2e_ms = statistics.mean(e2e_runs)
+    h2d = (hx.numel() + hp.numel() + (op.hi - op.lo) * k) * 4
+    d2h = op.rows * k * 4
+
+    stats = torch.tensor([total_ms, e2e_ms, product_ms, float(h2d), float(d2h)], device=dev, dtype=torch.float64)
+    if world > 1:
+        mx = stats.clone()
+        dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone()
+        dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms, e2e_ms, product_ms = float(mx[0]), float(mx[1]), float(mx[2])
+        h2d, d2h = float(sm[3]), float(sm[4])
+
+    if rank == 0:
+        peaks = measured_peaks()
+        ms_per_step = total_ms / args.steps
+        # All components share inputs, band and lengthscale, so the batch sum runs on the tensor
+        # cores (matmul_sum_tc_kernel): sum_b s_b cos(w_b tau) = <phi(x_i), psi(x_j)> with 2B-vectors
+        # of per-point phases.  Per UNIQUE (row, column) entry: three fp16 MMAs of 2B multiply-adds,
+        # one envelope exponential + 2B / 128 SFU operations for the column's phase vector (shared by
+        # the 128 rows of the block), and k + ~6 FP32 operations.  Row windows are equal, so a rank's
+        # launch does 1 / N of it.
+        e_unique = E / B / world
+        t_prod = product_ms * 1e-3
+        tensor_flops = e_unique * 3 * 2 * (2 * B)
+        f16_peak = peaks.get("bf16_tflops", 1590.0)
+        traffic = dram_traffic("cg_sum", "matmul_sum_tc_kernel") if args.workload == "cg_sum" else None
+        roofline = {
+            "bound": "tensor", "kernel": "matmul_sum_tc_kernel", "achieved": tensor_flops / t_prod / 1e12, "peak": f16_peak,
+            "unit": "TFLOP/s", "frac": tensor_flops / t_prod / 1e12 / f16_peak,
+            "traffic": traffic / world if traffic else None,
+            "traffic_source": "profiles/dram_traffic.json: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of "
+                              "the full single-GPU launch (profiles/matmul_sum_tc_kernel_cg_sum.md), copied by hand; divided "
+                              "by the number of ranks (traffic grows with the rows of a launch)",
+            "product_ms": product_ms, "algorithmic_tensor_flops_per_launch": tensor_flops,
+            "frac_of_sustained_bf16": tensor_flops / t_prod / 1e12 / peaks.get("bf16_tflops_sustained", 1400.0),
+            "frac_sfu": e_unique * (1 + 2 * B / 128) / t_prod / 1e12 / sfu_peak,
+            "frac_fp32": 2.0 * e_unique * (k + 6) / t_prod / 1e12 / fp32_peak,
+            "fp32_peak_tflops": fp32_peak, "sfu_peak_tops": sfu_peak,
+            "peak_source": ("MEASURED_PEAKS.json bf16_tflops (burst; kind::f16 MMAs run at the bf16 rate)" if peaks else
+                            "fallback 1590 TFLOP/s (MEASURED_PEAKS.json absent)") +
+                           "; product_ms = mean CUDA-event time around the product inside the timed iterations (it also "
+                           "covers the FMA-pipe companion launch whose CTAs leave at once); SFU and FP32 fractions against "
+                           "the library's live calibration kernels.  The metric counts component entries (B per unique "
+                           "entry), as the reference would evaluate them",
+        }
+        line = {
+            "metric": METRIC, "value": units / (ms_per_step * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": warm, "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": config_of(w, E),
+            "exchange": op.mode,
+            "collective": {"single": "none (one rank)",
+                           "halo": f"2 NCCL all_gather_into_tensor per iteration: [{op.halo_above} + {op.halo_below} halo rows "
+                                   f"of q + segment sums of p.q] and [segment sums of r.r]",
+                           "allgather": "3 NCCL all_gather_into_tensor per iteration: q (all rows, n x k fp32) and two sets "
+                                        "of segment sums"}[op.mode],
+            "l2": "flushed between iterations (256 MB write, outside the event pairs)",
+            "roofline": roofline,
+            "e2e": {"value": units * iters / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d / iters,
+                    "d2h_bytes_per_step": d2h / iters, "solve_ms": e2e_ms, "iterations": iters,
+                    "what": "host.cg_solve_from_host: pinned host x, params, Y rows in; band, operator set-up, "
+                            f"{iters} iterations; solution rows out"},
+            # per iteration: product (tensor-core kernel + FMA-pipe companion), q/dots, 2 x segment sums, 2 x update
+            "gpu_launches": 7 * args.steps,
+            "relative_residual_after_timed_region": residual,
+            "clocks": clocks, "wall_s": wall,
+        }
+    if rank == 0 and not args.no_secondary and world == 1:
+        sec = {}
+        del flush, y
+        torch.cuda.empty_cache()
+        sec["spectral_mixture"] = measure_mixture(workloads.spectral_mixture(), dev, min(args.steps, 10), args.path, fp32_peak,
+                                                  sfu_peak, with_e2e=True, with_ref=True)
+        for name in ("rbf_unbanded", "locally_periodic_bilinear", "rbf_unbanded_index", "rbf_small"):
+            sec[name] = measure_single_op(name, dev, min(args.steps, 5), fp32_peak, sfu_peak)
+        line["secondary"] = sec
+    if rank == 0:
+        if not args.no_cpu:
+            line["cpu_baseline"] = cpu_dense_sample_cg(w)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_mixture(args, rank: int, world: int, local: int) -> None:
+    """``--workload spectral_mixture``: forward + matmul_bwd of 16 spectral components; with N > 1
+    every rank runs its own copy (independent work, no collective, weak scaling)."""
+    import kernel_matmul_b200  # noqa: F401
+    from kernel_matmul_b200 import workloads
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+    w = make_workload(workloads, args.workload)
+    fp32_peak, sfu_peak = live_peaks(dev)
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local)
+    res = measure_mixture(w, dev, args.steps, args.path, fp32_peak, sfu_peak, with_e2e=True, with_ref=(rank == 0))
+    clocks = sampler.stop()
+    ms, e2e_ms = res["ms_per_step"], res["e2e"]["ms_per_step"]
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        units = res["config"]["units_per_step"] * world
+        kernels = res["kernels"]
+        dom = max(kernels, key=lambda kn: kernels[kn]["ms"])
+        d = kernels[dom]
+        line = {
+            "metric": METRIC, "value": units / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": 3, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "config": res["config"], "path": args.path, "l2": res["l2"],
+            "per_rank": "own batch of components (same seeded parameters on every rank), no collective",
+            "roofline": {"bound": "fp32", "kernel": dom, "achieved": d["achieved_tflops"], "peak": fp32_peak, "unit": "TFLOP/s",
+                         "frac": d["frac_fp32"], "traffic": d["traffic"], "traffic_source": "profiles/dram_traffic.json",
+                         "peak_source": "measured live: km_probe_fp32_peak (FFMA issue rate of all SMs)",
+                         "fp32_peak_tflops": fp32_peak, "sfu_peak_tops": sfu_peak, "kernels": kernels},
+            "e2e": {**res["e2e"], "value": units / (e2e_ms * 1e-3), "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": res["e2e"]["h2d_bytes_per_step"] * world,
+                    "d2h_bytes_per_step": res["e2e"]["d2h_bytes_per_step"] * world},
+            "gpu_launches": res["gpu_launches_per_step"] * args.steps, "clocks": clocks,
+        }
+        if "reference_cuda_kernels_same_gpu" in res:
+            line["reference_cuda_kernels_same_gpu"] = res["reference_cuda_kernels_same_gpu"]
+        if not args.no_cpu:
+            line["cpu_baseline"] = cpu_dense_sample_mixture(w)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_single(args, local: int) -> None:
+    import kernel_matmul_b200  # noqa: F401
+
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    fp32_peak, sfu_peak = live_peaks(dev)
+    sampler = ClockSampler(local)
+    res = measure_single_op(args.workload, dev, args.steps, fp32_peak, sfu_peak)
+    res.update({"n_gpus": 1, "warmup": 3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                "data": "synthetic", "gpu_launches": args.steps, "clocks": sampler.stop()})
+    print(json.dumps(res), flush=True)
 
 
 def main() -> None:
@@ -771,26 +855,29 @@ def main() -> None:
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="spectral_mixture")
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD)
+    ap.add_argument("--exchange", default="auto", choices=["auto", "halo", "allgather"],
+                    help="CG workloads: what the ranks exchange per iteration (auto: halo rows for a banded operator)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-secondary", action="store_true", help="skip the other configurations (N = 1)")
     ap.add_argument("--path", default="auto", choices=["auto", "fma", "tc"],
-                    help="default workload: kernels of the ops (auto: what the ops choose; fma: FMA-pipe kernels; "
-                         "tc: tensor-core kernels)")
+                    help="spectral-mixture workload: kernels of the ops (auto: what the ops choose; fma: FMA-pipe "
+                         "kernels; tc: tensor-core kernels)")
     args = ap.parse_args()
     rank, world, local = dist_env()
     if args.impl == "reference":
-        if args.workload != "spectral_mixture" and args.workload != "spectral_mixture_small":
+        if not (args.workload.startswith("cg_sum") or args.workload.startswith("spectral_mixture")):
             if rank == 0:
-                print(json.dumps({"impl": "reference", "unavailable": "CPU leg implemented for the default workload only"}))
+                print(json.dumps({"impl": "reference", "unavailable": "CPU leg implemented for the CG and spectral-mixture workloads"}))
             return
         run_reference(args, rank, world)
     elif args.workload.startswith("cg_sum"):
         run_cg(args, rank, world, local)
     elif args.workload in ("rbf_small", "locally_periodic_bilinear", "rbf_unbanded", "rbf_unbanded_index"):
         if rank == 0:
-            run_single_op(args, local)
+            run_single(args, local)
     else:
-        run_ours(args, rank, world, local)
+        run_mixture(args, rank, world, local)
 
 
 if __name__ == "__main__":

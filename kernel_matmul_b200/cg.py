@@ -278,7 +278,11 @@ def _round_up(v: int, to: int) -> int:
 
 class CGSolver:
     """State of a running solve; ``step()`` is one CG iteration.  All buffers are allocated here;
-    ``step()`` allocates nothing and never synchronises with the host."""
+    ``step()`` allocates nothing and never synchronises with the host.
+
+    ``y`` is the full ``(n, k)`` right-hand side, on the operator's device or in (pinned) host
+    memory; only the rows this rank keeps current, ``[op.lo, op.hi)``, are read (and, from host
+    memory, copied)."""
 
     def __init__(self, op: ShardedOperator, y: Tensor, max_iterations: int = 256):
         if y.dim() != 2 or y.shape[0] != op.n:
@@ -286,22 +290,22 @@ class CGSolver:
         self.op = op
         self.k = k = y.shape[-1]
         dev, dt = y.device, y.dtype
+        if not y.is_cuda and op.device is not None and op.device.type == "cuda":
+            dev = op.device  # right-hand side in host memory
         self.V = op.vector_ops
         if self.V is None:
-            if not y.is_cuda or dt != torch.float32:
+            if dev.type != "cuda" or dt != torch.float32:
                 raise RuntimeError("the CG kernels need float32 CUDA tensors (there is no CPU path)")
             self.V = CudaVectorOps(dev)
         esz = y.element_size()
         n_pad = max(op.n, op.world * op.per_rows)  # every rank's padded window exists in every vector
         self.x = torch.zeros(n_pad, k, device=dev, dtype=dt)
-        self.r = torch.empty(n_pad, k, device=dev, dtype=dt)
-        self.p = torch.empty(n_pad, k, device=dev, dtype=dt)
+        self.r = torch.zeros(n_pad, k, device=dev, dtype=dt)
+        self.p = torch.zeros(n_pad, k, device=dev, dtype=dt)
         self.kp = torch.zeros(n_pad, k, device=dev, dtype=dt)
-        self.r[: op.n] = y
-        self.p[: op.n] = y
-        if n_pad > op.n:
-            self.r[op.n:].zero_()
-            self.p[op.n:].zero_()
+        if op.hi > op.lo:
+            self.r[op.lo: op.hi].copy_(y[op.lo: op.hi], non_blocking=True)
+            self.p[op.lo: op.hi].copy_(self.r[op.lo: op.hi])
         self.bp = torch.zeros(max(op.count, 1), k, device=dev, dtype=dt)
         self.rs = torch.zeros(2, k, device=dev, dtype=dt)
         self.ynorm = torch.ones(k, device=dev, dtype=dt)
@@ -380,6 +384,10 @@ class CGSolver:
         flags = bad.tolist()
         if any(flags):
             raise RuntimeError(f"non-finite residual after {self.it} iterations on rank(s) {[i for i, f in enumerate(flags) if f]}")
+
+    def solution_rows(self) -> Tensor:
+        """This rank's rows ``[op.row0, op.row1)`` of the iterate (a view; no communication)."""
+        return self.x[self.op.row0: self.op.row1]
 
     def solution(self) -> Tensor:
         """The full iterate on every rank."""

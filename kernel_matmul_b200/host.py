@@ -85,3 +85,43 @@ def matmul_and_grad_from_host(
         grad.copy_(d_grad, non_blocking=True)
     d_grad.record_stream(streams.copy_out)
     cur.wait_stream(streams.copy_out)
+
+
+def cg_solve_from_host(
+    kernel_type: str,
+    x: Tensor,
+    params: Tensor,
+    y: Tensor,
+    cutoff: float | None,
+    sigma2: float,
+    iterations: int,
+    out: Tensor,
+    device: torch.device,
+    *,
+    group=None,
+    mode: str = "auto",
+):
+    """``(sum_b K_b(x, x; params[b]) + sigma2 I) V = y`` by ``iterations`` steps of the row-sharded CG,
+    for operands in (pinned) host memory.
+
+    ``x (n,)``, ``params (B, P)`` or ``(P,)``, ``y (n, k)`` and ``out (n, k)`` are host tensors.  Every
+    rank copies ``x`` and ``params`` in full (the band is built from all of ``x``) but of ``y`` only
+    the rows it keeps current (its own rows plus the band's halo), runs the solve, and copies ITS
+    rows of the solution into ``out[row0:row1]`` -- nothing else of ``out`` is written.  Returns
+    ``(solver, (row0, row1))``; the copy out is asynchronous on the current stream.  The reference
+    has no counterpart: its solves go through ``linear_operator``'s CG on device tensors
+    (tests/test_linear_operator.py:38).
+    """
+    from . import ranges
+    from .cg import CGSolver, ShardedOperator
+
+    dx = x.to(device, non_blocking=True)
+    dp = params.to(device, non_blocking=True)
+    start, end = ranges.make_ranges(cutoff, dx)
+    op = ShardedOperator.from_kernel(kernel_type, dx, dp, start, end, sigma2, group=group, mode=mode)
+    solver = CGSolver(op, y, max_iterations=max(iterations, 1))
+    for _ in range(iterations):
+        solver.step()
+    if op.rows > 0:
+        out[op.row0: op.row1].copy_(solver.solution_rows(), non_blocking=True)
+    return solver, (op.row0, op.row1)
