@@ -85,6 +85,16 @@ def fp32_instr_bwd(kt: str, k: int) -> int:
 # ------------------------------------------------------------------------------------ helpers
 
 
+_T0 = time.perf_counter()
+TRACE = bool(os.environ.get("KM_BENCH_TRACE"))
+
+
+def trace(msg: str) -> None:
+    """Progress lines on stderr (``--trace`` or KM_BENCH_TRACE=1): where a slow run spends its time."""
+    if TRACE:
+        print(f"[bench {time.perf_counter() - _T0:7.2f} s] {msg}", file=sys.stderr, flush=True)
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -406,6 +416,7 @@ def reference_cuda_timing(kind: str, kernel_type: str, k: int, call_args: tuple,
                 torch.cuda.synchronize()
                 ts.append(1e3 * (time.perf_counter() - t0))
             tried += 1
+            trace(f"reference module {name}: {min(ts):.3f} ms")
             if best is None or min(ts) < best[0]:
                 best = (min(ts), name)
         except Exception as exc:  # noqa: BLE001 - informational only
@@ -634,8 +645,10 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
     E = int(ops.count_entries(n, n, start, end))  # over all components
     units = float(E) * k
     op = ShardedOperator.from_kernel(kt, x, params, start[0], end[0], w.extra["sigma2"], mode=args.exchange)
+    trace(f"operator ready: mode {op.mode}, rows [{op.row0}, {op.row1}), kept current [{op.lo}, {op.hi})")
     fp32_peak, sfu_peak = live_peaks(dev)
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
+    trace("peaks probed")
 
     # a running solve: the first iterations are warm-up, then K timed iterations
     warm = max(args.warmup, 3)
@@ -654,6 +667,7 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
         solver.step()
     solver.check_finite()
     torch.cuda.synchronize()
+    trace("warm-up iterations done")
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
@@ -674,6 +688,7 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
     torch.cuda.synchronize()
     wall = time.perf_counter() - wall0
     clocks = sampler.stop()
+    trace("timed iterations done")
     op.matvec_rows = matvec
     total_ms = sum(a.elapsed_time(b) for a, b in step_events)
     product_ms = statistics.mean(a.elapsed_time(b) for a, b in product_events) if product_events else 0.0
@@ -697,6 +712,7 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
     for _ in range(2):
         e2e_runs.append(cuda_ms(solve_e2e))
     e2e_ms = statistics.mean(e2e_runs)
+    trace("end-to-end solves done")
     h2d = (hx.numel() + hp.numel() + (op.hi - op.lo) * k) * 4
     d2h = op.rows * k * 4
 
@@ -770,12 +786,15 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
         torch.cuda.empty_cache()
         sec["spectral_mixture"] = measure_mixture(workloads.spectral_mixture(), dev, min(args.steps, 10), args.path, fp32_peak,
                                                   sfu_peak, with_e2e=True, with_ref=True)
+        trace("secondary: spectral mixture done")
         for name in ("rbf_unbanded", "locally_periodic_bilinear", "rbf_unbanded_index", "rbf_small"):
             sec[name] = measure_single_op(name, dev, min(args.steps, 5), fp32_peak, sfu_peak)
+            trace(f"secondary: {name} done")
         line["secondary"] = sec
     if rank == 0:
         if not args.no_cpu:
             line["cpu_baseline"] = cpu_dense_sample_cg(w)
+            trace("CPU baseline done")
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -863,7 +882,10 @@ def main() -> None:
     ap.add_argument("--path", default="auto", choices=["auto", "fma", "tc"],
                     help="spectral-mixture workload: kernels of the ops (auto: what the ops choose; fma: FMA-pipe "
                          "kernels; tc: tensor-core kernels)")
+    ap.add_argument("--trace", action="store_true", help="progress lines on stderr")
     args = ap.parse_args()
+    global TRACE
+    TRACE = TRACE or args.trace
     rank, world, local = dist_env()
     if args.impl == "reference":
         if not (args.workload.startswith("cg_sum") or args.workload.startswith("spectral_mixture")):

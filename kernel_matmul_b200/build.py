@@ -77,7 +77,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     # The CUDA runtime is linked statically: the library is self-contained and shares the
     # primary context (and therefore streams and allocations) with whatever else is loaded.
     cmd = [_nvcc(), "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a",
-           "-cudart", "static"]
+           "-cudart", "static", "-Xlinker", "-soname=libkm_b200.so"]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
@@ -85,5 +85,39 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+TORCH_SRC = os.path.join(HERE, "csrc_torch", "km_torch.cpp")
+TORCH_EXT = os.path.join(HERE, "_C.so")
+
+
+def build_torch_extension(force: bool = False) -> str:
+    """Compile ``csrc_torch/km_torch.cpp`` into ``kernel_matmul_b200/_C.so``: the PyTorch C++
+    extension over the C ABI (needs the PyTorch headers of the running interpreter and g++; no
+    GPU).  It links against ``libkm_b200.so`` next to it (rpath ``$ORIGIN``)."""
+    build()
+    deps = [TORCH_SRC, HEADER, LIB, os.path.abspath(__file__)]
+    if not force and os.path.exists(TORCH_EXT) and all(os.path.getmtime(d) <= os.path.getmtime(TORCH_EXT) for d in deps):
+        return TORCH_EXT
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension
+
+    includes = cpp_extension.include_paths("cuda") + [sysconfig.get_paths()["include"]]
+    torch_lib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cuda_lib = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "lib64")
+    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", "-DTORCH_EXTENSION_NAME=_C",
+           "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           *[f"-I{p}" for p in includes], TORCH_SRC, "-o", TORCH_EXT,
+           f"-L{HERE}", "-lkm_b200", f"-L{torch_lib}", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch",
+           "-ltorch_python", f"-L{cuda_lib}", "-lcudart", "-Wl,-rpath,$ORIGIN", f"-Wl,-rpath,{torch_lib}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("build of the PyTorch extension kernel_matmul_b200/_C.so failed")
+    return TORCH_EXT
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--torch" in sys.argv:
+        print(build_torch_extension(force="--force" in sys.argv))

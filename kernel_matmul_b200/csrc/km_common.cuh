@@ -216,6 +216,15 @@ struct KernelFn<KM_KERNEL_RBF> {
         sums[0] = fmaf(v, t2, sums[0]);
         sums[1] += v;
     }
+    // the same with full-precision library functions instead of the SFU approximations: for the
+    // gather gradient, which adds few terms per batch (no averaging of the approximation errors)
+    // and is bound by memory latency, not arithmetic
+    __device__ __forceinline__ void accumulate_precise(float tau, float coeff, float *sums) const {
+        const float t2 = tau * tau;
+        const float v = coeff * exp2f(c0 * t2);
+        sums[0] = fmaf(v, t2, sums[0]);
+        sums[1] += v;
+    }
     // the same for two entries at once with packed FP32 operations (half the issue slots);
     // sums2[q] holds the two partial sums of sums[q]
     __device__ __forceinline__ void accumulate2(f32x2 tau, f32x2 coeff, f32x2 *sums2) const {
@@ -246,13 +255,14 @@ template <>
 struct KernelFn<KM_KERNEL_SPECTRAL> {
     static constexpr int P = 3;
     static constexpr int NSUMS = 3;
-    float c0, w, scale, ell;
+    float c0, w, scale, ell, f2;
     __device__ __forceinline__ void init(const float *theta, int64_t stride) {
         ell = theta[0];
         const float f = theta[stride];
         scale = theta[2 * stride];
         c0 = -(0.5f / (ell * ell)) * KM_LOG2E_F;
         w = 2.0f * KM_PI_F * f;
+        f2 = 2.0f * f;  // the phase in units of pi: cos(pi * f2 * tau), as the reference evaluates it
     }
     __device__ __forceinline__ float unscaled(float tau) const {
         return ex2_approx(c0 * tau * tau) * cos_approx(w * tau);
@@ -266,6 +276,16 @@ struct KernelFn<KM_KERNEL_SPECTRAL> {
         const float vs = v * sin_approx(ph);
         sums[0] = fmaf(vc, t2, sums[0]);
         sums[1] = fmaf(vs, tau, sums[1]);
+        sums[2] += vc;
+    }
+    __device__ __forceinline__ void accumulate_precise(float tau, float coeff, float *sums) const {
+        const float t2 = tau * tau;
+        float sn, cs;
+        sincospif(f2 * tau, &sn, &cs);  // exact argument reduction
+        const float v = coeff * exp2f(c0 * t2);
+        const float vc = v * cs;
+        sums[0] = fmaf(vc, t2, sums[0]);
+        sums[1] = fmaf(v * sn, tau, sums[1]);
         sums[2] += vc;
     }
     __device__ __forceinline__ void accumulate2(f32x2 tau, f32x2 coeff, f32x2 *sums2) const {
@@ -319,6 +339,17 @@ struct KernelFn<KM_KERNEL_LOCALLY_PERIODIC> {
         c0 = -(0.5f / (ell * ell)) * KM_LOG2E_F;
         c1 = -(2.0f / ell_per) * KM_LOG2E_F;
         w = KM_PI_F / period;
+    }
+    __device__ __forceinline__ void accumulate_precise(float tau, float coeff, float *sums) const {
+        float sn, cs;
+        sincospif(tau / period, &sn, &cs);  // exact argument reduction
+        const float t2 = tau * tau;
+        const float sn2 = sn * sn;
+        const float v = coeff * exp2f(fmaf(c0, t2, c1 * sn2));
+        sums[0] = fmaf(v, t2, sums[0]);
+        sums[1] = fmaf(v, sn2, sums[1]);
+        sums[2] = fmaf(v * sn, cs * tau, sums[2]);
+        sums[3] += v;
     }
     __device__ __forceinline__ float unscaled(float tau) const {
         const float sn = sin_approx(w * tau);

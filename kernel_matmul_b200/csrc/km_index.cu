@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(256) index_bwd_kernel(const IndexArgs a) {
             } else {
                 cur = 0;
             }
-            fn.accumulate(tau, a.out_grad[l], sums);
+            fn.accumulate_precise(tau, a.out_grad[l], sums);
         }
     }
 

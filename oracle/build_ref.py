@@ -23,8 +23,8 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 OUT = os.path.join(HERE, "_ref")
-# where the reference project is mounted (read-only); override with KM_REFERENCE_DIR
-REFERENCE_DIR = os.environ.get("KM_REFERENCE_DIR", "/root/reference")
+# where the reference project lies (read-only): the environment variable KM_REFERENCE_DIR or --reference
+REFERENCE_DIR = os.environ.get("KM_REFERENCE_DIR", "")
 
 KERNEL_DEFINE = {
     "rbf": "KERNEL_RBF",
@@ -94,6 +94,33 @@ def module_specs() -> list[tuple[str, str, dict]]:
     return specs
 
 
+# (kernel type, rhs columns) of the benchmark configurations whose forward product the reference's
+# autotuner would tune: small RBF (k = 1), spectral mixture (k = 16), one component of the CG
+# operator (k = 8), unbanded RBF (k = 128).
+TUNED_PRODUCTS = [("rbf", 1), ("spectral", 16), ("spectral", 8), ("rbf", 128)]
+
+
+def tuned_matmul_specs() -> list[tuple[str, str, dict]]:
+    """The candidates ``MatmulAutotuneConfiguration.make_candidates`` would time
+    (kernel_matmul/configurations.py:94-118): 3 thread shapes x 4 COL_BLOCKS, and for k > 32
+    three K_BLOCK sizes.  bench.py times them all on the GPU and quotes the fastest."""
+    specs = []
+    for kt, k in TUNED_PRODUCTS:
+        base = {"BLOCK_SIZE": 128, "BATCH_DIM": 1, KERNEL_DEFINE[kt]: None, "MATMUL_USE_SHM": 1}
+        k_blocks = [k] if k <= 32 else [16, 32, 64]
+        for threads, per in ((32, 4), (64, 2), (128, 1)):
+            for cb in (1, 4, 8, 16):
+                for kb in k_blocks:
+                    if (threads, per, cb) == (64, 2, 1) and kb == k:
+                        continue  # the single configuration, built as km_ref_matmul_<kt>_k<k>
+                    specs.append((
+                        f"km_ref_matmul_{kt}_k{k}_t{threads}x{per}_c{cb}_kb{kb}", "matmul",
+                        base | {"MATMUL_K_BLOCK_SIZE": kb, "MATMUL_THREADS": threads, "MATMUL_PER_THREAD": per,
+                                "MATMUL_COL_BLOCKS": cb},
+                    ))
+    return specs
+
+
 def build_one(reference: str, name: str, op: str, defines: dict) -> str:
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0")
     os.environ.setdefault("MAX_JOBS", "2")
@@ -128,12 +155,15 @@ def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", default=REFERENCE_DIR)
     ap.add_argument("--only", default=None, help="substring filter on module names")
+    ap.add_argument("--tuned", action="store_true",
+                    help="also build the reference's autotune candidates of the forward product for the benchmark widths")
     ap.add_argument("-j", type=int, default=4)
     args = ap.parse_args()
     if not os.path.isdir(os.path.join(args.reference, "native")):
         print(f"reference tree not found at {args.reference}; nothing built")
         return 0
-    specs = [s for s in module_specs() if args.only is None or args.only in s[0]]
+    specs = module_specs() + (tuned_matmul_specs() if args.tuned else [])
+    specs = [s for s in specs if args.only is None or args.only in s[0]]
     failed = []
     with concurrent.futures.ProcessPoolExecutor(max_workers=args.j) as pool:
         futs = {pool.submit(build_one, args.reference, *s): s[0] for s in specs}

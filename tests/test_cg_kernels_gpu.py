@@ -75,7 +75,11 @@ def test_vector_kernels_match_the_stand_in(k, layout):
     assert _close(a["bp"], b["bp"], 1e-5)
     segs = -(-cnt // seg_blocks)
     assert _close(a["send"][: segs * k * 8].view(torch.float64), b["send"][: segs * k * 8].view(torch.float64), 1e-5)
-    assert torch.equal(a["send"][a["top_off"]:], b["send"][b["top_off"]:])  # halo copies are copies
+    tr, br = min(top_rows, row1 - row0), min(bottom_rows, row1 - row0)
+    for st in (a, b):  # the halo copies are bit-exact copies of the rank's first / last rows of q
+        top = st["send"][st["top_off"]: st["top_off"] + tr * k * 4].view(torch.float32).view(tr, k)
+        bottom = st["send"][st["bottom_off"]: st["bottom_off"] + br * k * 4].view(torch.float32).view(br, k)
+        assert torch.equal(top, st["kp"][row0: row0 + tr]) and torch.equal(bottom, st["kp"][row1 - br: row1])
 
     q_below = (a["g1"], 0 * a["packed"] + a["bottom_off"], row0 - bottom_rows) if below else (None, 0, 0)
     q_above = (a["g1"], 2 * a["packed"] + a["top_off"], row1) if above else (None, 0, 0)

@@ -122,3 +122,21 @@ def test_workload_generators_are_deterministic():
     w = workloads.spectral_mixture(n=1024, components=4, k=2)
     assert w.params.shape == (4, 3) and len(w.cutoffs) == 4 and w.extra["out_grad"].shape == (4, 1024, 2)
     assert bool((w.x[1:] >= w.x[:-1]).all())
+
+
+def test_torch_extension_exports_the_ten_reference_functions():
+    """The ahead-of-time PyTorch extension loads without a GPU and refuses CPU tensors with the
+    reference's message (native/common/entrypoint.h:3-5)."""
+    import kernel_matmul_b200  # noqa: F401  (loads libkm_b200.so, which the extension links against)
+    from kernel_matmul_b200 import _C
+
+    for name in ("matmul", "matmul_bwd", "bilinear_derivative", "dense", "dense_bwd", "index", "index_bwd",
+                 "make_ranges", "make_ranges_symmetric", "transpose_ranges"):
+        assert callable(getattr(_C, name)), name
+    assert (_C.KERNEL_RBF, _C.KERNEL_SPECTRAL, _C.KERNEL_LOCALLY_PERIODIC) == (0, 1, 2)
+    x = torch.rand(10)
+    s = torch.zeros(1, dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="x must be a CUDA tensor"):
+        _C.matmul(0, x, x, torch.rand(10, 1), torch.ones(2), s, s)
+    with pytest.raises(RuntimeError, match="x must be a CUDA tensor"):
+        _C.make_ranges_symmetric(x[None], 1.0, 128)

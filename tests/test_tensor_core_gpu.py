@@ -67,9 +67,12 @@ def test_tc_product_unbanded_and_empty_bands():
     assert rel_err(out, O.matmul("rbf", x1, x2, rhs, params, start, end)) <= 1e-5
 
 
-def test_tc_product_reports_its_workspace():
+def test_tc_product_says_that_it_ran_on_the_tensor_cores():
+    from kernel_matmul_b200 import ops
+
     out = _run("rbf", 300, 300, 64, square=True)
     assert ops.used_tensor_cores(out)
+    ops.check()
 
 
 # ------------------------------------------------------------------ GEMM widths 16 / 32 / 64 / 128
