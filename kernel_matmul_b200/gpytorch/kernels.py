@@ -10,7 +10,6 @@ kernel for its four parameters).
 """
 from __future__ import annotations
 
-import math
 from typing import Any
 
 import torch
@@ -19,8 +18,8 @@ from gpytorch.kernels import Kernel
 from gpytorch.priors import Prior
 from torch import Size, Tensor, nn
 
+from ..kernels import band_for, same_tensor
 from ..linear_operator import KernelMatmulLinearOperator
-from ..ranges import make_ranges, make_ranges_symmetric_cutoffs
 
 
 class KernelMatmulKernel(Kernel):
@@ -85,36 +84,15 @@ class KernelMatmulKernel(Kernel):
     def _get_largest_lengthscale(self) -> float:
         return max(getattr(self, name).max().item() for name in self._LENGTHSCALES)
 
-    def _cutoff_now(self) -> float | None:
-        if self._epsilon is not None:
-            # |tau| beyond which a unit Gaussian of the largest lengthscale holds less than epsilon
-            z = math.sqrt(2.0) * torch.special.erfinv(torch.tensor(1.0 - self._epsilon)).item()
-            return z * self._get_largest_lengthscale()
-        return self._cutoff
-
-    def _cutoff_on_device(self) -> Tensor:
-        """The dynamic cutoff of ``_cutoff_now`` as a 0-dim fp32 tensor on the parameters' device,
-        computed without a host synchronisation (kernel_matmul/gpytorch/base.py:59-64 reads the
-        largest lengthscale back with ``.item()`` on every forward)."""
-        z = math.sqrt(2.0) * torch.special.erfinv(torch.tensor(1.0 - self._epsilon)).item()
-        largest = torch.stack([getattr(self, name).detach().max() for name in self._LENGTHSCALES]).max()
-        return (largest.double() * z).float()
-
     def forward(self, x1: Tensor, x2: Tensor, diag: bool = False, last_dim_is_batch: bool = False, **params):
         if last_dim_is_batch:
             raise NotImplementedError("last_dim_is_batch not supported for KernelMatmulKernel")
-        symmetric = x1.shape == x2.shape and torch.equal(x1, x2)
-        xs = x1.squeeze(-1)
-        if symmetric and self._epsilon is not None and xs.is_cuda and xs.dim() == 1:
-            # dynamic cutoff without reading the lengthscale back to the host: the band is built on
-            # the device from a device-resident cutoff (same value: double product, rounded to fp32)
-            start, end = make_ranges_symmetric_cutoffs(self._cutoff_on_device().reshape(1), xs)
-            start, end = start[0], end[0]
-        elif symmetric:
-            cutoff = self._cutoff_now()
-            start, end = make_ranges(cutoff, xs, align=True)
-        else:
-            start, end = make_ranges(self._cutoff_now(), xs, x2.squeeze(-1), align=True)
+        # x1 == x2 from the tensors' identity where possible, and the band (fixed cutoff or epsilon
+        # rule) built on the device: no host synchronisation on the training path
+        # (kernel_matmul/gpytorch/base.py:56-66 compares contents and reads the lengthscale back)
+        symmetric = same_tensor(x1, x2) or (x1.shape == x2.shape and torch.equal(x1, x2))
+        start, end = band_for(x1, x2, symmetric, self._cutoff, self._epsilon,
+                              [getattr(self, name) for name in self._LENGTHSCALES])
         operator = KernelMatmulLinearOperator(
             x1, x2, self._get_params(), start, end,
             kernel_type=self._KERNEL_TYPE, symmetric=symmetric, compile_pool=self._compile_pool,
