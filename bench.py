@@ -389,12 +389,15 @@ def reference_cuda_timing(kind: str, kernel_type: str, k: int, call_args: tuple,
     oracle/build_ref.py) on the same inputs: every autotune candidate that was built for this op,
     kernel type and width (kernel_matmul/configurations.py:94-118), the fastest one reported.
     The reference launches on the legacy default stream, so each call is timed between device
-    synchronisations.  None when no module was built."""
+    synchronisations.  None when no module was built.  Every module is compiled for ONE leading
+    batch dim (KM_BATCH_DIM = 1): the arguments must have exactly one."""
     import glob
 
     base = os.path.join(ROOT, "oracle", "_ref")
     stem = f"km_ref_matmul_{kernel_type}_k{k}" if kind == "matmul" else f"km_ref_{kind}_{kernel_type}"
     best, tried, errors = None, 0, []
+    if call_args[0].dim() != 2:
+        return {"error": "reference modules take exactly one leading batch dim"}
     for d in sorted(glob.glob(os.path.join(base, stem + "*"))):
         name = os.path.basename(d)
         if name != stem and not name.startswith(stem + "_"):
@@ -542,8 +545,8 @@ def measure_single_op(name: str, dev, steps: int, fp32_peak: float, sfu_peak: fl
         fn = lambda: ops.matmul(kt, x, x, rhs, params, start, end)  # noqa: E731
         model = {"bound": "launch latency", "fp32_instr": fp32_instr_fwd(kt, k), "sfu": GEN_FWD[kt][1]}
         units, kernel = E * k, "matmul_fma_cluster_kernel"
-        if with_ref:
-            ref = reference_cuda_timing("matmul", kt, k, (x, x, rhs, params, start, end))
+        if with_ref:  # (the reference modules are built for one leading batch dim)
+            ref = reference_cuda_timing("matmul", kt, k, tuple(t.unsqueeze(0) for t in (x, x, rhs, params, start, end)))
     elif name == "locally_periodic_bilinear":
         w = workloads.locally_periodic_bilinear()
         B = w.params.shape[0]
@@ -568,7 +571,7 @@ def measure_single_op(name: str, dev, steps: int, fp32_peak: float, sfu_peak: fl
         model = {"bound": "tensor", "tensor_flops": 3 * 2.0 * E * k, "fp32_instr": TC_FWD[kt][0], "sfu": TC_FWD[kt][1]}
         units, kernel = E * k, "matmul_tc_kernel"
         if with_ref:
-            ref = reference_cuda_timing("matmul", kt, k, (x, x, rhs, params, start, end), reps=1)
+            ref = reference_cuda_timing("matmul", kt, k, tuple(t.unsqueeze(0) for t in (x, x, rhs, params, start, end)), reps=1)
     elif name == "rbf_unbanded_index":
         w = workloads.rbf_unbanded()
         x = w.x.to(dev)
@@ -709,9 +712,15 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
     if world > 1:
         dist.barrier()
     e2e_runs = []
+    e2e_solver = None
     for _ in range(2):
-        e2e_runs.append(cuda_ms(solve_e2e))
+        box = []
+        e2e_runs.append(cuda_ms(lambda: box.append(solve_e2e()[0])))
+        e2e_solver = box[0]
     e2e_ms = statistics.mean(e2e_runs)
+    e2e_solver.check_finite()
+    e2e_residual = float(e2e_solver.residual_norms()[-1].max())
+    del e2e_solver, box
     trace("end-to-end solves done")
     h2d = (hx.numel() + hp.numel() + (op.hi - op.lo) * k) * 4
     d2h = op.rows * k * 4
@@ -773,6 +782,7 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
             "roofline": roofline,
             "e2e": {"value": units * iters / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d / iters,
                     "d2h_bytes_per_step": d2h / iters, "solve_ms": e2e_ms, "iterations": iters,
+                    "relative_residual": e2e_residual,
                     "what": "host.cg_solve_from_host: pinned host x, params, Y rows in; band, operator set-up, "
                             f"{iters} iterations; solution rows out"},
             # per iteration: product (tensor-core kernel + FMA-pipe companion), q/dots, 2 x segment sums, 2 x update
@@ -784,6 +794,15 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
         sec = {}
         del flush, y
         torch.cuda.empty_cache()
+        # the reference's own product kernel on ONE component of this operator (B = 1 keeps its int32
+        # offsets below 2^31; the 64-component call overflows them and is not run): x 64 for the sum
+        one = reference_cuda_timing("matmul", kt, k, (x[None], x[None], w.rhs.to(dev)[None], params[1:2], start[:1].contiguous(),
+                                                      end[:1].contiguous()), reps=1)
+        if one is not None:
+            line["reference_cuda_kernels_same_gpu"] = {
+                "matmul_one_component": one,
+                "note": f"one of {B} components; the reference evaluates the sum as {B} such products plus a reduction",
+                "matvec_ms_extrapolated": one["ms"] * B if "ms" in one else None}
         sec["spectral_mixture"] = measure_mixture(workloads.spectral_mixture(), dev, min(args.steps, 10), args.path, fp32_peak,
                                                   sfu_peak, with_e2e=True, with_ref=True)
         trace("secondary: spectral mixture done")

@@ -35,7 +35,8 @@ def test_vector_kernels_match_the_stand_in(k, layout):
     else:
         row0, row1, lo, hi = 128 * 14, n, 128 * 11, n
     cnt = -(-(row1 - row0) // 128)
-    seg_blocks, slots, ranks = 3, 4, 3
+    slots, ranks = 4, 3
+    seg_blocks = -(-cnt // slots) if cnt > 3 * slots else 3  # at most `slots` segments per rank
     below, above = row0 - lo, hi - row1
     top_rows, bottom_rows = 128 * 3, 128 * 3
     C, T = CudaVectorOps(dev), TorchVectorOps()
