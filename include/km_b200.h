@@ -382,20 +382,22 @@ KM_API int km_cg_init_scalars_f32(int64_t k, const void *seg_sums, int64_t seg_r
 /* alpha = rs / (p . q) from the gathered sums; x += alpha p on the own rows; r -= alpha q on
  * [lo, hi), with q of a row below / above the own window read from
  * q_below[(row - below_origin) * k + c] / q_above[(row - above_origin) * k + c]; block partials of
- * the new r . r over the own rows. */
+ * the new r . r over the own rows.  alpha_row (may be NULL): alpha[k] of this iteration is stored
+ * there (with the betas, the Lanczos coefficients of the solve: log-determinant estimates). */
 KM_API int km_cg_update_xr_f32(int64_t k, float *x, float *r, const float *p, const float *q_own,
                                const float *q_below, int64_t below_origin, const float *q_above,
                                int64_t above_origin, int64_t row0, int64_t row1, int64_t lo, int64_t hi,
                                const void *pq_seg_sums, int64_t seg_rank_stride_bytes, int32_t seg_ranks,
-                               int32_t seg_slots, const float *rs, float *block_partials, void *stream);
+                               int32_t seg_slots, const float *rs, float *block_partials, float *alpha_row,
+                               void *stream);
 
 /* rs_new = total of the gathered sums of r . r; beta = rs_new / rs_old; p = r + beta p on [lo, hi);
  * rs_new[k] is stored (rs_old and rs_new must be different buffers) and, if history_row is not
- * NULL, history_row[c] = sqrt(rs_new[c]) / ynorm[c]. */
+ * NULL, history_row[c] = sqrt(rs_new[c]) / ynorm[c]; if beta_row is not NULL, beta_row[c] = beta. */
 KM_API int km_cg_update_p_f32(int64_t k, float *p, const float *r, int64_t lo, int64_t hi, const void *rr_seg_sums,
                               int64_t seg_rank_stride_bytes, int32_t seg_ranks, int32_t seg_slots,
                               const float *rs_old, float *rs_new, const float *ynorm, float *history_row,
-                              void *stream);
+                              float *beta_row, void *stream);
 
 /* ---------------------------------------------------------------------------------------
  * Self-tests of the give-up path of the tensor-core kernels.  No reference counterpart (the

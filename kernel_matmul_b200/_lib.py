@@ -110,9 +110,9 @@ def _load() -> ctypes.CDLL:
     lib.km_cg_init_scalars_f32.restype = ctypes.c_int
     lib.km_cg_init_scalars_f32.argtypes = [i64, vp, i64, i32, i32, vp, vp, vp]
     lib.km_cg_update_xr_f32.restype = ctypes.c_int
-    lib.km_cg_update_xr_f32.argtypes = [i64, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, vp, i64, i32, i32, vp, vp, vp]
+    lib.km_cg_update_xr_f32.argtypes = [i64, vp, vp, vp, vp, vp, i64, vp, i64, i64, i64, i64, i64, vp, i64, i32, i32, vp, vp, vp, vp]
     lib.km_cg_update_p_f32.restype = ctypes.c_int
-    lib.km_cg_update_p_f32.argtypes = [i64, vp, vp, i64, i64, vp, i64, i32, i32, vp, vp, vp, vp, vp]
+    lib.km_cg_update_p_f32.argtypes = [i64, vp, vp, i64, i64, vp, i64, i32, i32, vp, vp, vp, vp, vp, vp]
     lib.km_selftest_bounded_wait.restype = ctypes.c_int
     lib.km_selftest_bounded_wait.argtypes = [i64, vp, vp]
     lib.km_selftest_set_wait_polls.restype = ctypes.c_int

@@ -76,6 +76,9 @@ class CGResult:
     solution: Tensor  # (n, k)
     residual_norms: Tensor  # (iterations + 1, k): ||r_i|| / ||y||
     iterations: int
+    alphas: Tensor | None = None  # (iterations, k) step lengths
+    betas: Tensor | None = None  # (iterations, k) direction updates
+    y_norms: Tensor | None = None  # (k,) ||y||
 
 
 class ShardMismatchError(RuntimeError):
@@ -115,17 +118,18 @@ class CudaVectorOps:
         self.check(self.lib.km_cg_init_scalars_f32(k, _ptr(gathered), rank_stride, ranks, slots, _ptr(rs), _ptr(ynorm), self._stream()))
 
     def update_xr(self, x, r, p, q_own, q_below, q_above, row0, row1, lo, hi, gathered, rank_stride, ranks, slots, rs,
-                  block_partials) -> None:
+                  block_partials, alpha_row=None) -> None:
         (tb, ob, gb), (ta, oa, ga) = q_below, q_above
         self.check(self.lib.km_cg_update_xr_f32(
             p.shape[-1], _ptr(x), _ptr(r), _ptr(p), _ptr(q_own), _ptr(tb, ob) if tb is not None else None, gb,
             _ptr(ta, oa) if ta is not None else None, ga, row0, row1, lo, hi, _ptr(gathered), rank_stride, ranks, slots,
-            _ptr(rs), _ptr(block_partials), self._stream()))
+            _ptr(rs), _ptr(block_partials), _ptr(alpha_row) if alpha_row is not None else None, self._stream()))
 
-    def update_p(self, p, r, lo, hi, gathered, rank_stride, ranks, slots, rs_old, rs_new, ynorm, history_row) -> None:
+    def update_p(self, p, r, lo, hi, gathered, rank_stride, ranks, slots, rs_old, rs_new, ynorm, history_row,
+                 beta_row=None) -> None:
         self.check(self.lib.km_cg_update_p_f32(
             p.shape[-1], _ptr(p), _ptr(r), lo, hi, _ptr(gathered), rank_stride, ranks, slots, _ptr(rs_old), _ptr(rs_new),
-            _ptr(ynorm), _ptr(history_row), self._stream()))
+            _ptr(ynorm), _ptr(history_row), _ptr(beta_row) if beta_row is not None else None, self._stream()))
 
 
 class ShardedOperator:
@@ -311,6 +315,10 @@ class CGSolver:
         self.ynorm = torch.ones(k, device=dev, dtype=dt)
         self.max_iterations = max_iterations
         self.history = torch.ones(max_iterations + 1, k, device=dev, dtype=dt)
+        # alpha and beta of every iteration: the Lanczos coefficients of the solve (gp.py turns them
+        # into log-determinant estimates)
+        self.alphas = torch.zeros(max_iterations, k, device=dev, dtype=dt)
+        self.betas = torch.zeros(max_iterations, k, device=dev, dtype=dt)
         self.it = 0
         # exchange buffers: [segment sums (fp64)] [first halo_above rows of q] [last halo_below rows of q]
         self.seg_bytes = _round_up(op.segs_per_rank * k * 8, 256)
@@ -361,12 +369,12 @@ class CGSolver:
         if self.gq is not None:
             self._gather(self.gq, self.kp[op.rank * op.per_rows: (op.rank + 1) * op.per_rows])
         V.update_xr(self.x, self.r, self.p, self.kp, self.q_below, self.q_above, op.row0, op.row1, op.lo, op.hi,
-                    self.g1, self.packed, op.world, op.segs_per_rank, rs_old, self.bp)
+                    self.g1, self.packed, op.world, op.segs_per_rank, rs_old, self.bp, self.alphas[self.it])
         V.segment_sums(k, self.bp, op.count, op.seg_blocks, self.send2, 0)
         self._gather(self.g2, self.send2)
         self.it += 1
         V.update_p(self.p, self.r, op.lo, op.hi, self.g2, self.seg_bytes, op.world, op.segs_per_rank, rs_old, rs_new,
-                   self.ynorm, self.history[self.it])
+                   self.ynorm, self.history[self.it], self.betas[self.it - 1])
         return self.history[self.it]
 
     def residual_norms(self) -> Tensor:
@@ -410,4 +418,5 @@ def conjugate_gradient(op: ShardedOperator, y: Tensor, iterations: int, tol: flo
         done += 1
         if tol > 0 and bool((res <= tol).all()):
             break
-    return CGResult(solver.solution(), solver.residual_norms().clone(), done)
+    return CGResult(solver.solution(), solver.residual_norms().clone(), done, solver.alphas[:done].clone(),
+                    solver.betas[:done].clone(), solver.ynorm.clone())

@@ -166,6 +166,7 @@ struct CgUpdateArgs {
     const float *rs_in;             // [k] r . r of the current residual
     float *rs_out;                  // update_p: [k] r . r of the new residual
     float *history;                 // update_p: [k] sqrt(rs_new) / ynorm
+    float *coeff_out;               // [k] alpha (update_xr) / beta (update_p) of this iteration, or null
     const float *ynorm;             // [k]
     float *block_partials;          // update_xr: partials of r . r over own row blocks
     float tiny;
@@ -186,6 +187,7 @@ __global__ void __launch_bounds__(CG_THREADS) cg_update_xr_kernel(const CgUpdate
             const int c = c0 + threadIdx.x;
             const double pq = cg_total(g.seg_base, g.seg_rank_stride, g.seg_ranks, g.seg_slots, k, c);
             alpha_s[threadIdx.x] = g.rs_in[c] / fmaxf((float)pq, g.tiny);
+            if (blockIdx.x == 0 && g.coeff_out != nullptr) g.coeff_out[c] = alpha_s[threadIdx.x];
         }
         __syncthreads();
         float alpha[KC];
@@ -243,6 +245,7 @@ __global__ void __launch_bounds__(CG_THREADS) cg_update_p_kernel(const CgUpdateA
             const float rs_new = (float)cg_total(g.seg_base, g.seg_rank_stride, g.seg_ranks, g.seg_slots, k, c);
             beta_s[threadIdx.x] = rs_new / fmaxf(g.rs_in[c], g.tiny);
             if (blockIdx.x == 0) {
+                if (g.coeff_out != nullptr) g.coeff_out[c] = beta_s[threadIdx.x];
                 g.rs_out[c] = rs_new;
                 if (g.history != nullptr) g.history[c] = sqrtf(rs_new) / g.ynorm[c];
             }
@@ -372,7 +375,8 @@ extern "C" int km_cg_update_xr_f32(int64_t k, float *x, float *r, const float *p
                                    const float *q_below, int64_t below_origin, const float *q_above,
                                    int64_t above_origin, int64_t row0, int64_t row1, int64_t lo, int64_t hi,
                                    const void *pq_seg_sums, int64_t seg_rank_stride_bytes, int32_t seg_ranks,
-                                   int32_t seg_slots, const float *rs, float *block_partials, void *stream) {
+                                   int32_t seg_slots, const float *rs, float *block_partials, float *alpha_row,
+                                   void *stream) {
     using namespace km;
     KM_CG_ROWS_OK("km_cg_update_xr_f32");
     KM_REQUIRE(lo >= 0 && lo <= row0 && hi >= row1, KM_ERR_INVALID_ARGUMENT,
@@ -386,6 +390,7 @@ extern "C" int km_cg_update_xr_f32(int64_t k, float *x, float *r, const float *p
     g.q_own = q_own, g.q_below = q_below, g.q_above = q_above, g.below_origin = below_origin, g.above_origin = above_origin;
     g.seg_base = static_cast<const unsigned char *>(pq_seg_sums), g.seg_rank_stride = seg_rank_stride_bytes;
     g.seg_ranks = seg_ranks, g.seg_slots = seg_slots, g.rs_in = rs, g.block_partials = block_partials;
+    g.coeff_out = alpha_row;
     g.tiny = 1.17549435e-38f;
     g.vec = cg_vec_ok(k, {x, r, p, q_own, q_below, q_above}) ? 1 : 0;
     const int64_t blocks = ceil_div(hi, KM_BLOCK_SIZE) - lo / KM_BLOCK_SIZE;
@@ -400,7 +405,7 @@ extern "C" int km_cg_update_xr_f32(int64_t k, float *x, float *r, const float *p
 extern "C" int km_cg_update_p_f32(int64_t k, float *p, const float *r, int64_t lo, int64_t hi, const void *rr_seg_sums,
                                   int64_t seg_rank_stride_bytes, int32_t seg_ranks, int32_t seg_slots,
                                   const float *rs_old, float *rs_new, const float *ynorm, float *history_row,
-                                  void *stream) {
+                                  float *beta_row, void *stream) {
     using namespace km;
     KM_REQUIRE(k >= 1 && lo >= 0 && hi >= lo, KM_ERR_INVALID_ARGUMENT, "km_cg_update_p_f32: bad sizes");
     KM_REQUIRE(p && r && rr_seg_sums && rs_old && rs_new && rs_old != rs_new && (history_row == nullptr || ynorm) &&
@@ -410,7 +415,7 @@ extern "C" int km_cg_update_p_f32(int64_t k, float *p, const float *r, int64_t l
     g.k = k, g.lo = lo, g.hi = hi, g.p = p, g.r = const_cast<float *>(r);
     g.seg_base = static_cast<const unsigned char *>(rr_seg_sums), g.seg_rank_stride = seg_rank_stride_bytes;
     g.seg_ranks = seg_ranks, g.seg_slots = seg_slots, g.rs_in = rs_old, g.rs_out = rs_new, g.history = history_row;
-    g.ynorm = ynorm, g.tiny = 1.17549435e-38f;
+    g.ynorm = ynorm, g.tiny = 1.17549435e-38f, g.coeff_out = beta_row;
     g.vec = cg_vec_ok(k, {p, r}) ? 1 : 0;
     const int64_t blocks = std::max<int64_t>(1, ceil_div(hi, KM_BLOCK_SIZE) - lo / KM_BLOCK_SIZE);  // CTA 0 always runs
     cudaStream_t s = static_cast<cudaStream_t>(stream);

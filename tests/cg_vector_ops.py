@@ -69,12 +69,14 @@ class TorchVectorOps:
         ynorm.copy_(t.sqrt().clamp_min(torch.finfo(rs.dtype).tiny))
 
     def update_xr(self, x, r, p, q_own, q_below, q_above, row0, row1, lo, hi, gathered, rank_stride, ranks, slots, rs,
-                  block_partials) -> None:
+                  block_partials, alpha_row=None) -> None:
         if hi == lo:
             return
         k = p.shape[-1]
         tiny = torch.finfo(rs.dtype).tiny
         alpha = rs / _total(gathered, rank_stride, ranks, slots, k).to(rs.dtype).clamp_min(tiny)
+        if alpha_row is not None:
+            alpha_row.copy_(alpha)
         x[row0:row1] += alpha * p[row0:row1]
         r[row0:row1] -= alpha * q_own[row0:row1]
         if lo < row0:
@@ -87,11 +89,14 @@ class TorchVectorOps:
             r[row1:hi] -= alpha * src[row1 - origin: hi - origin]
         _block_partials(r[row0:row1] * r[row0:row1], block_partials)
 
-    def update_p(self, p, r, lo, hi, gathered, rank_stride, ranks, slots, rs_old, rs_new, ynorm, history_row) -> None:
+    def update_p(self, p, r, lo, hi, gathered, rank_stride, ranks, slots, rs_old, rs_new, ynorm, history_row,
+                 beta_row=None) -> None:
         k = p.shape[-1]
         tiny = torch.finfo(rs_old.dtype).tiny
         new = _total(gathered, rank_stride, ranks, slots, k).to(rs_old.dtype)
         beta = new / rs_old.clamp_min(tiny)
+        if beta_row is not None:
+            beta_row.copy_(beta)
         p[lo:hi] = r[lo:hi] + beta * p[lo:hi]
         rs_new.copy_(new)
         if history_row is not None:

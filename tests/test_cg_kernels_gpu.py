@@ -51,7 +51,8 @@ def test_vector_kernels_match_the_stand_in(k, layout):
         st = dict(x=mk(n, k), r=mk(n, k), p=mk(n, k), kp=mk(n, k), bp=torch.zeros(cnt, k, device=dev),
                   send=torch.zeros(packed, dtype=torch.uint8, device=dev), g1=torch.zeros(ranks * packed, dtype=torch.uint8, device=dev),
                   g2=torch.zeros(ranks * seg_bytes, dtype=torch.uint8, device=dev), rs=torch.rand(2, k, generator=g).to(dev) + 0.5,
-                  ynorm=torch.rand(k, generator=g).to(dev) + 0.5, hist=torch.zeros(k, device=dev))
+                  ynorm=torch.rand(k, generator=g).to(dev) + 0.5, hist=torch.zeros(k, device=dev),
+                  alpha=torch.zeros(k, device=dev), beta=torch.zeros(k, device=dev))
         # what the three ranks would have gathered: segment sums (positive) and halo rows of q
         for rk in range(ranks):
             seg = torch.rand(slots, k, generator=g, dtype=torch.float64) + 0.1
@@ -88,11 +89,12 @@ def test_vector_kernels_match_the_stand_in(k, layout):
         qb = (st["g1"],) + q_below[1:] if below else q_below
         qa = (st["g1"],) + q_above[1:] if above else q_above
         V.update_xr(st["x"], st["r"], st["p"], st["kp"], qb, qa, row0, row1, lo, hi, st["g1"], st["packed"], ranks, slots,
-                    st["rs"][0], st["bp"])
+                    st["rs"][0], st["bp"], st["alpha"])
         V.segment_sums(k, st["bp"], cnt, seg_blocks, st["send"], 0)
         V.update_p(st["p"], st["r"], lo, hi, st["g2"], st["seg_bytes"], ranks, slots, st["rs"][0], st["rs"][1], st["ynorm"],
-                   st["hist"])
+                   st["hist"], st["beta"])
     torch.cuda.synchronize()
+    assert _close(a["alpha"], b["alpha"], 1e-6) and _close(a["beta"], b["beta"], 1e-6)
     for name in ("x", "r", "p"):
         assert _close(a[name], b[name], 2e-6), name
         if layout != "single":  # nothing outside [lo, hi) (x: outside the own rows) is touched
@@ -119,7 +121,7 @@ def test_cg_entry_points_validate_their_arguments():
     assert lib.km_cg_block_dots_f32(4, p(x), p(x), 64, 256, p(x), None) == 1  # window must start at a row block
     assert b"row-block boundary" in lib.km_last_error()
     assert lib.km_cg_q_dots_f32(4, p(x), p(x), 0.1, 0, 128, p(x), None, 300, None, 0, None) == 1
-    assert lib.km_cg_update_p_f32(4, p(x), p(x), 0, 256, p(x), 64, 1, 1, p(x), p(x), p(x), None, None) == 1
+    assert lib.km_cg_update_p_f32(4, p(x), p(x), 0, 256, p(x), 64, 1, 1, p(x), p(x), p(x), None, None, None) == 1
     assert b"must differ" in lib.km_last_error()
 
 

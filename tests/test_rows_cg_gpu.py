@@ -1,4 +1,6 @@
 """Row-window / batch-sum product and the CG solve on the GPU against the fp64 oracle."""
+import math
+
 import pytest
 import torch
 
@@ -156,6 +158,16 @@ def test_marginal_likelihood_gradient_matches_dense_fp64(kt):
     assert torch.allclose(g, g_ref, rtol=1e-4, atol=1e-4 * float(g_ref.abs().max())), (g, g_ref)
     assert abs(float(out.grad_sigma2) - float(g_sigma_ref)) <= 1e-4 * abs(float(g_sigma_ref))
     assert abs(float(out.inv_quad) - float(y.double() @ u)) <= 1e-4 * abs(float(y.double() @ u))
+    # log det: the Lanczos estimate from the CG coefficients against the same estimator with the exact
+    # matrix logarithm, (1 / t) sum_i z_i^T log(Khat) z_i, and that against the true log-determinant
+    evals, evecs = torch.linalg.eigh(Khat.detach())
+    proj = evecs.T @ probes.double()
+    exact_estimator = float(((proj ** 2) * torch.log(evals)[:, None]).sum() / t)
+    assert abs(float(out.logdet) - exact_estimator) <= 2e-3 * abs(exact_estimator), (float(out.logdet), exact_estimator)
+    true_logdet = float(torch.log(evals).sum())
+    assert abs(exact_estimator - true_logdet) <= 0.1 * abs(true_logdet)  # 12 probes: a noisy but unbiased estimate
+    nll = 0.5 * float(y.double() @ V[:, 0]) + 0.5 * float(out.logdet) + 0.5 * n * math.log(2 * math.pi)
+    assert abs(float(out.nll) - nll) <= 1e-3 * abs(nll)
     # and with exact solves the same estimator agrees to the accuracy of the CG solves
     u, w = V[:, 0], V[:, 1:]
     est = -0.5 * (u @ K @ u) + (0.5 / t) * (w * (K @ probes.double())).sum()
