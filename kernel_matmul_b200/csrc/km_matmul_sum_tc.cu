@@ -20,10 +20,17 @@
 //   * a control warp issues tcgen05.mma kind::f16 (N = 64, K = 16; 3 per 16 values of 2B) into
 //     one of two tensor-memory stages: C[128 x 64] = sum_b s_b cos(w_b tau);
 //   * the row threads read C with tcgen05.ld, multiply by the envelope exp(-tau^2 / 2 l^2) (one
-//     SFU operation per entry) and contract with the rhs tile (k <= 16 columns, FMA pipe).
+//     SFU operation per entry) and contract with the rhs tile (k <= 16 columns, FMA pipe).  All of
+//     that arithmetic is packed (f32x2): a thread handles the band columns two at a time -- tau,
+//     the exponent and the product for (j, j + 1) are one instruction each -- and the rhs tile
+//     lies in shared memory as pairs (rhs[j][c], rhs[j + 1][c]), so that one fma.rn.f32x2 adds
+//     both columns' contributions to output column c (even and odd band columns keep separate
+//     partial sums, added at the end).
 // SFU work per entry: 1 + 2B / 128 (psi is shared by the 128 rows) instead of B + 1.
 //
 // No workspace: a CTA whose bounded wait gives up writes NaN into its output rows.
+#include <cstdlib>
+
 #include "km_tcgen05.cuh"
 
 namespace km {
@@ -33,9 +40,13 @@ constexpr int ST_IN_STAGES = 4;   // x2 / rhs tiles in shared memory
 constexpr int ST_TMEM_COLS = 256; // A (2 * 64) + two C stages of 64
 constexpr int ST_C_COL = 128;     // first C column
 
-// KB: rhs columns held per thread (8 or 16).
-template <int KB>
-__global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a) {
+// KB: rhs columns held per thread (8 or 16).  G: groups of 128 row threads.  With G = 2 the two
+// groups own the same rows (tensor-memory lanes) and alternate tiles: group g generates psi for,
+// and consumes, the tiles t = g, g + 2, ... through psi / C stage g, each with its own partial
+// sums, which are added at the end.  Twice the warps per SM hide the latencies (SFU results,
+// tensor-memory loads, MMA completion) that a single group per CTA leaves exposed.
+template <int KB, int G>
+__global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const SumTcArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_in[ST_IN_STAGES];  // x2 + rhs tile landed
     __shared__ __align__(8) uint64_t bar_bready[2];         // psi tile written
@@ -44,12 +55,15 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
     __shared__ __align__(8) uint64_t bar_drain;             // give-up path: every issued MMA has completed
     __shared__ uint32_t tmem_base_slot;
     __shared__ int fail_flag;
-    __shared__ float w_tab[SUM_TC_MAX_COMPONENTS], s_tab[SUM_TC_MAX_COMPONENTS];
+    __shared__ __align__(16) float w_tab[SUM_TC_MAX_COMPONENTS];
+    __shared__ __align__(16) float s_tab[SUM_TC_MAX_COMPONENTS];
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const bool is_ctl_warp = warp == 4;
+    const bool is_ctl_warp = warp == 4 * G;
+    const int g = tid >> 7;            // row group
+    const int row_local = tid & 127;  // row of the block = tensor-memory lane
     const int B = (int)a.comp_count;  // components of this launch: [comp_begin, comp_begin + B)
     const int Bp = (B + 7) & ~7;  // components padded to whole MMA steps (K = 2 Bp)
     const int ksteps = Bp / 8;
@@ -116,9 +130,9 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
     const uint32_t tmem_base = tmem_base_slot;
     bool failed = false;
 
-    f32x2 acc2[KB / 2];  // output columns in packed pairs
+    f32x2 acc2[KB];  // per output column: (sum over even band columns, sum over odd band columns)
 #pragma unroll
-    for (int c = 0; c < KB / 2; c++) acc2[c] = 0ull;
+    for (int c = 0; c < KB; c++) acc2[c] = 0ull;
 
     if (is_ctl_warp) {
         // ------------------------------------------------ input fetches (all lanes) + MMA issue (lane 0)
@@ -133,10 +147,12 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
                 const bool valid = j0 + jj < n;
                 cp_async4_zfill(xs + jj, x2 + (valid ? j0 + jj : 0) * a.x2.s0, valid);
             }
+            // rhs rows in pairs: rs[((jj / 2) * KB + c) * 2 + (jj & 1)] = rhs[j0 + jj][c]
             for (int q = lane; q < ST_COLS * KB; q += 32) {
                 const int jj = q / KB, c = q % KB;
                 const bool valid = j0 + jj < n && c < a.k;
-                cp_async4_zfill(rs + q, rhs + (valid ? (j0 + jj) * a.rhs.s0 + c * a.rhs.s1 : 0), valid);
+                cp_async4_zfill(rs + (((jj >> 1) * KB + c) << 1) + (jj & 1),
+                                rhs + (valid ? (j0 + jj) * a.rhs.s0 + c * a.rhs.s1 : 0), valid);
             }
             cp_async_mbar_arrive(&bar_in[st]);
         };
@@ -199,14 +215,14 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
         __syncwarp();
     } else {
         // ------------------------------------------------------------------------ row threads
-        const int64_t row = r * KM_BLOCK_SIZE + tid;
+        const int64_t row = r * KM_BLOCK_SIZE + row_local;
         const float x1v = row < a.m ? a.x1.data[row * a.x1.s0] : x0;
-        const uint32_t tmem_lane = tmem_base + ((uint32_t)(warp * 32) << 16);
+        const uint32_t tmem_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
 
         // phi of this row -> tensor memory: per 8 components [8 hi pairs | 8 lo pairs]
         {
             const float ai = x1v - x0;
-            for (int ks = 0; ks < ksteps; ks++) {
+            for (int ks = g; ks < ksteps; ks += G) {
                 float v[16], lo[16];
 #pragma unroll
                 for (int u = 0; u < 8; u++) {
@@ -220,31 +236,34 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
             }
             tmem_st_wait();
             tc_fence_before();
+            // both groups' parts of phi are in place before either announces a psi tile
+            if (G > 1) asm volatile("bar.sync 1, %0;" ::"n"(128 * G) : "memory");
         }
 
-        // psi of the tile's columns -> shared memory (thread: column tid % 64, half of the components)
+        // psi of the tile's columns -> shared memory (thread: column row_local % 64, half of the components)
         auto generate = [&](int t) {
             const int st = t & 1;
-            const int jj = tid & 63;
+            const int jj = row_local & 63;
             const float aj = in_x2(t % ST_IN_STAGES)[jj] - x0;
             unsigned char *hi = b_stage(st) + jj * 16;
             unsigned char *lo = hi + b_part_bytes;
             // 4 components = 8 K values = one 16-byte chunk
-            for (int kc = (tid >> 6) * (Bp / 8); kc < ((tid >> 6) + 1) * (Bp / 8); kc++) {
-                float v[8];
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const float ph = w_tab[kc * 4 + u] * aj;
-                    v[2 * u] = cos_approx(ph);
-                    v[2 * u + 1] = sin_approx(ph);
-                }
+            for (int kc = (row_local >> 6) * (Bp / 8); kc < ((row_local >> 6) + 1) * (Bp / 8); kc++) {
+                // (cos, sin) of one component as a packed pair; hi = the pair truncated to fp16
+                // precision (cvt.rz), lo = pair - hi rounded (one packed subtraction)
+                const float4 wq = *reinterpret_cast<const float4 *>(w_tab + kc * 4);
+                const float wv[4] = {wq.x, wq.y, wq.z, wq.w};
                 uint32_t h[4], l[4];
 #pragma unroll
                 for (int u = 0; u < 4; u++) {
-                    asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(h[u]) : "f"(v[2 * u + 1]), "f"(v[2 * u]));
-                    asm("cvt.rn.f16x2.f32 %0, %1, %2;"
-                        : "=r"(l[u])
-                        : "f"(v[2 * u + 1] - tf32_hi(v[2 * u + 1])), "f"(v[2 * u] - tf32_hi(v[2 * u])));
+                    const float ph = wv[u] * aj;
+                    const f32x2 v2 = pack2(cos_approx(ph), sin_approx(ph));
+                    const f32x2 lo2 = sub2(v2, v2 & 0xffffe000ffffe000ull);
+                    float vc, vs, lc, ls;
+                    unpack2(v2, vc, vs);
+                    unpack2(lo2, lc, ls);
+                    asm("cvt.rz.f16x2.f32 %0, %1, %2;" : "=r"(h[u]) : "f"(vs), "f"(vc));
+                    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(l[u]) : "f"(ls), "f"(lc));
                 }
                 *reinterpret_cast<uint4 *>(hi + kc * (ST_COLS * 16)) = make_uint4(h[0], h[1], h[2], h[3]);
                 *reinterpret_cast<uint4 *>(lo + kc * (ST_COLS * 16)) = make_uint4(l[0], l[1], l[2], l[3]);
@@ -254,13 +273,20 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
             if (lane == 0) mbar_arrive(&bar_bready[st]);
         };
 
-        if (tiles > 0) {
+        if (G == 1 && tiles > 0) {
             if (!mbar_wait_warp(&bar_in[0], 0u, a.wait_polls)) failed = true;
             if (!failed) generate(0);
         }
-        for (int t = 0; t < tiles && !failed; t++) {
+        for (int t = (G == 1 ? 0 : g); t < tiles && !failed; t += G) {
             const int st = t & 1;
-            if (t + 1 < tiles) {
+            if (G > 1) {
+                // this group's tile: psi first, then the product of the tensor core
+                if (!mbar_wait_warp(&bar_in[t % ST_IN_STAGES], (unsigned)((t / ST_IN_STAGES) & 1), a.wait_polls)) {
+                    failed = true;
+                    break;
+                }
+                generate(t);
+            } else if (t + 1 < tiles) {
                 // (the psi stage of tile t + 1 was read by the MMAs of tile t - 1, whose completion
                 // this thread has seen when it consumed tile t - 1)
                 if (!mbar_wait_warp(&bar_in[(t + 1) % ST_IN_STAGES], (unsigned)(((t + 1) / ST_IN_STAGES) & 1), a.wait_polls)) {
@@ -277,35 +303,44 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
             const int j0 = (tile_lo + t) * ST_COLS;
             const float *xs = in_x2(t % ST_IN_STAGES);
             const float *rs = in_rhs(t % ST_IN_STAGES);
+            const f32x2 x1v2 = splat2(x1v), c02 = splat2(c0);
             auto consume = [&](auto masked_tag) {
                 constexpr bool MASKED = decltype(masked_tag)::value;
+                // the tensor-memory load of the next 16 columns is in flight while these are processed
+                uint32_t cbuf[2][16];
+                tmem_ld16_nowait(tmem_lane + (uint32_t)(ST_C_COL + st * ST_COLS), cbuf[0]);
+                tmem_ld_wait16(cbuf[0]);
 #pragma unroll
                 for (int p = 0; p < ST_COLS / 16; p++) {
-                    uint32_t cv[16];
-                    tmem_ld16_nowait(tmem_lane + (uint32_t)(ST_C_COL + st * ST_COLS + p * 16), cv);
-                    tmem_ld_wait16(cv);
+                    if (p + 1 < ST_COLS / 16)
+                        tmem_ld16_nowait(tmem_lane + (uint32_t)(ST_C_COL + st * ST_COLS + (p + 1) * 16), cbuf[(p + 1) & 1]);
+                    const uint32_t(&cv)[16] = cbuf[p & 1];
 #pragma unroll
                     for (int h = 0; h < 4; h++) {
-                        const float4 xq = *reinterpret_cast<const float4 *>(xs + p * 16 + h * 4);
-                        const float xj[4] = {xq.x, xq.y, xq.z, xq.w};
+                        // four band columns = two packed pairs
+                        const ulonglong2 xq = *reinterpret_cast<const ulonglong2 *>(xs + p * 16 + h * 4);
 #pragma unroll
-                        for (int u = 0; u < 4; u++) {
-                            const int jj = p * 16 + h * 4 + u;
-                            const float tau = x1v - xj[u];
-                            float v = __uint_as_float(cv[h * 4 + u]) * ex2_approx(c0 * tau * tau);
+                        for (int q = 0; q < 2; q++) {
+                            const int jj = p * 16 + h * 4 + 2 * q;  // even
+                            const f32x2 tau2 = sub2(x1v2, q ? xq.y : xq.x);
+                            const f32x2 e2 = ex2_approx2(mul2(mul2(tau2, tau2), c02));
+                            uint32_t ca = cv[h * 4 + 2 * q], cb = cv[h * 4 + 2 * q + 1];
                             if (MASKED) {
-                                if (j0 + jj < band_lo || j0 + jj >= band_hi) v = 0.0f;
+                                if (j0 + jj < band_lo || j0 + jj >= band_hi) ca = 0u;
+                                if (j0 + jj + 1 < band_lo || j0 + jj + 1 >= band_hi) cb = 0u;
                             }
-                            // rhs row of column jj (a broadcast read), two columns per packed FMA
-                            const f32x2 v2 = splat2(v);
+                            const f32x2 v2 = mul2((f32x2)ca | ((f32x2)cb << 32), e2);
+                            // rhs pairs of the two band columns (a broadcast read): one packed FMA per output column
+                            const float *rp = rs + (jj >> 1) * (2 * KB);
 #pragma unroll
-                            for (int c4 = 0; c4 < KB / 4; c4++) {
-                                const ulonglong2 rv = *reinterpret_cast<const ulonglong2 *>(rs + jj * KB + c4 * 4);
-                                acc2[c4 * 2 + 0] = fma2(v2, rv.x, acc2[c4 * 2 + 0]);
-                                acc2[c4 * 2 + 1] = fma2(v2, rv.y, acc2[c4 * 2 + 1]);
+                            for (int c2 = 0; c2 < KB / 2; c2++) {
+                                const ulonglong2 rv = *reinterpret_cast<const ulonglong2 *>(rp + c2 * 4);
+                                acc2[c2 * 2 + 0] = fma2(v2, rv.x, acc2[c2 * 2 + 0]);
+                                acc2[c2 * 2 + 1] = fma2(v2, rv.y, acc2[c2 * 2 + 1]);
                             }
                         }
                     }
+                    if (p + 1 < ST_COLS / 16) tmem_ld_wait16(cbuf[(p + 1) & 1]);
                 }
             };
             if (j0 < band_lo || j0 + ST_COLS > band_hi)
@@ -321,13 +356,30 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
 
     tc_fence_before();
     __syncthreads();
-    if (!is_ctl_warp) {
-        const int64_t row = r * KM_BLOCK_SIZE + tid;
+    float acc[KB];
+#pragma unroll
+    for (int c = 0; c < KB; c++) {
+        float even, odd;
+        unpack2(acc2[c], even, odd);
+        acc[c] = even + odd;
+    }
+    if (G > 1) {
+        // the second group hands its partial sums over through shared memory (the pipelines are done)
+        float *xch = reinterpret_cast<float *>(smem_raw);
+        if (!is_ctl_warp && g == 1) {
+#pragma unroll
+            for (int c = 0; c < KB; c++) xch[c * 128 + row_local] = acc[c];
+        }
+        __syncthreads();
+        if (!is_ctl_warp && g == 0) {
+#pragma unroll
+            for (int c = 0; c < KB; c++) acc[c] += xch[c * 128 + row_local];
+        }
+    }
+    if (!is_ctl_warp && g == 0) {
+        const int64_t row = r * KM_BLOCK_SIZE + row_local;
         if (row < a.m) {
             const bool bad = fail_flag != 0;
-            float acc[KB];
-#pragma unroll
-            for (int c = 0; c < KB / 2; c++) unpack2(acc2[c], acc[2 * c], acc[2 * c + 1]);
             float *orow = a.out.data + (row - a.rb_begin * KM_BLOCK_SIZE) * a.out.s0;
 #pragma unroll
             for (int c = 0; c < KB; c++)
@@ -352,19 +404,29 @@ __global__ void __launch_bounds__(160, 2) matmul_sum_tc_kernel(const SumTcArgs a
     }
 }
 
-template <int KB>
+template <int KB, int G>
 static int launch_sum_tc_kb(const SumTcArgs &a, cudaStream_t stream) {
     const int Bp = ((int)a.comp_count + 7) & ~7;
     const size_t b_stage = (size_t)2 * (2 * Bp / 8) * ST_COLS * 16;
     size_t smem = 2 * b_stage + (size_t)ST_IN_STAGES * (ST_COLS + ST_COLS * KB) * sizeof(float);
     // two CTAs of 256 tensor-memory columns fill an SM: keep a third from being scheduled
     smem = std::max<size_t>(smem, 80 * 1024);
-    auto kernel = matmul_sum_tc_kernel<KB>;
+    auto kernel = matmul_sum_tc_kernel<KB, G>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(matmul_sum_tc)");
-    kernel<<<(unsigned)a.row_blocks, 160, smem, stream>>>(a);
+    kernel<<<(unsigned)a.row_blocks, 128 * G + 32, smem, stream>>>(a);
     KM_CHECK_LAUNCH("km_matmul_rows_f32 (tensor-core batch sum) launch");
     return KM_OK;
+}
+
+// Row groups per CTA: 2, or what the environment variable KM_SUM_TC_GROUPS says (1 or 2; read once;
+// a tuning and comparison hook).
+static int sum_tc_groups() {
+    static const int groups = [] {
+        const char *e = getenv("KM_SUM_TC_GROUPS");
+        return (e != nullptr && e[0] == '1') ? 1 : 2;
+    }();
+    return groups;
 }
 
 int launch_matmul_sum_tc(const SumTcArgs &a, cudaStream_t stream) {
@@ -379,7 +441,11 @@ int launch_matmul_sum_tc(const SumTcArgs &a, cudaStream_t stream) {
     for (int64_t b0 = 0; b0 < a.batch.count; b0 += SUM_TC_MAX_COMPONENTS) {
         chunk.comp_begin = b0;
         chunk.comp_count = std::min<int64_t>(SUM_TC_MAX_COMPONENTS, a.batch.count - b0);
-        const int rc = a.k <= 8 ? launch_sum_tc_kb<8>(chunk, stream) : launch_sum_tc_kb<16>(chunk, stream);
+        int rc;
+        if (sum_tc_groups() == 1)
+            rc = a.k <= 8 ? launch_sum_tc_kb<8, 1>(chunk, stream) : launch_sum_tc_kb<16, 1>(chunk, stream);
+        else
+            rc = a.k <= 8 ? launch_sum_tc_kb<8, 2>(chunk, stream) : launch_sum_tc_kb<16, 2>(chunk, stream);
         if (rc != KM_OK) return rc;
     }
     return KM_OK;

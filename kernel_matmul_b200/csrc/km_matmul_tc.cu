@@ -442,44 +442,44 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             // the 16 band columns: [8 hi pairs | 8 lo pairs].
 #pragma unroll
             for (int half = g; half < TC_BK / 16; half += G) {  // this group's 16-column steps
-                float kv[16], lo[16];
-                // packed f32x2 arithmetic: two entries per FP32 instruction
-                {
-                    const ulonglong2 *xs2 = reinterpret_cast<const ulonglong2 *>(xs);
-                    const f32x2 x1v2 = splat2(x1v);
-                    f32x2 kv2[8];
-                    if (use_ph) {
-                        // cos(W tau) = c_i c_j + s_i s_j from the slot's per-column factors
-                        const ulonglong2 *cj2 = xs2 + TC_SCOLS / 4, *sj2 = xs2 + 2 * (TC_SCOLS / 4);
+                // packed f32x2 arithmetic: two entries per FP32 instruction, kept as pairs up to the
+                // fp16 conversions (8 hi words, 8 lo words: the 16 tensor-memory columns of this step)
+                const ulonglong2 *xs2 = reinterpret_cast<const ulonglong2 *>(xs);
+                const f32x2 x1v2 = splat2(x1v);
+                f32x2 kv2[8];
+                if (use_ph) {
+                    // cos(W tau) = c_i c_j + s_i s_j from the slot's per-column factors
+                    const ulonglong2 *cj2 = xs2 + TC_SCOLS / 4, *sj2 = xs2 + 2 * (TC_SCOLS / 4);
 #pragma unroll
-                        for (int h = 0; h < 4; h++) {
-                            const ulonglong2 xv = xs2[half * 4 + h], cj = cj2[half * 4 + h], sj = sj2[half * 4 + h];
-                            kv2[2 * h] = fn.unscaled2_ph(sub2(x1v2, xv.x), fma2(ci2, cj.x, mul2(si2, sj.x)), 0ull);
-                            kv2[2 * h + 1] = fn.unscaled2_ph(sub2(x1v2, xv.y), fma2(ci2, cj.y, mul2(si2, sj.y)), 0ull);
-                        }
-                    } else {
-#pragma unroll
-                        for (int h = 0; h < 4; h++) {
-                            const ulonglong2 xv = xs2[half * 4 + h];
-                            kv2[2 * h] = fn.unscaled2(sub2(x1v2, xv.x));
-                            kv2[2 * h + 1] = fn.unscaled2(sub2(x1v2, xv.y));
-                        }
+                    for (int h = 0; h < 4; h++) {
+                        const ulonglong2 xv = xs2[half * 4 + h], cj = cj2[half * 4 + h], sj = sj2[half * 4 + h];
+                        kv2[2 * h] = fn.unscaled2_ph(sub2(x1v2, xv.x), fma2(ci2, cj.x, mul2(si2, sj.x)), 0ull);
+                        kv2[2 * h + 1] = fn.unscaled2_ph(sub2(x1v2, xv.y), fma2(ci2, cj.y, mul2(si2, sj.y)), 0ull);
                     }
+                } else {
 #pragma unroll
-                    for (int u = 0; u < 8; u++) {
-                        unpack2(kv2[u], kv[2 * u], kv[2 * u + 1]);
-                        const f32x2 l2 = sub2(kv2[u], kv2[u] & 0xffffe000ffffe000ull);
-                        unpack2(l2, lo[2 * u], lo[2 * u + 1]);
+                    for (int h = 0; h < 4; h++) {
+                        const ulonglong2 xv = xs2[half * 4 + h];
+                        kv2[2 * h] = fn.unscaled2(sub2(x1v2, xv.x));
+                        kv2[2 * h + 1] = fn.unscaled2(sub2(x1v2, xv.y));
                     }
                 }
                 if (partial) {
 #pragma unroll
-                    for (int u = 0; u < 16; u++) {
-                        const int j = j0 + half * 16 + u;
-                        if (j < band_lo || j >= band_hi) kv[u] = lo[u] = 0.0f;
+                    for (int u = 0; u < 8; u++) {
+                        const int j = j0 + half * 16 + 2 * u;
+                        const f32x2 keep = ((j >= band_lo && j < band_hi) ? 0x00000000ffffffffull : 0ull) |
+                                           ((j + 1 >= band_lo && j + 1 < band_hi) ? 0xffffffff00000000ull : 0ull);
+                        kv2[u] &= keep;
                     }
                 }
-                split_store16(tmem_lane + (uint32_t)(s * TC_A_COLS + half * 16), kv, lo);
+                uint32_t words[16];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    words[u] = cvt_rz_f16x2_pair(kv2[u]);  // hi: truncated to fp16 precision
+                    words[8 + u] = cvt_rn_f16x2_pair(sub2(kv2[u], kv2[u] & 0xffffe000ffffe000ull));  // lo = kv - hi
+                }
+                tmem_st16(tmem_lane + (uint32_t)(s * TC_A_COLS + half * 16), words);
             }
             tmem_st_wait();
             tc_fence_before();

@@ -175,6 +175,19 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16
           "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
         : "memory");
 }
+// A packed pair of fp32 values -> one 32-bit word of two fp16 values (first element in the low
+// half), truncating (rz: the fp16 "hi" part of a value) or rounding to nearest (rn).  The pair is
+// taken apart inside the asm block, so the compiler sees no separate fp32 values to move around.
+__device__ __forceinline__ uint32_t cvt_rz_f16x2_pair(unsigned long long v) {
+    uint32_t r;
+    asm("{\n\t.reg .f32 a, b;\n\tmov.b64 {a, b}, %1;\n\tcvt.rz.f16x2.f32 %0, b, a;\n\t}" : "=r"(r) : "l"(v));
+    return r;
+}
+__device__ __forceinline__ uint32_t cvt_rn_f16x2_pair(unsigned long long v) {
+    uint32_t r;
+    asm("{\n\t.reg .f32 a, b;\n\tmov.b64 {a, b}, %1;\n\tcvt.rn.f16x2.f32 %0, b, a;\n\t}" : "=r"(r) : "l"(v));
+    return r;
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // 4-byte asynchronous copy that writes zero when `valid` is false (the source is not read)

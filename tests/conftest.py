@@ -22,6 +22,19 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200)")
 
 
+def pytest_terminal_summary(terminalreporter):
+    """Which clause of the gradient criterion the gradient checks passed by: per test function the
+    number of compared elements, how many met the plain 1e-5 relative bound, the largest relative
+    error seen and the largest error in units of the cancellation-free scale."""
+    if not GRAD_STATS:
+        return
+    tr = terminalreporter
+    tr.write_sep("-", "gradient criterion: |err| <= 1e-5 |ref|  or  |err| <= 1e-6 sum|terms|")
+    tr.write_line(f"{'test':58s} {'elements':>9s} {'strict':>9s} {'max rel err':>12s} {'max err/scale':>14s}")
+    for name, (count, strict, max_rel, max_scaled) in sorted(GRAD_STATS.items()):
+        tr.write_line(f"{name:58s} {count:9d} {strict:9d} {max_rel:12.3e} {max_scaled:14.3e}")
+
+
 @pytest.fixture(autouse=True)
 def seed(request) -> int:
     rng = random.Random(request.node.nodeid)
@@ -115,6 +128,9 @@ def rel_err(actual: torch.Tensor, expected: torch.Tensor, dim=None) -> float:
 
 GRAD_RTOL = 1e-5
 GRAD_COND_TOL = 1e-6
+# per test function: [elements, elements within the strict relative bound, max strict relative
+# error, max error / term scale] -- printed at the end of the run (pytest_terminal_summary)
+GRAD_STATS: dict[str, list] = {}
 
 
 def assert_grad_close(actual: torch.Tensor, expected: torch.Tensor, term_scale: torch.Tensor) -> None:
@@ -131,7 +147,15 @@ def assert_grad_close(actual: torch.Tensor, expected: torch.Tensor, term_scale: 
     e = expected.detach().double().cpu()
     s = term_scale.detach().double().cpu()
     err = (a - e).abs()
-    ok = (err <= GRAD_RTOL * e.abs()) | (err <= GRAD_COND_TOL * s)
+    strict = err <= GRAD_RTOL * e.abs()
+    ok = strict | (err <= GRAD_COND_TOL * s)
+    name = os.environ.get("PYTEST_CURRENT_TEST", "?").split("::")[-1].split("[")[0].split(" ")[0]
+    st = GRAD_STATS.setdefault(name, [0, 0, 0.0, 0.0])
+    st[0] += err.numel()
+    st[1] += int(strict.sum())
+    if err.numel():
+        st[2] = max(st[2], float((err / e.abs().clamp_min(1e-300)).max()))
+        st[3] = max(st[3], float((err / s.clamp_min(1e-300)).max()))
     assert bool(ok.all()), f"max rel err {float((err / e.abs().clamp_min(1e-300)).max()):.3e}, max err/scale {float((err / s.clamp_min(1e-300)).max()):.3e}"
 
 

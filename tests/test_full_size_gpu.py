@@ -23,7 +23,7 @@ def _sample_blocks(R, count, seed=0):
 
 
 def test_rbf_small_config_exact_against_full_oracle():
-    """BASELINE config 1 in full (n = 4096): every output row against the oracle."""
+    """The small RBF configuration in full (n = 4096): every output row against the oracle."""
     from kernel_matmul_b200 import ops, workloads
     from oracle import oracle as O
 
@@ -38,8 +38,30 @@ def test_rbf_small_config_exact_against_full_oracle():
     assert rel_err(out, ref) <= 1e-5
 
 
+def test_spectral_mixture_config_every_row_of_the_product():
+    """The 16-component spectral mixture (n = 65536, k = 16) in full: every one of the 1 048 576
+    output rows x 16 columns against the fp64 oracle (1.76e9 entries, a few tens of seconds of
+    CPU), on both kernel families."""
+    from kernel_matmul_b200 import ops, workloads
+    from oracle import oracle as O
+
+    w = workloads.spectral_mixture()
+    B, n, k = w.params.shape[0], w.n, w.rhs.shape[-1]
+    x = w.x.cuda()
+    start, end = workloads.band(w, x)
+    ref = O.matmul("spectral", w.x.expand(B, n), w.x.expand(B, n), w.rhs.expand(B, n, k), w.params, start.cpu(), end.cpu())
+    xb = x.expand(B, n)
+    for path in ("tc", "fma"):
+        out = ops.matmul("spectral", xb, xb, w.rhs.cuda().expand(B, n, k), w.params.cuda(), start, end, path=path)
+        ops.check()
+        err = (out.cpu().double() - ref).abs()
+        assert float(err.max() / ref.abs().max()) <= 1e-5, path
+        # per component as well (their scales differ by the lengthscale)
+        assert bool((err.amax(dim=(1, 2)) <= 1e-5 * ref.abs().amax(dim=(1, 2))).all()), path
+
+
 def test_spectral_mixture_config_sampled_blocks_and_properties():
-    """BASELINE config 2 (16 components, n = 65536, k = 16): forward on sampled row blocks,
+    """The spectral-mixture configuration (16 components, n = 65536, k = 16): forward on sampled row blocks,
     gradient restricted to sampled row blocks, symmetry and linearity on the full product."""
     from kernel_matmul_b200 import ops, workloads
     from oracle import oracle as O
@@ -81,7 +103,7 @@ def test_spectral_mixture_config_sampled_blocks_and_properties():
 
 
 def test_locally_periodic_bilinear_config_sampled_blocks():
-    """BASELINE config 3 (batch 4, n = 262144, k = 32): bilinear_derivative restricted to sampled
+    """The locally periodic configuration (batch 4, n = 262144, k = 32): bilinear_derivative restricted to sampled
     row blocks against the oracle, and the full-size call for shape / finiteness."""
     from kernel_matmul_b200 import ops, workloads
     from oracle import oracle as O
@@ -106,7 +128,7 @@ def test_locally_periodic_bilinear_config_sampled_blocks():
 
 
 def test_unbanded_rbf_config_sampled_blocks_and_gather():
-    """BASELINE config 4 (n = 131072 unbanded, k = 128; 2^24 gathers)."""
+    """The unbanded RBF configuration (n = 131072 unbanded, k = 128; 2^24 gathers)."""
     from kernel_matmul_b200 import ops, ranges, workloads
     from oracle import oracle as O
 
@@ -127,7 +149,7 @@ def test_unbanded_rbf_config_sampled_blocks_and_gather():
 
 
 def test_cg_sum_config_sampled_blocks_and_64bit_offsets():
-    """BASELINE config 5 (64 components, n = 2^22, k = 8): the batch-summed product and the
+    """The CG configuration (64 components, n = 2^22, k = 8): the batch-summed product and the
     batched product (whose output has 2.1e9 elements, past int32 offsets) on sampled row blocks."""
     from kernel_matmul_b200 import ops, workloads
     from oracle import oracle as O
