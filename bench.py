@@ -707,20 +707,22 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
     def solve_e2e():
         return host.cg_solve_from_host(kt, hx, hp, hy, w.cutoffs[0], w.extra["sigma2"], iters, hsol, dev, mode=args.exchange)
 
-    solve_e2e()  # warm-up (allocator, NCCL buffers)
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    e2e_runs = []
-    e2e_solver = None
-    for _ in range(2):
-        box = []
-        e2e_runs.append(cuda_ms(lambda: box.append(solve_e2e()[0])))
-        e2e_solver = box[0]
-    e2e_ms = statistics.mean(e2e_runs)
-    e2e_solver.check_finite()
-    e2e_residual = float(e2e_solver.residual_norms()[-1].max())
-    del e2e_solver, box
+    e2e_ms, e2e_residual = float("nan"), None
+    if not args.no_e2e:
+        solve_e2e()  # warm-up (allocator, NCCL buffers)
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e2e_runs = []
+        e2e_solver = None
+        for _ in range(2):
+            box = []
+            e2e_runs.append(cuda_ms(lambda: box.append(solve_e2e()[0])))
+            e2e_solver = box[0]
+        e2e_ms = statistics.mean(e2e_runs)
+        e2e_solver.check_finite()
+        e2e_residual = float(e2e_solver.residual_norms()[-1].max())
+        del e2e_solver, box
     trace("end-to-end solves done")
     h2d = (hx.numel() + hp.numel() + (op.hi - op.lo) * k) * 4
     d2h = op.rows * k * 4
@@ -780,7 +782,7 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
                                         "of segment sums"}[op.mode],
             "l2": "flushed between iterations (256 MB write, outside the event pairs)",
             "roofline": roofline,
-            "e2e": {"value": units * iters / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d / iters,
+            "e2e": None if args.no_e2e else {"value": units * iters / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d / iters,
                     "d2h_bytes_per_step": d2h / iters, "solve_ms": e2e_ms, "iterations": iters,
                     "relative_residual": e2e_residual,
                     "what": "host.cg_solve_from_host: pinned host x, params, Y rows in; band, operator set-up, "
@@ -898,6 +900,8 @@ def main() -> None:
                     help="CG workloads: what the ranks exchange per iteration (auto: halo rows for a banded operator)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-secondary", action="store_true", help="skip the other configurations (N = 1)")
+    ap.add_argument("--no-e2e", action="store_true",
+                    help="CG workloads: skip the end-to-end solves (profiling runs; the e2e key is then not a measurement)")
     ap.add_argument("--path", default="auto", choices=["auto", "fma", "tc"],
                     help="spectral-mixture workload: kernels of the ops (auto: what the ops choose; fma: FMA-pipe "
                          "kernels; tc: tensor-core kernels)")
