@@ -628,7 +628,7 @@ static int matmul_entry(const char *name, int kernel_type, const km_batch *batch
             t.out = a.out;
             t.comp_begin = 0;
             t.comp_count = 0;
-            const int rc = launch_matmul_sum_tc(t, s);
+            const int rc = sum_tc_variant() == 1 ? launch_matmul_sum_tc(t, s) : launch_matmul_sum_tc2(t, s);
             if (rc != KM_OK) return rc;
             a.sum_tc_launched = 1;
         }

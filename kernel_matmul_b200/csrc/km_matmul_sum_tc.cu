@@ -419,14 +419,16 @@ static int launch_sum_tc_kb(const SumTcArgs &a, cudaStream_t stream) {
     return KM_OK;
 }
 
-// Row groups per CTA: 2, or what the environment variable KM_SUM_TC_GROUPS says (1 or 2; read once;
-// a tuning and comparison hook).
+// Row groups per CTA: 2, or what the environment variable KM_SUM_TC_GROUPS says (1 or 2; read at
+// every launch; a tuning and comparison hook).
 static int sum_tc_groups() {
-    static const int groups = [] {
-        const char *e = getenv("KM_SUM_TC_GROUPS");
-        return (e != nullptr && e[0] == '1') ? 1 : 2;
-    }();
-    return groups;
+    const char *e = getenv("KM_SUM_TC_GROUPS");
+    return (e != nullptr && e[0] == '1') ? 1 : 2;
+}
+
+int sum_tc_variant() {
+    const char *e = getenv("KM_SUM_TC_VARIANT");  // read at every launch: tests switch it at run time
+    return (e != nullptr && e[0] == '2') ? 2 : 1;
 }
 
 int launch_matmul_sum_tc(const SumTcArgs &a, cudaStream_t stream) {

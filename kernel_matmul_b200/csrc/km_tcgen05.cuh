@@ -265,5 +265,12 @@ constexpr int SUM_TC_MAX_COMPONENTS = 64;    // per launch; more are processed i
 constexpr int SUM_TC_MAX_TOTAL = 1024;       // (the FMA-pipe kernel's shared-envelope table holds this many)
 constexpr int SUM_TC_MAX_K = 16;
 int launch_matmul_sum_tc(const SumTcArgs &a, cudaStream_t stream);
+// The same sum with the second contraction (kernel tile x rhs tile) on the tensor cores as well
+// (km_matmul_sum_tc2.cu): correct, but measured slower than the first form (17.5 against 11.7 ms on
+// the 64-component benchmark), so it only runs when asked for.
+int launch_matmul_sum_tc2(const SumTcArgs &a, cudaStream_t stream);
+// Which of the two runs: 1 (default) or 2, from the environment variable KM_SUM_TC_VARIANT (read at
+// every launch; a comparison hook).
+int sum_tc_variant();
 
 }  // namespace km

@@ -175,8 +175,18 @@ def test_marginal_likelihood_gradient_matches_dense_fp64(kt):
     assert torch.allclose(g, g_exact, rtol=5e-2, atol=5e-2 * float(g_exact.abs().max())), (g, g_exact)
 
 
+@pytest.fixture(params=["both contractions on the tensor cores", "second contraction on the FMA pipe",
+                        "second contraction on the FMA pipe, one row group"])
+def sum_kernel_variant(request, monkeypatch):
+    """The three forms of the tensor-core batch sum (the library reads the switches at every launch)."""
+    monkeypatch.setenv("KM_SUM_TC_VARIANT", "1" if request.param.startswith("second") else "2")
+    if request.param.endswith("one row group"):
+        monkeypatch.setenv("KM_SUM_TC_GROUPS", "1")
+    return request.param
+
+
 @pytest.mark.parametrize("B,k", [(2, 1), (7, 8), (64, 8), (33, 11), (64, 16), (100, 8), (130, 3)])
-def test_batch_sum_on_tensor_cores(B, k):
+def test_batch_sum_on_tensor_cores(B, k, sum_kernel_variant):
     """Spectral components with one lengthscale: the batch sum as a tensor-core dot product of
     per-point phase vectors (km_matmul_sum_tc.cu) against the fp64 oracle, incl. row windows."""
     from kernel_matmul_b200 import ops
