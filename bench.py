@@ -655,7 +655,7 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
 
     # a running solve: the first iterations are warm-up, then K timed iterations
     warm = max(args.warmup, 3)
-    solver = CGSolver(op, y, max_iterations=warm + args.steps + 8)
+    solver = CGSolver(op, y, max_iterations=warm + args.steps + 16)
     matvec = op.matvec_rows
     product_events = []
 
@@ -678,6 +678,11 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
     sampler = ClockSampler(local)
     wall0 = time.perf_counter()
     step_events = []
+    # ~2 ms of device-side delay first: the launches of the first iterations are then already queued
+    # when their events are reached (the events measure device time; the host's enqueue latency is
+    # part of the end-to-end figure)
+    device_delay()
+    device_delay()
     for _ in range(args.steps):
         flush.fill_(1)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -694,7 +699,28 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
     trace("timed iterations done")
     op.matvec_rows = matvec
     total_ms = sum(a.elapsed_time(b) for a, b in step_events)
+    trace("iteration times (ms): " + " ".join(f"{a.elapsed_time(b):.3f}" for a, b in step_events))
     product_ms = statistics.mean(a.elapsed_time(b) for a, b in product_events) if product_events else 0.0
+    # where an iteration's time goes: a few more iterations with an event at every phase boundary
+    phases: dict[str, list] = {}
+    marks: list = []
+
+    def mark(name):
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        marks.append((name, ev))
+
+    solver.mark = mark
+    device_delay()
+    for _ in range(5):
+        flush.fill_(1)
+        solver.step()
+    solver.mark = None
+    torch.cuda.synchronize()
+    for (name, ev), (nxt, ev2) in zip(marks, marks[1:]):
+        if name != "end":
+            phases.setdefault(name, []).append(ev.elapsed_time(ev2))
+    breakdown = {name: statistics.mean(v) for name, v in phases.items()}
     solver.check_finite()
     residual = float(solver.residual_norms()[-1].max())
     del solver
@@ -789,6 +815,7 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
                             f"{iters} iterations; solution rows out"},
             # per iteration: product (tensor-core kernel + FMA-pipe companion), q/dots, 2 x segment sums, 2 x update
             "gpu_launches": 7 * args.steps,
+            "iteration_breakdown_ms": breakdown,
             "relative_residual_after_timed_region": residual,
             "clocks": clocks, "wall_s": wall,
         }

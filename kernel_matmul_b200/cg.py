@@ -222,10 +222,24 @@ class ShardedOperator:
         sb = start.expand(*B, start.shape[-1]) if batched else start
         eb = end.expand(*B, end.shape[-1]) if batched else end
 
+        prepared: dict = {}  # (buffers, window) -> launch with all arguments already marshalled
+
         def matvec_rows(v: Tensor, rb_begin: int, rb_count: int, out: Tensor) -> None:
-            rhs = v.expand(*B, *v.shape) if batched else v
-            ops.matmul_rows(kernel_type, xb, xb, rhs, params, sb, eb, row_block_begin=rb_begin,
-                            row_block_count=rb_count, sum_batches=batched, out=out)
+            # a solve calls this with the same two buffers every iteration: validate and marshal once
+            key = (v.data_ptr(), tuple(v.shape), tuple(v.stride()), out.data_ptr(), tuple(out.shape), rb_begin, rb_count)
+            call = prepared.get(key)
+            if call is None:
+                rhs = v.expand(*B, *v.shape) if batched else v
+                call = ops.prepare_matmul_rows(kernel_type, xb, xb, rhs, params, sb, eb, row_block_begin=rb_begin,
+                                               row_block_count=rb_count, sum_batches=batched, out=out)
+                if call is None:  # (a product that needs a workspace: the unprepared call)
+                    def call(rhs=rhs, out=out):
+                        ops.matmul_rows(kernel_type, xb, xb, rhs, params, sb, eb, row_block_begin=rb_begin,
+                                        row_block_count=rb_count, sum_batches=batched, out=out)
+                if len(prepared) >= 8:
+                    prepared.clear()
+                prepared[key] = call
+            call()
 
         import torch.distributed as dist
 
@@ -320,6 +334,9 @@ class CGSolver:
         self.alphas = torch.zeros(max_iterations, k, device=dev, dtype=dt)
         self.betas = torch.zeros(max_iterations, k, device=dev, dtype=dt)
         self.it = 0
+        #: set to a callable ``mark(name)`` to be told where the phases of ``step()`` begin
+        #: (bench.py records CUDA events there for its per-phase breakdown)
+        self.mark = None
         # exchange buffers: [segment sums (fp64)] [first halo_above rows of q] [last halo_below rows of q]
         self.seg_bytes = _round_up(op.segs_per_rank * k * 8, 256)
         top, bottom = (op.halo_above, op.halo_below) if op.mode == "halo" else (0, 0)
@@ -360,21 +377,29 @@ class CGSolver:
         if self.it >= self.max_iterations:
             raise RuntimeError(f"more than max_iterations = {self.max_iterations} steps")
         rs_old, rs_new = self.rs[self.it & 1], self.rs[(self.it + 1) & 1]
+        mark = self.mark or (lambda name: None)
+        mark("product")
         if op.rows > 0:
             op.matvec_rows(self.p[: op.n], op.begin, op.count, self.kp[op.row0: op.row1])
+        mark("q_dots")
         V.q_dots(self.kp, self.p, op.sigma2, op.row0, op.row1, self.bp, self.send1, self.top_off, self.top_rows,
                  self.bottom_off, self.bottom_rows)
         V.segment_sums(k, self.bp, op.count, op.seg_blocks, self.send1, 0)
+        mark("gather1")
         self._gather(self.g1, self.send1)
         if self.gq is not None:
             self._gather(self.gq, self.kp[op.rank * op.per_rows: (op.rank + 1) * op.per_rows])
+        mark("update_xr")
         V.update_xr(self.x, self.r, self.p, self.kp, self.q_below, self.q_above, op.row0, op.row1, op.lo, op.hi,
                     self.g1, self.packed, op.world, op.segs_per_rank, rs_old, self.bp, self.alphas[self.it])
         V.segment_sums(k, self.bp, op.count, op.seg_blocks, self.send2, 0)
+        mark("gather2")
         self._gather(self.g2, self.send2)
         self.it += 1
+        mark("update_p")
         V.update_p(self.p, self.r, op.lo, op.hi, self.g2, self.seg_bytes, op.world, op.segs_per_rank, rs_old, rs_new,
                    self.ynorm, self.history[self.it], self.betas[self.it - 1])
+        mark("end")
         return self.history[self.it]
 
     def residual_norms(self) -> Tensor:

@@ -338,6 +338,52 @@ def matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: T
     return out
 
 
+class PreparedRowsProduct:
+    """``matmul_rows`` with everything but the launch done once: arguments validated and expanded,
+    the C structures filled.  For loops that call the same product on the same buffers many times
+    (a CG solve: ``rhs`` and ``out`` are fixed buffers whose CONTENTS change) -- a call is then one
+    foreign-function call, a few microseconds of host time instead of a few hundred.  Only the
+    entry point without a workspace (``km_matmul_rows_f32``: FMA pipe, and the batch sum on either
+    pipe) can be prepared; ``prepare_matmul_rows`` returns ``None`` where ``matmul_rows`` would
+    take the tensor-core kernel with its workspace."""
+
+    def __init__(self, dev, args, keep):
+        self._dev, self._args, self._keep = dev, args, keep
+        self._state = _state(dev)
+
+    def __call__(self) -> None:
+        self._state.poll(wait=False)
+        with torch.cuda.device(self._dev):
+            _check(lib.km_matmul_rows_f32(*self._args, _stream(self._dev)))
+
+
+def prepare_matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor, start: Tensor, end: Tensor,
+                        *, row_block_begin: int, row_block_count: int, sum_batches: bool, out: Tensor):
+    """A ``PreparedRowsProduct`` that computes what ``matmul_rows(..., out=out)`` computes, or ``None``
+    (see there).  The tensors must stay alive and in place; their contents may change between calls."""
+    kid, dev, batch, m, n, (x1e, x2e, pe, se, ee, re) = _prep(kernel_type, x1, x2, params, start, end, [(rhs, 2)])
+    if rhs.shape[-2] != n:
+        raise RuntimeError(f"rhs must have n = {n} rows, got {rhs.shape[-2]}")
+    k = rhs.shape[-1]
+    R = -(-m // BLOCK_SIZE)
+    if row_block_begin < 0 or row_block_count < 0 or row_block_begin + row_block_count > R:
+        raise RuntimeError(f"row-block window [{row_block_begin}, {row_block_begin + row_block_count}) outside [0, {R})")
+    rows = max(0, min(m, (row_block_begin + row_block_count) * BLOCK_SIZE) - row_block_begin * BLOCK_SIZE)
+    if sum_batches and len(batch) == 0:
+        sum_batches = False
+    shape = (rows, k) if sum_batches else (*batch, rows, k)
+    if tuple(out.shape) != shape or out.dtype != torch.float32 or out.device != dev:
+        raise RuntimeError(f"out must be a float32 tensor of shape {shape} on {dev}")
+    if len(batch) > KM_MAX_BATCH_DIMS:
+        return None
+    if not sum_batches and rows > 0 and k >= TENSOR_CORE_MIN_K and _enough_items(batch, row_block_count * BLOCK_SIZE):
+        return None  # matmul_rows would run the tensor-core kernel, which needs a workspace per call
+    kb = _km_batch(batch)
+    views = [_view(x1e, 1), _view(x2e, 1), _view(re, 2), _view(pe, 1), _view(se, 1), _view(ee, 1), _view(out, 2)]
+    args = (kid, kb, m, n, k, *views, row_block_begin, row_block_count, 1 if sum_batches else 0)
+    return PreparedRowsProduct(dev, args, (x1e, x2e, re, pe, se, ee, out, kb, views))
+
+
 #: column count from which the gradient ops take the tensor-core kernel on ``path="auto"``
 #: (if the problem has ``TENSOR_CORE_MIN_ITEMS`` work items)
 GRAD_TENSOR_CORE_MIN_K = 8
@@ -503,6 +549,6 @@ def count_entries(m: int, n: int, start: Tensor, end: Tensor) -> Tensor:
 
 
 __all__ = [
-    "matmul", "matmul_rows", "tc_status", "check", "used_tensor_cores", "KernelGaveUpError", "matmul_bwd", "bilinear_derivative", "dense", "dense_bwd", "index", "index_bwd",
+    "matmul", "matmul_rows", "prepare_matmul_rows", "PreparedRowsProduct", "tc_status", "check", "used_tensor_cores", "KernelGaveUpError", "matmul_bwd", "bilinear_derivative", "dense", "dense_bwd", "index", "index_bwd",
     "count_entries", "BLOCK_SIZE", "NUM_PARAMS",
 ]
