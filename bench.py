@@ -57,6 +57,7 @@ if ROOT not in sys.path:
 METRIC = "kernel_entries_x_rhs_cols_per_s"
 UNIT = "entry-cols/s"
 DEFAULT_WORKLOAD = "cg_sum"
+ALIGN_ITERATIONS = 2  # untimed CG iterations between the barrier and the timed ones (see run_cg)
 
 # Algorithmic per-entry instruction budget of the FMA path (FP32-pipe instructions, SFU ops):
 # generation + contraction.  Forward: k FFMA per entry; gradient: k FFMA for the coefficient
@@ -655,7 +656,7 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
 
     # a running solve: the first iterations are warm-up, then K timed iterations
     warm = max(args.warmup, 3)
-    solver = CGSolver(op, y, max_iterations=warm + args.steps + 16)
+    solver = CGSolver(op, y, max_iterations=warm + ALIGN_ITERATIONS + args.steps + 16)
     matvec = op.matvec_rows
     product_events = []
 
@@ -680,9 +681,15 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
     step_events = []
     # ~2 ms of device-side delay first: the launches of the first iterations are then already queued
     # when their events are reached (the events measure device time; the host's enqueue latency is
-    # part of the end-to-end figure)
+    # part of the end-to-end figure).  The ranks leave the barrier a few milliseconds apart, and the
+    # rank that is first would count its wait for the last one inside its first all-gather: two
+    # more untimed iterations, enqueued back to back with the timed ones, bring the ranks into
+    # step on the device before the first event pair.
     device_delay()
     device_delay()
+    for _ in range(ALIGN_ITERATIONS):
+        flush.fill_(1)
+        solver.step()
     for _ in range(args.steps):
         flush.fill_(1)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -807,6 +814,9 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
                            "allgather": "3 NCCL all_gather_into_tensor per iteration: q (all rows, n x k fp32) and two sets "
                                         "of segment sums"}[op.mode],
             "l2": "flushed between iterations (256 MB write, outside the event pairs)",
+            "timed_region": f"barrier + synchronize, {ALIGN_ITERATIONS} untimed iterations that bring the ranks into step on the "
+                            f"device, {args.steps} iterations each inside its own CUDA-event pair (their sum, max over ranks), "
+                            "synchronize + barrier",
             "roofline": roofline,
             "e2e": None if args.no_e2e else {"value": units * iters / (e2e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": h2d / iters,
                     "d2h_bytes_per_step": d2h / iters, "solve_ms": e2e_ms, "iterations": iters,

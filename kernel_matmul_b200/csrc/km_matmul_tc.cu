@@ -60,7 +60,10 @@ constexpr int TC_SCALE_WORDS = 2 * TC_MAX_N;
 template <int N>
 struct TcCfg {
     static constexpr int G = N == 128 ? 4 : (N == 64 ? 2 : 1);  // generator groups of 128 threads
-    static constexpr int THREADS = 128 * G + 32;
+    // at N >= 64 a second helper warp does the slot fetches, so that the warp that issues the MMAs
+    // never waits for a copy to be issued or for a slot to drain
+    static constexpr bool FETCH_WARP = N >= 64;
+    static constexpr int THREADS = 128 * G + 32 + (FETCH_WARP ? 32 : 0);
     static constexpr int BK = N == 128 ? 64 : 32;        // band columns per tile
     static constexpr int SUPER = TC_SCOLS / BK;           // tiles per rhs / x2 slot
     static constexpr int A_COLS = BK;                     // tensor-memory columns per A stage: per 16 band columns hi 8 | lo 8
@@ -175,7 +178,10 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
+    constexpr bool FW = Cfg::FETCH_WARP;
     const bool is_ctl_warp = warp == 4 * G;
+    const bool is_fetch_warp = FW && warp == 4 * G + 1;
+    const bool is_gen = warp < 4 * G;
     const int g = tid >> 7;            // generator group
     const int row_local = tid & 127;  // row of the block = tensor-memory lane
 
@@ -255,56 +261,60 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
 #pragma unroll
     for (int c = 0; c < NPT; c++) acc[c] = 0.0f;
 
-    if (is_ctl_warp) {
-        // ------------------------------------------- slot fetches (all lanes) + MMA issue (lane 0)
-        // Slots are fetched in increasing order, so a phase kernel keeps the x2 values of the
-        // next fetch in registers (loaded one fetch ahead: the load latency never stalls the warp).
-        float x_ahead[TC_SCOLS / 32];
-        auto load_ahead = [&](int sr) {
+    if (is_ctl_warp || is_fetch_warp) {
+    // ------------------------------------------------------ slot fetches (all lanes of a helper warp)
+    // Slots are fetched in increasing order, so a phase kernel keeps the x2 values of the
+    // next fetch in registers (loaded one fetch ahead: the load latency never stalls the warp).
+    float x_ahead[TC_SCOLS / 32];
+    auto load_ahead = [&](int sr) {
+#pragma unroll
+        for (int u = 0; u < TC_SCOLS / 32; u++) {
+            const int64_t j = (int64_t)(super_lo + sr) * TC_SCOLS + lane + 32 * u;
+            x_ahead[u] = (sr < supers && j < n) ? __ldg(x2 + j * a.x2.s0) : 0.0f;
+        }
+    };
+    int fetched = 0, landed = 0;  // slots whose copies were issued / (set when a wait gives up) were seen complete
+    auto fetch = [&](int sr) {
+        fetched = sr + 1;
+        const int sl = sr % TC_SLOTS;
+        const int64_t sup = super_lo + sr;
+        float *xs = slot_x2(sl);
+        if (lane == 0) {
+            mbar_expect_tx(&bar_full[sl], TC_IMG_BYTES);
+            bulk_copy_g2s(slot_img(sl), images + sup * TC_IMG_BYTES, TC_IMG_BYTES, &bar_full[sl]);
+        }
+        if constexpr (KernelFn<KT>::PHASE) {
 #pragma unroll
             for (int u = 0; u < TC_SCOLS / 32; u++) {
-                const int64_t j = (int64_t)(super_lo + sr) * TC_SCOLS + lane + 32 * u;
-                x_ahead[u] = (sr < supers && j < n) ? __ldg(x2 + j * a.x2.s0) : 0.0f;
-            }
-        };
-        if constexpr (KernelFn<KT>::PHASE) load_ahead(0);
-        int fetched = 0, landed = 0;  // slots whose copies were issued / (set when a wait gives up) were seen complete
-        auto fetch = [&](int sr) {
-            fetched = sr + 1;
-            const int sl = sr % TC_SLOTS;
-            const int64_t sup = super_lo + sr;
-            float *xs = slot_x2(sl);
-            if (lane == 0) {
-                mbar_expect_tx(&bar_full[sl], TC_IMG_BYTES);
-                bulk_copy_g2s(slot_img(sl), images + sup * TC_IMG_BYTES, TC_IMG_BYTES, &bar_full[sl]);
-            }
-            if constexpr (KernelFn<KT>::PHASE) {
-#pragma unroll
-                for (int u = 0; u < TC_SCOLS / 32; u++) {
-                    const int jj = lane + 32 * u;
-                    const float xv = x_ahead[u];
-                    xs[jj] = xv;
-                    if (use_ph) {
-                        const float ph = phase_w * (xv - x0);
-                        xs[TC_SCOLS + jj] = cos_approx(ph);
-                        xs[2 * TC_SCOLS + jj] = sin_approx(ph);
-                    }
+                const int jj = lane + 32 * u;
+                const float xv = x_ahead[u];
+                xs[jj] = xv;
+                if (use_ph) {
+                    const float ph = phase_w * (xv - x0);
+                    xs[TC_SCOLS + jj] = cos_approx(ph);
+                    xs[2 * TC_SCOLS + jj] = sin_approx(ph);
                 }
-                load_ahead(sr + 1);
-                __syncwarp();  // every lane's stores precede lane 0's (releasing) arrival
-                if (lane == 0) mbar_arrive(&bar_full[sl]);
-            } else {
-#pragma unroll
-                for (int u = 0; u < TC_SCOLS / 32; u++) {
-                    const int jj = lane + 32 * u;
-                    const int64_t j = sup * TC_SCOLS + jj;
-                    const bool valid = j < n;
-                    cp_async4_zfill(xs + jj, x2 + (valid ? j : 0) * a.x2.s0, valid);
-                }
-                cp_async_mbar_arrive(&bar_full[sl]);
             }
-        };
-        for (int sr = 0; sr < min(supers, TC_SLOTS); sr++) fetch(sr);
+            load_ahead(sr + 1);
+            __syncwarp();  // every lane's stores precede lane 0's (releasing) arrival
+            if (lane == 0) mbar_arrive(&bar_full[sl]);
+        } else {
+#pragma unroll
+            for (int u = 0; u < TC_SCOLS / 32; u++) {
+                const int jj = lane + 32 * u;
+                const int64_t j = sup * TC_SCOLS + jj;
+                const bool valid = j < n;
+                cp_async4_zfill(xs + jj, x2 + (valid ? j : 0) * a.x2.s0, valid);
+            }
+            cp_async_mbar_arrive(&bar_full[sl]);
+        }
+    };
+    if (is_ctl_warp) {
+        // ---------------------------------------------------------------- MMA issue (lane 0)
+        if constexpr (!FW) {
+            if constexpr (KernelFn<KT>::PHASE) load_ahead(0);
+            for (int sr = 0; sr < min(supers, TC_SLOTS); sr++) fetch(sr);
+        }
 
         // B: core matrices of 8 columns (N) x 16 bytes (8 fp16 along K); K-adjacent matrices N * 16 bytes apart
         constexpr uint32_t lbo_b = N * 16, sbo = 128;
@@ -352,7 +362,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             }
             __syncwarp();
             // after the first tile of a slot: the previous slot is re-filled once its MMAs are done
-            if (slot_first && sr >= 1 && sr - 1 + TC_SLOTS < supers) {
+            if (!FW && slot_first && sr >= 1 && sr - 1 + TC_SLOTS < supers) {
                 const int prev = sr - 1;
                 ok = mbar_wait(&bar_sfree[prev % TC_SLOTS], (unsigned)((prev / TC_SLOTS) & 1), a.wait_polls);
                 if (!__all_sync(0xffffffffu, ok)) {
@@ -382,6 +392,30 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
         // no cp.async may be in flight when the CTA exits
         cp_async_wait<0>();
         __syncwarp();
+    } else if (is_fetch_warp) {
+        // ------------------------------------------------------------- slot fetches (N >= 64)
+        if constexpr (KernelFn<KT>::PHASE) load_ahead(0);
+        for (int sr = 0; sr < supers; sr++) {
+            if (sr >= TC_SLOTS) {
+                // the slot's previous content has been read by its MMAs (whose A tiles the generators
+                // wrote after reading the slot's x2 values)
+                const int prev = sr - TC_SLOTS;
+                const bool ok = mbar_wait(&bar_sfree[prev % TC_SLOTS], (unsigned)((prev / TC_SLOTS) & 1), a.wait_polls);
+                if (!__all_sync(0xffffffffu, ok)) {
+                    failed = true;
+                    break;
+                }
+            }
+            fetch(sr);
+        }
+        // No copy may be in flight when the CTA exits: the last copy into every slot has landed
+        // (immediately true unless a wait gave up; then with the full poll limit: copies do arrive).
+        for (int sr = max(0, fetched - TC_SLOTS); sr < fetched; sr++)
+            mbar_wait(&bar_full[sr % TC_SLOTS], (unsigned)((sr / TC_SLOTS) & 1), TC_WAIT_POLLS);
+        if (failed && lane == 0) atomicExch(&fail_flag, 1);
+        cp_async_wait<0>();
+        __syncwarp();
+    }
     } else {
         // ----------------------------------------------------------------------- generators
         const int64_t row = r * KM_BLOCK_SIZE + row_local;
@@ -506,11 +540,11 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
         // failure also shows in whatever is computed from the result, without a host synchronisation
         if (tid == 0) atomicExch(a.status, 1);
         const int64_t row = r * KM_BLOCK_SIZE + row_local;
-        if (!is_ctl_warp && g == 0 && row < a.m) {
+        if (is_gen && g == 0 && row < a.m) {
             float *orow = out + (row - a.rb_begin * KM_BLOCK_SIZE) * a.out.s0 + (int64_t)kb * N * a.out.s1;
             for (int c = 0; c < (int)k_here; c++) orow[c * a.out.s1] = __int_as_float(0x7fc00000);
         }
-    } else if (!is_ctl_warp) {
+    } else if (is_gen) {
         const int64_t row = r * KM_BLOCK_SIZE + row_local;
         if (row < a.m) {
             // output scale times the inverse of the rhs column scale

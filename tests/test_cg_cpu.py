@@ -1,4 +1,4 @@
-"""Host logic of the row-sharded CG solve on CPU: world_size-2/3 gloo ranks against a single
+"""Host logic of the row-sharded CG solve on CPU: world_size-2/3/8 gloo ranks against a single
 process and against a dense fp64 solve.  The matvec is a dense torch product and the vector
 steps are the PyTorch stand-in of ``tests/cg_vector_ops.py`` (the CUDA kernels need a GPU);
 sharding by segments, the halo and all-gather exchanges, the buffer layout and the agreement
@@ -88,12 +88,12 @@ def test_solver_refuses_cpu_tensors_without_a_stand_in():
         CGSolver(op, y)
 
 
-def _worker(rank, world, port, out_dir, mode, n):
+def _worker(rank, world, port, out_dir, mode, n, span):
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        x, K, y = _system(n=n)
+        x, K, y = _system(n=n, span=span)
         R = -(-n // 128)
         begin, count = row_block_window(R, rank, world)
         if mode == "halo":
@@ -113,11 +113,12 @@ def _worker(rank, world, port, out_dir, mode, n):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world,mode,n", [(2, "allgather", 1500), (3, "allgather", 1500), (2, "halo", 3000), (3, "halo", 4500)])
-def test_cg_sharded_ranks_agree_with_single_process(tmp_path, world, mode, n):
+@pytest.mark.parametrize("world,mode,n,span", [(2, "allgather", 1500, 30.0), (3, "allgather", 1500, 30.0), (2, "halo", 3000, 30.0),
+                                               (3, "halo", 4500, 30.0), (8, "halo", 5000, 64.0), (8, "allgather", 2000, 30.0)])
+def test_cg_sharded_ranks_agree_with_single_process(tmp_path, world, mode, n, span):
     port = 29500 + (os.getpid() % 2000) + world + (10 if mode == "halo" else 0)
-    mp.spawn(_worker, args=(world, port, str(tmp_path), mode, n), nprocs=world, join=True)
-    x, K, y = _system(n=n)
+    mp.spawn(_worker, args=(world, port, str(tmp_path), mode, n, span), nprocs=world, join=True)
+    x, K, y = _system(n=n, span=span)
     single = conjugate_gradient(ShardedOperator(n, 0.05, _dense_matvec(K, x), vector_ops=TorchVectorOps()), y, iterations=25)
     outs = [torch.load(os.path.join(tmp_path, f"rank{r}.pt")) for r in range(world)]
     assert sum(o["window"][1] for o in outs) == -(-n // 128)
