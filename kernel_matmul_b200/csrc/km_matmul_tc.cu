@@ -51,11 +51,12 @@ constexpr int TC_SCALE_WORDS = 2 * TC_MAX_N;
 //   N = 16:  3 A stages (96 columns) + 2 accumulators of 16 = 128 columns, 4 CTAs per SM
 //   N = 32:  2 A stages (64)         + 2 x 32            = 128 columns, 3 CTAs per SM (registers)
 //   N = 64:  3 A stages (96)         + 2 x 64            = 224 -> 256 columns, 2 CTAs per SM with two
-//            generator groups (16 of the 32 band columns of a tile and 32 accumulator columns each)
+//            generator groups: group g generates every second tile (all 32 band columns of it) and
+//            owns the accumulator columns [32g, 32g + 32) of its row
 //   N = 128: 3 A stages of 64 (192) + 2 x 128           = 448 -> 512 columns, 1 CTA per SM with four
-//            generator groups of 128 threads and tiles of 64 band columns: group g generates the band
-//            columns [16g, 16g + 16) of every tile and owns the accumulator columns [32g, 32g + 32)
-//            of its row
+//            generator groups of 128 threads and tiles of 64 band columns: the groups {0, 1} and
+//            {2, 3} take alternate tiles, each group 32 band columns of its set's tile; group g owns
+//            the accumulator columns [32g, 32g + 32) of its row
 // A tile is BK band columns (BK / 16 MMA steps of K = 16); a thread generates 16 columns per step it owns.
 template <int N>
 struct TcCfg {
@@ -63,6 +64,10 @@ struct TcCfg {
     // at N >= 64 a second helper warp does the slot fetches, so that the warp that issues the MMAs
     // never waits for a copy to be issued or for a slot to drain
     static constexpr bool FETCH_WARP = N >= 64;
+    // with several generator groups the tiles alternate between two sets of groups: a thread then
+    // generates twice as many entries per hand-off (barrier waits, store fence, arrival)
+    static constexpr int TILE_SETS = G >= 2 ? 2 : 1;
+    static constexpr int SET_GROUPS = G / TILE_SETS;       // groups that share a tile
     static constexpr int THREADS = 128 * G + 32 + (FETCH_WARP ? 32 : 0);
     static constexpr int BK = N == 128 ? 64 : 32;        // band columns per tile
     static constexpr int SUPER = TC_SCOLS / BK;           // tiles per rhs / x2 slot
@@ -224,7 +229,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
         }
 #pragma unroll
         for (int s = 0; s < TC_A_STAGES; s++) {
-            mbar_init(&bar_ready[s], 4 * G);
+            mbar_init(&bar_ready[s], 4 * Cfg::SET_GROUPS);
             mbar_init(&bar_empty[s], 1);
         }
 #pragma unroll
@@ -438,27 +443,43 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             tc_fence_before();
         };
 
-        for (int t = 0; t < tiles; t++) {
+        const int groups = (tiles + TC_PROMO - 1) / TC_PROMO;  // accumulator groups of this row block
+        int collected = 0;                                      // groups this thread has added to its registers
+        auto collect_group = [&](int cg, bool release) {
+            if (!mbar_wait_warp(&bar_acc[cg & 1], (unsigned)((cg / 2) & 1), a.wait_polls)) {
+                failed = true;
+                return false;
+            }
+            collect(cg & 1);
+            __syncwarp();
+            // (the issuing warp waits for these arrivals before group cg + 2 overwrites the accumulator)
+            if (release && cg + 2 < groups && lane == 0) mbar_arrive(&bar_free[cg & 1]);
+            return true;
+        };
+        constexpr int TS = Cfg::TILE_SETS, GS = Cfg::SET_GROUPS;
+        const int set = g / GS, gi = g % GS;  // this thread's set of groups and its group's place in it
+        int seen_sr = -1;                      // last slot this thread has waited for
+        for (int t = set; t < tiles; t += TS) {
             const int ta = tile_lo + t;
             const int q = ta & (TC_SUPER - 1);
             const int sr = ta / TC_SUPER - super_lo;
             const int sl = sr % TC_SLOTS;
             const int s = t % TC_A_STAGES, use = t / TC_A_STAGES;
-            const int grp = t / TC_PROMO, ai = grp & 1;
-            if ((t == 0 || q == 0) && !mbar_wait_warp(&bar_full[sl], (unsigned)((sr / TC_SLOTS) & 1), a.wait_polls)) {
-                failed = true;
-                break;
-            }
-            // an accumulator that is about to be reused is first added to the registers
-            if ((t % TC_PROMO) == 0 && grp >= 2) {
-                if (!mbar_wait_warp(&bar_acc[ai], (unsigned)((grp / 2 - 1) & 1), a.wait_polls)) {
+            const int grp = t / TC_PROMO;
+            if (sr != seen_sr) {
+                if (!mbar_wait_warp(&bar_full[sl], (unsigned)((sr / TC_SLOTS) & 1), a.wait_polls)) {
                     failed = true;
                     break;
                 }
-                collect(ai);
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&bar_free[ai]);
+                seen_sr = sr;
             }
+            // an accumulator that is about to be reused (by accumulator group grp) is first added
+            // to the registers: every warp collects every group once, in order
+            while (collected + 2 <= grp) {
+                if (!collect_group(collected, true)) break;
+                collected++;
+            }
+            if (failed) break;
             // stage s must have been read by the MMAs of tile t - TC_A_STAGES
             if (use > 0) {
                 if (!mbar_wait_warp(&bar_empty[s], (unsigned)((use - 1) & 1), a.wait_polls)) {
@@ -475,7 +496,7 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             // far under the tolerance), lo = kv - hi rounded to fp16.  Tensor-memory columns of
             // the 16 band columns: [8 hi pairs | 8 lo pairs].
 #pragma unroll
-            for (int half = g; half < TC_BK / 16; half += G) {  // this group's 16-column steps
+            for (int half = gi; half < TC_BK / 16; half += GS) {  // this group's 16-column steps
                 // packed f32x2 arithmetic: two entries per FP32 instruction, kept as pairs up to the
                 // fp16 conversions (8 hi words, 8 lo words: the 16 tensor-memory columns of this step)
                 const ulonglong2 *xs2 = reinterpret_cast<const ulonglong2 *>(xs);
@@ -521,14 +542,10 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
             if (lane == 0) mbar_arrive(&bar_ready[s]);
         }
 
-        // drain: the last two groups still sit in tensor memory
-        const int groups = (tiles + TC_PROMO - 1) / TC_PROMO;
-        for (int grp = max(0, groups - 2); grp < groups && !failed; grp++) {
-            if (!mbar_wait_warp(&bar_acc[grp & 1], (unsigned)((grp / 2) & 1), a.wait_polls)) {
-                failed = true;
-                break;
-            }
-            collect(grp & 1);
+        // drain: the groups not collected yet (the last two, and any a set of groups had no tile in)
+        while (!failed && collected < groups) {
+            if (!collect_group(collected, true)) break;
+            collected++;
         }
         if (failed) atomicExch(&fail_flag, 1);
     }
