@@ -628,7 +628,9 @@ static int matmul_entry(const char *name, int kernel_type, const km_batch *batch
             t.out = a.out;
             t.comp_begin = 0;
             t.comp_count = 0;
-            const int rc = sum_tc_variant() == 1 ? launch_matmul_sum_tc(t, s) : launch_matmul_sum_tc2(t, s);
+            const int variant = sum_tc_variant();
+            const int rc = variant == 1 ? launch_matmul_sum_tc(t, s)
+                                        : (variant == 2 ? launch_matmul_sum_tc2(t, s) : launch_matmul_sum_tc3(t, s));
             if (rc != KM_OK) return rc;
             a.sum_tc_launched = 1;
         }

@@ -49,7 +49,8 @@ template <int KB, int G>
 __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const SumTcArgs a) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_in[ST_IN_STAGES];  // x2 + rhs tile landed
-    __shared__ __align__(8) uint64_t bar_bready[2];         // psi tile written
+    __shared__ __align__(8) uint64_t bar_bready[3];         // psi tile written
+    __shared__ __align__(8) uint64_t bar_pfree[3];          // psi tile read by its MMAs (tcgen05.commit)
     __shared__ __align__(8) uint64_t bar_cfull[2];          // C tile complete (tcgen05.commit)
     __shared__ __align__(8) uint64_t bar_cfree[2];          // C tile consumed
     __shared__ __align__(8) uint64_t bar_drain;             // give-up path: every issued MMA has completed
@@ -94,7 +95,11 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
     // shared memory: two psi stages [part: hi, lo][chunk = K / 8][j][8 halfs], then the input stages
     const int b_part_bytes = (2 * Bp / 8) * ST_COLS * 16;
     const int b_stage_bytes = 2 * b_part_bytes;
-    unsigned char *in_base = smem_raw + 2 * b_stage_bytes;
+    // With two row groups and k <= 8 there is room for a third psi stage (two CTAs per SM): a group
+    // then writes psi of its NEXT tile while the MMAs of its current one run, instead of idling.
+    constexpr bool AHEAD = G == 2 && KB == 8;
+    constexpr int P = AHEAD ? 3 : 2;  // psi stages; tile t uses stage t % P
+    unsigned char *in_base = smem_raw + P * b_stage_bytes;
     constexpr int IN_STAGE_FLOATS = ST_COLS + ST_COLS * KB;  // x2 values, then rhs rows
     auto b_stage = [&](int st) { return smem_raw + st * b_stage_bytes; };
     auto in_x2 = [&](int st) { return reinterpret_cast<float *>(in_base) + st * IN_STAGE_FLOATS; };
@@ -116,9 +121,13 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
         for (int s = 0; s < ST_IN_STAGES; s++) mbar_init(&bar_in[s], 32);  // one cp.async arrival per lane
 #pragma unroll
         for (int s = 0; s < 2; s++) {
-            mbar_init(&bar_bready[s], 4);
             mbar_init(&bar_cfull[s], 1);
             mbar_init(&bar_cfree[s], 4);
+        }
+#pragma unroll
+        for (int s = 0; s < 3; s++) {
+            mbar_init(&bar_bready[s], 4);
+            mbar_init(&bar_pfree[s], 1);
         }
         mbar_init(&bar_drain, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -173,7 +182,7 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
                 ok = mbar_wait(&bar_cfree[st], (unsigned)(((t >> 1) - 1) & 1), a.wait_polls);
                 if (__all_sync(0xffffffffu, ok) && t + 2 < tiles) fetch(t + 2);
             }
-            if (ok) ok = mbar_wait(&bar_bready[st], (unsigned)((t >> 1) & 1), a.wait_polls);
+            if (ok) ok = mbar_wait(&bar_bready[t % P], (unsigned)((t / P) & 1), a.wait_polls);
             if (!__all_sync(0xffffffffu, ok)) {
                 failed = true;
                 break;
@@ -181,7 +190,7 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t d_tmem = tmem_base + (uint32_t)(ST_C_COL + st * ST_COLS);
-                const uint64_t b_hi = d_b0 + st * stage_step, b_lo = b_hi + part_step;
+                const uint64_t b_hi = d_b0 + (t % P) * stage_step, b_lo = b_hi + part_step;
                 // straight-line code per k-step count (a partially unrolled run-time loop of MMAs gave
                 // wrong tiles in the gradient kernel; see there)
                 auto issue = [&](auto ks_tag) {
@@ -207,6 +216,7 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
                     default: issue(std::integral_constant<int, 8>{}); break;
                 }
                 mma_commit(&bar_cfull[st]);
+                if (AHEAD) mma_commit(&bar_pfree[t % P]);
             }
             __syncwarp();
         }
@@ -242,7 +252,7 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
 
         // psi of the tile's columns -> shared memory (thread: column row_local % 64, half of the components)
         auto generate = [&](int t) {
-            const int st = t & 1;
+            const int st = t % P;
             const int jj = row_local & 63;
             const float aj = in_x2(t % ST_IN_STAGES)[jj] - x0;
             unsigned char *hi = b_stage(st) + jj * 16;
@@ -277,9 +287,25 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
             if (!mbar_wait_warp(&bar_in[0], 0u, a.wait_polls)) failed = true;
             if (!failed) generate(0);
         }
+        if (AHEAD && g < tiles) {
+            if (!mbar_wait_warp(&bar_in[g], 0u, a.wait_polls)) failed = true;
+            if (!failed) generate(g);
+        }
         for (int t = (G == 1 ? 0 : g); t < tiles && !failed; t += G) {
             const int st = t & 1;
-            if (G > 1) {
+            if (AHEAD) {
+                // psi of this group's next tile while the MMAs of tile t run; its psi stage was last
+                // read by the MMAs of tile t - 1
+                if (t + 2 < tiles) {
+                    bool ok = mbar_wait_warp(&bar_in[(t + 2) % ST_IN_STAGES], (unsigned)(((t + 2) / ST_IN_STAGES) & 1), a.wait_polls);
+                    if (ok && t >= 1) ok = mbar_wait_warp(&bar_pfree[(t - 1) % P], (unsigned)(((t - 1) / P) & 1), a.wait_polls);
+                    if (!ok) {
+                        failed = true;
+                        break;
+                    }
+                    generate(t + 2);
+                }
+            } else if (G > 1) {
                 // this group's tile: psi first, then the product of the tensor core
                 if (!mbar_wait_warp(&bar_in[t % ST_IN_STAGES], (unsigned)((t / ST_IN_STAGES) & 1), a.wait_polls)) {
                     failed = true;
@@ -408,7 +434,8 @@ template <int KB, int G>
 static int launch_sum_tc_kb(const SumTcArgs &a, cudaStream_t stream) {
     const int Bp = ((int)a.comp_count + 7) & ~7;
     const size_t b_stage = (size_t)2 * (2 * Bp / 8) * ST_COLS * 16;
-    size_t smem = 2 * b_stage + (size_t)ST_IN_STAGES * (ST_COLS + ST_COLS * KB) * sizeof(float);
+    const int psi_stages = (G == 2 && KB == 8) ? 3 : 2;
+    size_t smem = psi_stages * b_stage + (size_t)ST_IN_STAGES * (ST_COLS + ST_COLS * KB) * sizeof(float);
     // two CTAs of 256 tensor-memory columns fill an SM: keep a third from being scheduled
     smem = std::max<size_t>(smem, 80 * 1024);
     auto kernel = matmul_sum_tc_kernel<KB, G>;
@@ -428,7 +455,9 @@ static int sum_tc_groups() {
 
 int sum_tc_variant() {
     const char *e = getenv("KM_SUM_TC_VARIANT");  // read at every launch: tests switch it at run time
-    return (e != nullptr && e[0] == '2') ? 2 : 1;
+    if (e != nullptr && e[0] == '2') return 2;
+    if (e != nullptr && e[0] == '3') return 3;
+    return 1;
 }
 
 int launch_matmul_sum_tc(const SumTcArgs &a, cudaStream_t stream) {

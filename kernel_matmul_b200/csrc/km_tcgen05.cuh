@@ -269,8 +269,11 @@ int launch_matmul_sum_tc(const SumTcArgs &a, cudaStream_t stream);
 // (km_matmul_sum_tc2.cu): correct, but measured slower than the first form (17.5 against 11.7 ms on
 // the 64-component benchmark), so it only runs when asked for.
 int launch_matmul_sum_tc2(const SumTcArgs &a, cudaStream_t stream);
-// Which of the two runs: 1 (default) or 2, from the environment variable KM_SUM_TC_VARIANT (read at
-// every launch; a comparison hook).
+// The first form with two row blocks per CTA (km_matmul_sum_tc3.cu): a thread owns a row of each,
+// so the rhs values, the psi tile and the x2 values it brings in serve twice the entries.
+int launch_matmul_sum_tc3(const SumTcArgs &a, cudaStream_t stream);
+// Which one runs: 1, 2 or 3, from the environment variable KM_SUM_TC_VARIANT (read at every launch; a
+// comparison hook).
 int sum_tc_variant();
 
 }  // namespace km
