@@ -140,6 +140,12 @@ KM_API int km_workspace_status(const void *workspace, int32_t *status_out, void 
  * The batch sum is the product with the reference's SumKernel operator
  * (kernel_matmul/gpytorch/sum.py:16-24: the batched operator summed over its batch dim), which
  * the reference evaluates as B separate products followed by a sum.
+ * Up to 1024 spectral components with one common lengthscale and k <= 16 take the tensor-core form
+ * of the sum (the sum over the components as a dot product of per-point phase vectors).  Two
+ * environment variables, read at every launch, select other arrangements of that kernel; they
+ * exist for the tests and for comparison, every setting gives the same result to fp32 accuracy:
+ *   KM_SUM_TC_VARIANT = 1 (default) | 2 (rhs contraction on the tensor core too) | 3 (two row
+ *   blocks per CTA, k <= 8);  KM_SUM_TC_GROUPS = 2 (default) | 1 (row groups per CTA, variant 1).
  * ------------------------------------------------------------------------------------- */
 KM_API int km_matmul_rows_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
                               int64_t k, const km_view *x1, const km_view *x2,

@@ -528,13 +528,8 @@ __global__ void __launch_bounds__(TcCfg<N>::THREADS, TcCfg<N>::MIN_CTAS) matmul_
                         kv2[u] &= keep;
                     }
                 }
-                uint32_t words[16];
-#pragma unroll
-                for (int u = 0; u < 8; u++) {
-                    words[u] = cvt_rz_f16x2_pair(kv2[u]);  // hi: truncated to fp16 precision
-                    words[8 + u] = cvt_rn_f16x2_pair(sub2(kv2[u], kv2[u] & 0xffffe000ffffe000ull));  // lo = kv - hi
-                }
-                tmem_st16(tmem_lane + (uint32_t)(s * TC_A_COLS + half * 16), words);
+                // hi = kv truncated to fp16 precision, lo = kv - hi rounded: 8 + 8 words, one store
+                split_store16_pairs(tmem_lane + (uint32_t)(s * TC_A_COLS + half * 16), kv2);
             }
             tmem_st_wait();
             tc_fence_before();

@@ -188,6 +188,33 @@ __device__ __forceinline__ uint32_t cvt_rn_f16x2_pair(unsigned long long v) {
     asm("{\n\t.reg .f32 a, b;\n\tmov.b64 {a, b}, %1;\n\tcvt.rn.f16x2.f32 %0, b, a;\n\t}" : "=r"(r) : "l"(v));
     return r;
 }
+// Eight packed pairs of fp32 values (16 kernel entries) -> their fp16 hi parts (truncated) and lo
+// parts (value - hi, rounded) -> 16 consecutive tensor-memory columns of this thread's lane:
+// [8 hi words | 8 lo words].  One asm block from the pairs to the store, so that the conversions
+// write straight into the consecutive registers tcgen05.st takes (with the words as C++ values
+// the compiler moved each of them once: two moves per pair of entries).
+__device__ __forceinline__ void split_store16_pairs(uint32_t taddr, const unsigned long long (&kv)[8]) {
+#define KM_SPLIT_PAIR(U, HI, LO)                                  \
+    "mov.b64 {x, y}, %" #U ";\n\t"                                 \
+    "cvt.rz.f16x2.f32 " #HI ", y, x;\n\t"                          \
+    "and.b64 m, %" #U ", 0xffffe000ffffe000;\n\t"                  \
+    "sub.rn.f32x2 d, %" #U ", m;\n\t"                              \
+    "mov.b64 {x, y}, d;\n\t"                                       \
+    "cvt.rn.f16x2.f32 " #LO ", y, x;\n\t"
+    asm volatile(
+        "{\n\t"
+        ".reg .b32 p<16>;\n\t"
+        ".reg .f32 x, y;\n\t"
+        ".reg .b64 m, d;\n\t"
+        KM_SPLIT_PAIR(1, p0, p8) KM_SPLIT_PAIR(2, p1, p9) KM_SPLIT_PAIR(3, p2, p10) KM_SPLIT_PAIR(4, p3, p11)
+        KM_SPLIT_PAIR(5, p4, p12) KM_SPLIT_PAIR(6, p5, p13) KM_SPLIT_PAIR(7, p6, p14) KM_SPLIT_PAIR(8, p7, p15)
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {p0, p1, p2, p3, p4, p5, p6, p7, p8, p9, p10, p11, p12, p13, p14, p15};\n\t"
+        "}"
+        :
+        : "r"(taddr), "l"(kv[0]), "l"(kv[1]), "l"(kv[2]), "l"(kv[3]), "l"(kv[4]), "l"(kv[5]), "l"(kv[6]), "l"(kv[7])
+        : "memory");
+#undef KM_SPLIT_PAIR
+}
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // 4-byte asynchronous copy that writes zero when `valid` is false (the source is not read)
