@@ -145,7 +145,8 @@ KM_API int km_workspace_status(const void *workspace, int32_t *status_out, void 
  * environment variables, read at every launch, select other arrangements of that kernel; they
  * exist for the tests and for comparison, every setting gives the same result to fp32 accuracy:
  *   KM_SUM_TC_VARIANT = 1 (default) | 2 (rhs contraction on the tensor core too) | 3 (two row
- *   blocks per CTA, k <= 8);  KM_SUM_TC_GROUPS = 2 (default) | 1 (row groups per CTA, variant 1).
+ *   blocks per CTA, k <= 8);  KM_SUM_TC_GROUPS = 2 (default) | 1 (row groups per CTA, variant 1);
+ *   KM_SUM_TC_WARP_MMA = 0 (default) | 1 (variant 1, k <= 8: rhs contraction by mma.sync).
  * ------------------------------------------------------------------------------------- */
 KM_API int km_matmul_rows_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
                               int64_t k, const km_view *x1, const km_view *x2,

@@ -45,8 +45,17 @@ constexpr int ST_C_COL = 128;     // first C column
 // and consumes, the tiles t = g, g + 2, ... through psi / C stage g, each with its own partial
 // sums, which are added at the end.  Twice the warps per SM hide the latencies (SFU results,
 // tensor-memory loads, MMA completion) that a single group per CTA leaves exposed.
-template <int KB, int G>
+//
+// MS (KB = 8, G = 2): the contraction with the rhs tile runs on the warp-level tensor path
+// (mma.sync m16n8k8, 3xTF32) instead of the FMA pipe.  A thread then reads C in the register layout
+// of an m16n8 accumulator (tcgen05.ld.16x256b: two rows, two adjacent band columns per load),
+// multiplies by the envelope and uses the products as the A fragment -- band columns (2t, 2t + 1)
+// standing for the fragment's columns (t, t + 4), the rhs pairs in shared memory laid out to
+// match -- so that per 128 entries a warp issues three MMAs and reads 8 bytes of rhs per thread,
+// where the FMA form issues 16 packed FMAs and reads 128 bytes.
+template <int KB, int G, bool MS>
 __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const SumTcArgs a) {
+    static_assert(!MS || (KB == 8 && G == 2), "the warp-level contraction is written for 8 rhs columns, two row groups");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_in[ST_IN_STAGES];  // x2 + rhs tile landed
     __shared__ __align__(8) uint64_t bar_bready[3];         // psi tile written
@@ -100,7 +109,11 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
     constexpr bool AHEAD = G == 2 && KB == 8;
     constexpr int P = AHEAD ? 3 : 2;  // psi stages; tile t uses stage t % P
     unsigned char *in_base = smem_raw + P * b_stage_bytes;
-    constexpr int IN_STAGE_FLOATS = ST_COLS + ST_COLS * KB;  // x2 values, then rhs rows
+    // rhs rows lie in shared memory as pairs of band columns: rs[((jj / 2) * RS + c) * 2 + (jj & 1)];
+    // RS = 12 spreads the warp-level form's reads (thread: pair-row 4 cb + lane % 4, column lane / 4)
+    // over the banks
+    constexpr int RS = MS ? 12 : KB;
+    constexpr int IN_STAGE_FLOATS = ST_COLS + ST_COLS * RS;  // x2 values, then rhs rows
     auto b_stage = [&](int st) { return smem_raw + st * b_stage_bytes; };
     auto in_x2 = [&](int st) { return reinterpret_cast<float *>(in_base) + st * IN_STAGE_FLOATS; };
     auto in_rhs = [&](int st) { return reinterpret_cast<float *>(in_base) + st * IN_STAGE_FLOATS + ST_COLS; };
@@ -142,6 +155,9 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
     f32x2 acc2[KB];  // per output column: (sum over even band columns, sum over odd band columns)
 #pragma unroll
     for (int c = 0; c < KB; c++) acc2[c] = 0ull;
+    // warp-level form: accumulator fragments of the warp's two 16-row tiles (thread lane: rows
+    // lane / 4 and lane / 4 + 8 of a tile, output columns 2 (lane % 4) and 2 (lane % 4) + 1)
+    float dacc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
 
     if (is_ctl_warp) {
         // ------------------------------------------------ input fetches (all lanes) + MMA issue (lane 0)
@@ -156,11 +172,11 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
                 const bool valid = j0 + jj < n;
                 cp_async4_zfill(xs + jj, x2 + (valid ? j0 + jj : 0) * a.x2.s0, valid);
             }
-            // rhs rows in pairs: rs[((jj / 2) * KB + c) * 2 + (jj & 1)] = rhs[j0 + jj][c]
+            // rhs rows in pairs: rs[((jj / 2) * RS + c) * 2 + (jj & 1)] = rhs[j0 + jj][c]
             for (int q = lane; q < ST_COLS * KB; q += 32) {
                 const int jj = q / KB, c = q % KB;
                 const bool valid = j0 + jj < n && c < a.k;
-                cp_async4_zfill(rs + (((jj >> 1) * KB + c) << 1) + (jj & 1),
+                cp_async4_zfill(rs + (((jj >> 1) * RS + c) << 1) + (jj & 1),
                                 rhs + (valid ? (j0 + jj) * a.rhs.s0 + c * a.rhs.s1 : 0), valid);
             }
             cp_async_mbar_arrive(&bar_in[st]);
@@ -228,6 +244,15 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
         const int64_t row = r * KM_BLOCK_SIZE + row_local;
         const float x1v = row < a.m ? a.x1.data[row * a.x1.s0] : x0;
         const uint32_t tmem_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+        // warp-level form: x1 of this thread's four rows 32 (warp % 4) + 16 mt + lane / 4 + 8 hh, as pairs
+        f32x2 xi2[2][2];
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                const int64_t ri = r * KM_BLOCK_SIZE + (warp & 3) * 32 + 16 * mt + (lane >> 2) + 8 * hh;
+                xi2[mt][hh] = splat2((MS && ri < a.m) ? a.x1.data[ri * a.x1.s0] : x0);
+            }
 
         // phi of this row -> tensor memory: per 8 components [8 hi pairs | 8 lo pairs]
         {
@@ -369,10 +394,65 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
                     if (p + 1 < ST_COLS / 16) tmem_ld_wait16(cbuf[(p + 1) & 1]);
                 }
             };
-            if (j0 < band_lo || j0 + ST_COLS > band_hi)
-                consume(std::true_type{});
-            else
-                consume(std::false_type{});
+            auto consume_ms = [&](auto masked_tag) {
+                constexpr bool MASKED = decltype(masked_tag)::value;
+                const int gq = lane >> 2, tq = lane & 3;
+                constexpr f32x2 HI2 = 0xffffe000ffffe000ull;  // the tf32 part of both values of a pair
+                const uint32_t c_tile = tmem_lane + (uint32_t)(ST_C_COL + st * ST_COLS);
+                // the loads of the next 8 columns are in flight while these are processed
+                uint32_t cv[2][2][4];  // [buffer][16-row tile][fragment]
+                tmem_ld_m16n8_nowait(c_tile, cv[0][0]);
+                tmem_ld_m16n8_nowait(c_tile + (16u << 16), cv[0][1]);
+                tmem_ld_wait4x2(cv[0][0], cv[0][1]);
+#pragma unroll
+                for (int cb = 0; cb < ST_COLS / 8; cb++) {
+                    if (cb + 1 < ST_COLS / 8) {
+                        tmem_ld_m16n8_nowait(c_tile + (uint32_t)((cb + 1) * 8), cv[(cb + 1) & 1][0]);
+                        tmem_ld_m16n8_nowait(c_tile + (16u << 16) + (uint32_t)((cb + 1) * 8), cv[(cb + 1) & 1][1]);
+                    }
+                    const int jj = cb * 8 + 2 * tq;  // this thread's band columns jj, jj + 1 of the tile
+                    const f32x2 xj2 = *reinterpret_cast<const f32x2 *>(xs + jj);
+                    // B fragment: rhs[jj][gq], rhs[jj + 1][gq], split into tf32 hi and lo
+                    const f32x2 b2 = *reinterpret_cast<const f32x2 *>(rs + ((((jj >> 1) * RS) + gq) << 1));
+                    const f32x2 bh2 = b2 & HI2, bl2 = sub2(b2, bh2);
+                    const uint32_t bh0 = (uint32_t)bh2, bh1 = (uint32_t)(bh2 >> 32), bl0 = (uint32_t)bl2, bl1 = (uint32_t)(bl2 >> 32);
+#pragma unroll
+                    for (int mt = 0; mt < 2; mt++) {
+                        const uint32_t(&c4)[4] = cv[cb & 1][mt];
+                        f32x2 wh[2], wl[2];
+#pragma unroll
+                        for (int hh = 0; hh < 2; hh++) {
+                            const f32x2 tau2 = sub2(xi2[mt][hh], xj2);
+                            const f32x2 e2 = ex2_approx2(mul2(mul2(tau2, tau2), c02));
+                            uint32_t ca = c4[2 * hh], cbv = c4[2 * hh + 1];
+                            if (MASKED) {
+                                if (j0 + jj < band_lo || j0 + jj >= band_hi) ca = 0u;
+                                if (j0 + jj + 1 < band_lo || j0 + jj + 1 >= band_hi) cbv = 0u;
+                            }
+                            const f32x2 w2 = mul2((f32x2)ca | ((f32x2)cbv << 32), e2);
+                            wh[hh] = w2 & HI2;
+                            wl[hh] = sub2(w2, wh[hh]);
+                        }
+                        // A fragment: (row, k) = (hh, band column parity): a0 = (0, 0), a1 = (1, 0), a2 = (0, 1), a3 = (1, 1)
+                        mma_sync_tf32(dacc[mt], (uint32_t)wl[0], (uint32_t)wl[1], (uint32_t)(wl[0] >> 32), (uint32_t)(wl[1] >> 32), bh0, bh1);
+                        mma_sync_tf32(dacc[mt], (uint32_t)wh[0], (uint32_t)wh[1], (uint32_t)(wh[0] >> 32), (uint32_t)(wh[1] >> 32), bl0, bl1);
+                        mma_sync_tf32(dacc[mt], (uint32_t)wh[0], (uint32_t)wh[1], (uint32_t)(wh[0] >> 32), (uint32_t)(wh[1] >> 32), bh0, bh1);
+                    }
+                    if (cb + 1 < ST_COLS / 8) tmem_ld_wait4x2(cv[(cb + 1) & 1][0], cv[(cb + 1) & 1][1]);
+                }
+            };
+            const bool edge = j0 < band_lo || j0 + ST_COLS > band_hi;
+            if constexpr (MS) {
+                if (edge)
+                    consume_ms(std::true_type{});
+                else
+                    consume_ms(std::false_type{});
+            } else {
+                if (edge)
+                    consume(std::true_type{});
+                else
+                    consume(std::false_type{});
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_cfree[st]);
@@ -389,7 +469,27 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
         unpack2(acc2[c], even, odd);
         acc[c] = even + odd;
     }
-    if (G > 1) {
+    if constexpr (MS) {
+        // both groups' accumulator fragments go through shared memory (the pipelines are done) into
+        // row-per-thread order; group 0 adds the two
+        float *xch = reinterpret_cast<float *>(smem_raw);
+        if (!is_ctl_warp) {
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                for (int hh = 0; hh < 2; hh++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const int row_in_block = (warp & 3) * 32 + 16 * mt + (lane >> 2) + 8 * hh, c = 2 * (lane & 3) + e;
+                        xch[(g * KB + c) * 128 + row_in_block] = dacc[mt][2 * hh + e];
+                    }
+        }
+        __syncthreads();
+        if (!is_ctl_warp && g == 0) {
+#pragma unroll
+            for (int c = 0; c < KB; c++) acc[c] = xch[c * 128 + row_local] + xch[(KB + c) * 128 + row_local];
+        }
+    } else if (G > 1) {
         // the second group hands its partial sums over through shared memory (the pipelines are done)
         float *xch = reinterpret_cast<float *>(smem_raw);
         if (!is_ctl_warp && g == 1) {
@@ -430,15 +530,15 @@ __global__ void __launch_bounds__(128 * G + 32, 2) matmul_sum_tc_kernel(const Su
     }
 }
 
-template <int KB, int G>
+template <int KB, int G, bool MS = false>
 static int launch_sum_tc_kb(const SumTcArgs &a, cudaStream_t stream) {
     const int Bp = ((int)a.comp_count + 7) & ~7;
     const size_t b_stage = (size_t)2 * (2 * Bp / 8) * ST_COLS * 16;
     const int psi_stages = (G == 2 && KB == 8) ? 3 : 2;
-    size_t smem = psi_stages * b_stage + (size_t)ST_IN_STAGES * (ST_COLS + ST_COLS * KB) * sizeof(float);
+    size_t smem = psi_stages * b_stage + (size_t)ST_IN_STAGES * (ST_COLS + ST_COLS * (MS ? 12 : KB)) * sizeof(float);
     // two CTAs of 256 tensor-memory columns fill an SM: keep a third from being scheduled
     smem = std::max<size_t>(smem, 80 * 1024);
-    auto kernel = matmul_sum_tc_kernel<KB, G>;
+    auto kernel = matmul_sum_tc_kernel<KB, G, MS>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(matmul_sum_tc)");
     kernel<<<(unsigned)a.row_blocks, 128 * G + 32, smem, stream>>>(a);
@@ -451,6 +551,15 @@ static int launch_sum_tc_kb(const SumTcArgs &a, cudaStream_t stream) {
 static int sum_tc_groups() {
     const char *e = getenv("KM_SUM_TC_GROUPS");
     return (e != nullptr && e[0] == '1') ? 1 : 2;
+}
+
+// Contraction with the rhs tile (two row groups, k <= 8): on the FMA pipe, or on the warp-level
+// tensor path when the environment variable KM_SUM_TC_WARP_MMA is 1 (read at every launch; measured
+// slower on the 64-component benchmark, 12.6 against 11.6 ms, although it issues 40 % fewer
+// instructions per entry and reads an eighth of the shared-memory bytes: a comparison hook).
+static bool sum_tc_warp_mma() {
+    const char *e = getenv("KM_SUM_TC_WARP_MMA");
+    return e != nullptr && e[0] == '1';
 }
 
 int sum_tc_variant() {
@@ -475,8 +584,10 @@ int launch_matmul_sum_tc(const SumTcArgs &a, cudaStream_t stream) {
         int rc;
         if (sum_tc_groups() == 1)
             rc = a.k <= 8 ? launch_sum_tc_kb<8, 1>(chunk, stream) : launch_sum_tc_kb<16, 1>(chunk, stream);
+        else if (a.k <= 8)
+            rc = sum_tc_warp_mma() ? launch_sum_tc_kb<8, 2, true>(chunk, stream) : launch_sum_tc_kb<8, 2>(chunk, stream);
         else
-            rc = a.k <= 8 ? launch_sum_tc_kb<8, 2>(chunk, stream) : launch_sum_tc_kb<16, 2>(chunk, stream);
+            rc = launch_sum_tc_kb<16, 2>(chunk, stream);
         if (rc != KM_OK) return rc;
     }
     return KM_OK;

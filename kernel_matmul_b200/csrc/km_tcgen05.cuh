@@ -152,6 +152,32 @@ __device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t (&r)[1
         : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// A 16-lane x 8-column tile of tensor memory (the lane field of `taddr` names the first of the 16
+// lanes: offset 0 or 16 inside the warp's 32) in the register layout of an mma.sync m16n8
+// accumulator: thread T holds (lane T / 4, columns 2 (T % 4) and 2 (T % 4) + 1) in r[0], r[1] and
+// (lane T / 4 + 8, the same columns) in r[2], r[3].  The wait is issued by the caller.
+__device__ __forceinline__ void tmem_ld_m16n8_nowait(uint32_t taddr, uint32_t (&r)[4]) {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x1.b32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(taddr)
+                 : "memory");
+}
+// The wait for two such loads, tied to their registers (see tmem_ld_wait16)
+__device__ __forceinline__ void tmem_ld_wait4x2(uint32_t (&p)[4], uint32_t (&q)[4]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(p[0]), "+r"(p[1]), "+r"(p[2]), "+r"(p[3]), "+r"(q[0]), "+r"(q[1]), "+r"(q[2]), "+r"(q[3])
+                 :
+                 : "memory");
+}
+// d (16 x 8, fp32) += a (16 x 8, tf32, row-major fragment) . b (8 x 8, tf32, column fragment) on
+// the warp-level tensor path; operands are fp32 bit patterns of which the tensor core uses the
+// leading 19 bits
+__device__ __forceinline__ void mma_sync_tf32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                              uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 // The wait for the loads into `r`, tied to those registers: the registers of a tcgen05.ld are
 // valid only after tcgen05.wait::ld, but as operands they look complete to the compiler as soon
 // as the load is issued, so arithmetic on them could be scheduled ahead of a wait that does not

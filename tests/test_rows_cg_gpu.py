@@ -176,11 +176,13 @@ def test_marginal_likelihood_gradient_matches_dense_fp64(kt):
 
 
 @pytest.fixture(params=["both contractions on the tensor cores", "second contraction on the FMA pipe",
-                        "second contraction on the FMA pipe, one row group", "two row blocks per CTA"])
+                        "second contraction on the FMA pipe, one row group", "two row blocks per CTA",
+                        "second contraction on the warp-level tensor path"])
 def sum_kernel_variant(request, monkeypatch):
-    """The four forms of the tensor-core batch sum (the library reads the switches at every launch)."""
+    """The five forms of the tensor-core batch sum (the library reads the switches at every launch)."""
     variant = "3" if request.param.startswith("two row blocks") else ("1" if request.param.startswith("second") else "2")
     monkeypatch.setenv("KM_SUM_TC_VARIANT", variant)
+    monkeypatch.setenv("KM_SUM_TC_WARP_MMA", "1" if request.param.endswith("warp-level tensor path") else "0")
     if request.param.endswith("one row group"):
         monkeypatch.setenv("KM_SUM_TC_GROUPS", "1")
     return request.param
