@@ -155,6 +155,37 @@ KM_API int km_matmul_rows_f32(int kernel_type, const km_batch *batch, int64_t m,
                               int64_t row_block_count, int32_t sum_batches, void *stream);
 
 /* ---------------------------------------------------------------------------------------
+ * The batch sum of spectral components with the per-point phase vectors written ONCE per
+ * operator.  The tensor-core form of the sum evaluates, for every tile of band columns and every
+ * row block again, the vectors (cos, sin)(2 pi f_b x_j) of the columns -- values that depend on
+ * the operator (x2, the frequencies) and not on rhs.  A solver that applies one operator many
+ * times calls km_sum_phases_prepare_f32 once: it writes those vectors for all n columns and the
+ * vectors s_b (cos, sin)(2 pi f_b x_i) of all m rows into `workspace` (fp16 hi / lo images in the
+ * tensor core's operand layouts; sine and cosine in fp64 with exact range reduction), and
+ * km_matmul_rows_phases_f32 -- km_matmul_rows_f32 with sum_batches != 0 and the same arguments --
+ * copies them (one bulk copy of 32 KB per tile).  x1, x2 must be shared by all components (batch
+ * stride 0); the workspace is valid for these x1, x2, frequencies and output scales; size from
+ * km_sum_phases_workspace_bytes (about (m + n) * 8 bytes per component), 256-byte aligned.  Where
+ * the tensor-core form does not apply (another kernel type, more than 1024 components, k > 16,
+ * different lengthscales) the call computes what km_matmul_rows_f32 computes and ignores the
+ * workspace.  No reference counterpart: the reference evaluates every component's kernel entries
+ * inside every product (native/matmul/matmul.cu).
+ * ------------------------------------------------------------------------------------- */
+KM_API size_t km_sum_phases_workspace_bytes(const km_batch *batch, int64_t m, int64_t n);
+
+KM_API int km_sum_phases_prepare_f32(const km_batch *batch, int64_t m, int64_t n, const km_view *x1,
+                                     const km_view *x2, const km_view *params, void *workspace,
+                                     size_t workspace_bytes, void *stream);
+
+KM_API int km_matmul_rows_phases_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
+                                     int64_t k, const km_view *x1, const km_view *x2,
+                                     const km_view *rhs, const km_view *params, const km_view *start,
+                                     const km_view *end, const km_view *out, int64_t row_block_begin,
+                                     int64_t row_block_count, const void *phases, size_t phases_bytes,
+                                     void *stream);
+
+
+/* ---------------------------------------------------------------------------------------
  * grad[b, q] = d/d theta_q  sum_{i, j in band, c} left[b,i,c] * kappa(x1[b,i], x2[b,j]) * right[b,j,c]
  * Replaces bilinear_derivative.call(x1, x2, left, right, params, start, end)
  * (native/bilinear_derivative/bilinear_derivative.cpp:6-21, .cu:138-183) and, with

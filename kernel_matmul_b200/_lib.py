@@ -53,6 +53,12 @@ def _load() -> ctypes.CDLL:
     lib.km_matmul_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, vp]
     lib.km_matmul_rows_f32.restype = ctypes.c_int
     lib.km_matmul_rows_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, i64, i64, i32, vp]
+    lib.km_sum_phases_workspace_bytes.restype = sz
+    lib.km_sum_phases_workspace_bytes.argtypes = [bp, i64, i64]
+    lib.km_sum_phases_prepare_f32.restype = ctypes.c_int
+    lib.km_sum_phases_prepare_f32.argtypes = [bp, i64, i64, wp, wp, wp, vp, sz, vp]
+    lib.km_matmul_rows_phases_f32.restype = ctypes.c_int
+    lib.km_matmul_rows_phases_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, i64, i64, vp, sz, vp]
     lib.km_matmul_tc_workspace_bytes.restype = sz
     lib.km_matmul_tc_workspace_bytes.argtypes = [bp, i64, i64, wp]
     lib.km_matmul_tc_f32.restype = ctypes.c_int
@@ -131,7 +137,7 @@ EXPORTED = [
     "km_make_ranges_symmetric_f32", "km_make_ranges_symmetric_cutoffs_f32", "km_transpose_ranges_i32", "km_count_entries",
     "km_probe_fp32_peak", "km_probe_sfu_peak", "km_selftest_bounded_wait", "km_selftest_set_wait_polls",
     "km_cg_block_dots_f32", "km_cg_q_dots_f32", "km_cg_segment_sums_f32", "km_cg_init_scalars_f32", "km_cg_update_xr_f32",
-    "km_cg_update_p_f32",
+    "km_cg_update_p_f32", "km_sum_phases_workspace_bytes", "km_sum_phases_prepare_f32", "km_matmul_rows_phases_f32",
 ]
 
 

@@ -210,9 +210,16 @@ class ShardedOperator:
 
     @classmethod
     def from_kernel(cls, kernel_type: str, x: Tensor, params: Tensor, start: Tensor, end: Tensor, sigma2: float,
-                    group=None, mode: str = "auto") -> "ShardedOperator":
+                    group=None, mode: str = "auto", phases: bool | None = None) -> "ShardedOperator":
         """Operator backed by ``ops.matmul_rows`` (sum over the batch of ``params`` if batched);
-        ``start`` / ``end`` are one band ``(R,)`` shared by all components."""
+        ``start`` / ``end`` are one band ``(R,)`` shared by all components.
+
+        ``phases``: for a sum of spectral components, write the per-point phase vectors once now
+        (``ops.prepare_sum_phases``: about ``16 B n`` bytes for ``B`` components) so that every product
+        of the solve copies them instead of evaluating them again; default: yes, unless the
+        environment variable ``KM_SUM_PHASES`` is ``0``."""
+        import os
+
         from . import ops
 
         n = x.shape[-1]
@@ -222,6 +229,9 @@ class ShardedOperator:
         sb = start.expand(*B, start.shape[-1]) if batched else start
         eb = end.expand(*B, end.shape[-1]) if batched else end
 
+        if phases is None:
+            phases = os.environ.get("KM_SUM_PHASES", "1") != "0"
+        phase_ws = ops.prepare_sum_phases(kernel_type, x, x, params) if (phases and batched) else None
         prepared: dict = {}  # (buffers, window) -> launch with all arguments already marshalled
 
         def matvec_rows(v: Tensor, rb_begin: int, rb_count: int, out: Tensor) -> None:
@@ -231,11 +241,11 @@ class ShardedOperator:
             if call is None:
                 rhs = v.expand(*B, *v.shape) if batched else v
                 call = ops.prepare_matmul_rows(kernel_type, xb, xb, rhs, params, sb, eb, row_block_begin=rb_begin,
-                                               row_block_count=rb_count, sum_batches=batched, out=out)
+                                               row_block_count=rb_count, sum_batches=batched, out=out, phases=phase_ws)
                 if call is None:  # (a product that needs a workspace: the unprepared call)
                     def call(rhs=rhs, out=out):
                         ops.matmul_rows(kernel_type, xb, xb, rhs, params, sb, eb, row_block_begin=rb_begin,
-                                        row_block_count=rb_count, sum_batches=batched, out=out)
+                                        row_block_count=rb_count, sum_batches=batched, out=out, phases=phase_ws)
                 if len(prepared) >= 8:
                     prepared.clear()
                 prepared[key] = call

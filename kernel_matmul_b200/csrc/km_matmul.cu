@@ -566,7 +566,8 @@ static int dispatch_matmul(MatmulArgs<float> &a, cudaStream_t stream) {
 static int matmul_entry(const char *name, int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
                         const km_view *x1, const km_view *x2, const km_view *rhs, const km_view *params,
                         const km_view *start, const km_view *end, const km_view *out, int64_t rb_begin,
-                        int64_t rb_count, bool sum_batches, void *stream) {
+                        int64_t rb_count, bool sum_batches, void *stream, const void *phases = nullptr,
+                        size_t phases_bytes = 0) {
     KM_REQUIRE(valid_kernel_type(kernel_type), KM_ERR_INVALID_ARGUMENT, "%s: unknown kernel type %d", name, kernel_type);
     KM_REQUIRE(batch && x1 && x2 && rhs && params && start && end && out, KM_ERR_INVALID_ARGUMENT, "%s: null argument", name);
     KM_REQUIRE(m >= 0 && n >= 0 && k >= 0 && n <= 0x7fffffffLL && m <= 0x7fffffffLL * 64, KM_ERR_INVALID_ARGUMENT,
@@ -629,8 +630,10 @@ static int matmul_entry(const char *name, int kernel_type, const km_batch *batch
             t.comp_begin = 0;
             t.comp_count = 0;
             const int variant = sum_tc_variant();
-            const int rc = variant == 1 ? launch_matmul_sum_tc(t, s)
-                                        : (variant == 2 ? launch_matmul_sum_tc2(t, s) : launch_matmul_sum_tc3(t, s));
+            const int rc = phases != nullptr
+                               ? launch_matmul_sum_ph(t, phases, phases_bytes, s)
+                               : (variant == 1 ? launch_matmul_sum_tc(t, s)
+                                               : (variant == 2 ? launch_matmul_sum_tc2(t, s) : launch_matmul_sum_tc3(t, s)));
             if (rc != KM_OK) return rc;
             a.sum_tc_launched = 1;
         }
@@ -664,4 +667,41 @@ extern "C" int km_matmul_rows_f32(int kernel_type, const km_batch *batch, int64_
                                   int32_t sum_batches, void *stream) {
     return km::matmul_entry("km_matmul_rows_f32", kernel_type, batch, m, n, k, x1, x2, rhs, params, start, end, out,
                             row_block_begin, row_block_count, sum_batches != 0, stream);
+}
+
+extern "C" size_t km_sum_phases_workspace_bytes(const km_batch *batch, int64_t m, int64_t n) {
+    km::Batch b;
+    if (batch == nullptr || m < 0 || n < 0 || km::make_batch(batch, &b) != KM_OK) return 0;
+    return km::sum_phases_workspace_bytes(b.count, m, n);
+}
+
+extern "C" int km_sum_phases_prepare_f32(const km_batch *batch, int64_t m, int64_t n, const km_view *x1, const km_view *x2,
+                                         const km_view *params, void *workspace, size_t workspace_bytes, void *stream) {
+    KM_REQUIRE(batch && x1 && x2 && params, KM_ERR_INVALID_ARGUMENT, "km_sum_phases_prepare_f32: null argument");
+    KM_REQUIRE(m >= 0 && n >= 0 && n <= 0x7fffffffLL && m <= 0x7fffffffLL * 64, KM_ERR_INVALID_ARGUMENT,
+               "km_sum_phases_prepare_f32: bad sizes m=%lld n=%lld", (long long)m, (long long)n);
+    km::Batch b;
+    const int rc = km::make_batch(batch, &b);
+    if (rc != KM_OK) return rc;
+    KM_REQUIRE(b.count >= 1 && b.count <= km::SUM_TC_MAX_TOTAL, KM_ERR_UNSUPPORTED,
+               "km_sum_phases_prepare_f32: 1 .. %d components, got %lld", km::SUM_TC_MAX_TOTAL, (long long)b.count);
+    if (m == 0 && n == 0) return KM_OK;
+    KM_REQUIRE(params->data && (m == 0 || x1->data) && (n == 0 || x2->data), KM_ERR_INVALID_ARGUMENT,
+               "km_sum_phases_prepare_f32: null data pointer");
+    const km::View<const float> v1 = km::make_view<const float>(x1, b), v2 = km::make_view<const float>(x2, b);
+    for (int d = 0; d < b.ndim; d++)
+        KM_REQUIRE(b.size[d] <= 1 || (v1.bs[d] == 0 && v2.bs[d] == 0), KM_ERR_UNSUPPORTED,
+                   "km_sum_phases_prepare_f32: x1 and x2 must be shared by all components (batch stride 0)");
+    return km::sum_phases_prepare(b, km::make_view<const float>(params, b), v1, v2, m, n, workspace, workspace_bytes,
+                                  static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int km_matmul_rows_phases_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,
+                                         const km_view *x1, const km_view *x2, const km_view *rhs,
+                                         const km_view *params, const km_view *start, const km_view *end,
+                                         const km_view *out, int64_t row_block_begin, int64_t row_block_count,
+                                         const void *phases, size_t phases_bytes, void *stream) {
+    KM_REQUIRE(phases != nullptr, KM_ERR_WORKSPACE, "km_matmul_rows_phases_f32: null workspace");
+    return km::matmul_entry("km_matmul_rows_phases_f32", kernel_type, batch, m, n, k, x1, x2, rhs, params, start, end, out,
+                            row_block_begin, row_block_count, true, stream, phases, phases_bytes);
 }

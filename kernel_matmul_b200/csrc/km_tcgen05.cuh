@@ -313,6 +313,9 @@ struct SumTcArgs {
     View<float> out;            // (rows_in_window, k)
     int64_t comp_begin, comp_count;  // components of one launch (set by the launcher)
     unsigned wait_polls;        // poll limit of every hand-off wait
+    // precomputed phase images of one chunk of components (km_matmul_sum_ph.cu only)
+    const unsigned char *psi_img = nullptr;
+    const uint32_t *phi_img = nullptr;
 };
 constexpr int SUM_TC_MAX_COMPONENTS = 64;    // per launch; more are processed in chunks
 constexpr int SUM_TC_MAX_TOTAL = 1024;       // (the FMA-pipe kernel's shared-envelope table holds this many)
@@ -325,6 +328,13 @@ int launch_matmul_sum_tc2(const SumTcArgs &a, cudaStream_t stream);
 // The first form with two row blocks per CTA (km_matmul_sum_tc3.cu): a thread owns a row of each,
 // so the rhs values, the psi tile and the x2 values it brings in serve twice the entries.
 int launch_matmul_sum_tc3(const SumTcArgs &a, cudaStream_t stream);
+// The first form with the phase vectors precomputed once per operator (km_matmul_sum_ph.cu): the
+// pre-pass, the size of its workspace and the product that reads it.
+size_t sum_phases_workspace_bytes(int64_t components, int64_t m, int64_t n);
+int sum_phases_prepare(const Batch &batch, const View<const float> &params, const View<const float> &x1,
+                       const View<const float> &x2, int64_t m, int64_t n, void *workspace, size_t workspace_bytes,
+                       cudaStream_t stream);
+int launch_matmul_sum_ph(const SumTcArgs &a, const void *workspace, size_t workspace_bytes, cudaStream_t stream);
 // Which one runs: 1, 2 or 3, from the environment variable KM_SUM_TC_VARIANT (read at every launch; a
 // comparison hook).
 int sum_tc_variant();

@@ -282,16 +282,52 @@ def tc_status(out: Tensor) -> int:
     return 0
 
 
+def prepare_sum_phases(kernel_type: str, x1: Tensor, x2: Tensor, params: Tensor) -> Tensor | None:
+    """Phase images for the batch sum of spectral components (``km_sum_phases_prepare_f32``): the
+    per-point vectors ``(cos, sin)(2 pi f_b x)`` of all rows and columns, written once per operator
+    in the layouts the tensor-core kernel takes them.  Pass the returned workspace to
+    ``matmul_rows(..., sum_batches=True, phases=...)``: products with the same ``x1``, ``x2`` and
+    ``params`` (frequencies and output scales; one common lengthscale) then copy the vectors instead
+    of evaluating them again for every row block.  ``None`` where it does not apply (another kernel
+    type, fewer than 2 or more than 1024 components); ``x1`` / ``x2`` of shape ``(m,)`` / ``(n,)``."""
+    if kernel_type != "spectral" or params.dim() < 2:
+        return None
+    batch = tuple(params.shape[:-1])
+    comps = 1
+    for b in batch:
+        comps *= int(b)
+    if comps < 2 or comps > 1024 or len(batch) > KM_MAX_BATCH_DIMS:
+        return None
+    if x1.dim() != 1 or x2.dim() != 1:
+        raise RuntimeError("prepare_sum_phases takes the shared inputs x1 (m,) and x2 (n,)")
+    if params.shape[-1] != NUM_PARAMS[kernel_type]:
+        raise RuntimeError(f"params must have {NUM_PARAMS[kernel_type]} entries in the last dim")
+    for t in (x1, x2, params):
+        _check_f32(t)
+    dev = _same_device(x1, x2, params)
+    m, n = x1.shape[0], x2.shape[0]
+    x1e, x2e = x1.expand(*batch, m), x2.expand(*batch, n)
+    kb = _km_batch(batch)
+    nbytes = int(lib.km_sum_phases_workspace_bytes(kb, m, n))
+    raw = torch.empty(max(nbytes, 256) + 256, dtype=torch.uint8, device=dev)
+    ws = raw[(-raw.data_ptr()) % 256:][:max(nbytes, 256)]
+    with torch.cuda.device(dev):
+        _check(lib.km_sum_phases_prepare_f32(kb, m, n, _view(x1e, 1), _view(x2e, 1), _view(params, 1),
+                                             ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream(dev)))
+    return ws
+
+
 def matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor, start: Tensor, end: Tensor,
                 *, row_block_begin: int = 0, row_block_count: int | None = None, sum_batches: bool = False,
-                out: Tensor | None = None, path: str = "auto") -> Tensor:
+                out: Tensor | None = None, path: str = "auto", phases: Tensor | None = None) -> Tensor:
     """``matmul`` restricted to the row blocks ``[row_block_begin, row_block_begin + row_block_count)``
     and, with ``sum_batches``, summed over all batch dims inside the kernel.
 
     Returns ``(*batch, rows, k)`` or, with ``sum_batches``, ``(rows, k)``, where ``rows`` is the
     number of rows of ``x1`` inside the window.  ``out`` may be passed to receive the result
     (e.g. a rank's slice of an all-gather buffer).  ``path`` as in ``matmul`` (the batch sum runs
-    on the FMA pipe).
+    on the FMA pipe).  ``phases``: the workspace of ``prepare_sum_phases`` for this operator (batch
+    sum only).
     """
     kid, dev, batch, m, n, (x1e, x2e, pe, se, ee, re) = _prep(kernel_type, x1, x2, params, start, end, [(rhs, 2)])
     if rhs.shape[-2] != n:
@@ -331,10 +367,16 @@ def matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: T
         out._km_tensor_cores = True
         return out
     with torch.cuda.device(dev):
-        _check(lib.km_matmul_rows_f32(
-            kid, _km_batch(batch), m, n, k, _view(x1e, 1), _view(x2e, 1), _view(re, 2), _view(pe, 1),
-            _view(se, 1), _view(ee, 1), _view(oute, 2), row_block_begin, row_block_count,
-            1 if sum_batches else 0, _stream(dev)))
+        if phases is not None and sum_batches:
+            _check(lib.km_matmul_rows_phases_f32(
+                kid, _km_batch(batch), m, n, k, _view(x1e, 1), _view(x2e, 1), _view(re, 2), _view(pe, 1),
+                _view(se, 1), _view(ee, 1), _view(oute, 2), row_block_begin, row_block_count,
+                ctypes.c_void_p(phases.data_ptr()), phases.numel(), _stream(dev)))
+        else:
+            _check(lib.km_matmul_rows_f32(
+                kid, _km_batch(batch), m, n, k, _view(x1e, 1), _view(x2e, 1), _view(re, 2), _view(pe, 1),
+                _view(se, 1), _view(ee, 1), _view(oute, 2), row_block_begin, row_block_count,
+                1 if sum_batches else 0, _stream(dev)))
     return out
 
 
@@ -347,18 +389,20 @@ class PreparedRowsProduct:
     pipe) can be prepared; ``prepare_matmul_rows`` returns ``None`` where ``matmul_rows`` would
     take the tensor-core kernel with its workspace."""
 
-    def __init__(self, dev, args, keep):
+    def __init__(self, dev, args, keep, fn=None):
         self._dev, self._args, self._keep = dev, args, keep
+        self._fn = fn if fn is not None else lib.km_matmul_rows_f32
         self._state = _state(dev)
 
     def __call__(self) -> None:
         self._state.poll(wait=False)
         with torch.cuda.device(self._dev):
-            _check(lib.km_matmul_rows_f32(*self._args, _stream(self._dev)))
+            _check(self._fn(*self._args, _stream(self._dev)))
 
 
 def prepare_matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, params: Tensor, start: Tensor, end: Tensor,
-                        *, row_block_begin: int, row_block_count: int, sum_batches: bool, out: Tensor):
+                        *, row_block_begin: int, row_block_count: int, sum_batches: bool, out: Tensor,
+                        phases: Tensor | None = None):
     """A ``PreparedRowsProduct`` that computes what ``matmul_rows(..., out=out)`` computes, or ``None``
     (see there).  The tensors must stay alive and in place; their contents may change between calls."""
     kid, dev, batch, m, n, (x1e, x2e, pe, se, ee, re) = _prep(kernel_type, x1, x2, params, start, end, [(rhs, 2)])
@@ -380,6 +424,9 @@ def prepare_matmul_rows(kernel_type: str, x1: Tensor, x2: Tensor, rhs: Tensor, p
         return None  # matmul_rows would run the tensor-core kernel, which needs a workspace per call
     kb = _km_batch(batch)
     views = [_view(x1e, 1), _view(x2e, 1), _view(re, 2), _view(pe, 1), _view(se, 1), _view(ee, 1), _view(out, 2)]
+    if phases is not None and sum_batches:
+        args = (kid, kb, m, n, k, *views, row_block_begin, row_block_count, ctypes.c_void_p(phases.data_ptr()), phases.numel())
+        return PreparedRowsProduct(dev, args, (x1e, x2e, re, pe, se, ee, out, kb, views, phases), lib.km_matmul_rows_phases_f32)
     args = (kid, kb, m, n, k, *views, row_block_begin, row_block_count, 1 if sum_batches else 0)
     return PreparedRowsProduct(dev, args, (x1e, x2e, re, pe, se, ee, out, kb, views))
 

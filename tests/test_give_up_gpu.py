@@ -112,11 +112,17 @@ def test_batch_sum_that_gives_up_writes_nan_and_the_solver_notices(short_waits):
     out = ops.matmul_rows(*args, sum_batches=True)
     torch.cuda.synchronize()
     assert bool(torch.isnan(out).all())
+    # the form with precomputed phase vectors (bulk copies in flight when its waits run out)
+    ws = ops.prepare_sum_phases("spectral", x, x, params)
+    out = ops.matmul_rows(*args, sum_batches=True, phases=ws)
+    torch.cuda.synchronize()
+    assert bool(torch.isnan(out).all())
     solver = CGSolver(ShardedOperator.from_kernel("spectral", x, params, start, end, 0.1), rhs)
     solver.step()
     with pytest.raises(RuntimeError, match="non-finite residual"):
         solver.check_finite()
     assert lib.km_selftest_set_wait_polls(-1) == 0
     out = ops.matmul_rows(*args, sum_batches=True)
+    out_ph = ops.matmul_rows(*args, sum_batches=True, phases=ws)
     torch.cuda.synchronize()
-    assert bool(torch.isfinite(out).all())
+    assert bool(torch.isfinite(out).all()) and bool(torch.isfinite(out_ph).all())

@@ -189,6 +189,49 @@ def sum_kernel_variant(request, monkeypatch):
 
 
 @pytest.mark.parametrize("B,k", [(2, 1), (7, 8), (64, 8), (33, 11), (64, 16), (100, 8), (130, 3)])
+def test_batch_sum_with_precomputed_phases(B, k):
+    """The same sum with the per-point phase vectors written once per operator
+    (km_matmul_sum_ph.cu: ``ops.prepare_sum_phases`` + ``matmul_rows(..., phases=...)``) against the
+    fp64 oracle: large input offsets (the phases are taken at the points themselves, in fp64),
+    row windows bit-identical to the full product, reuse of the workspace for several right-hand
+    sides, and the fallback for different lengthscales."""
+    from kernel_matmul_b200 import ops
+    from oracle import oracle as O
+
+    n = 1400  # ragged last row block
+    x = torch.sort(torch.rand(n) * 300 + 50000)[0]
+    params = torch.stack([torch.full((B,), 1.3), torch.rand(B) * 1.5, (torch.rand(B) + 0.5) / B], dim=-1)
+    params[0, 1] = 0.0
+    start, end = O.make_ranges(5.0, x)
+    d = lambda t: t.cuda()  # noqa: E731
+    xd, pd = d(x), d(params)
+    ws = ops.prepare_sum_phases("spectral", xd, xd, pd)
+    assert ws is not None and ws.data_ptr() % 256 == 0
+    for trial in range(2):  # one workspace, several right-hand sides
+        rhs = torch.randn(n, k)
+        ref = O.matmul("spectral", x.expand(B, n), x.expand(B, n), rhs.expand(B, n, k), params, start.expand(B, -1),
+                       end.expand(B, -1)).sum(0)
+        args = ("spectral", xd.expand(B, n), xd.expand(B, n), d(rhs).expand(B, n, k), pd, d(start).expand(B, -1),
+                d(end).expand(B, -1))
+        out = ops.matmul_rows(*args, sum_batches=True, phases=ws)
+        assert out.shape == (n, k) and bool(torch.isfinite(out).all())
+        assert rel_err(out, ref) <= 1e-5
+        win = ops.matmul_rows(*args, sum_batches=True, row_block_begin=3, row_block_count=5, phases=ws)
+        assert torch.equal(win, out[384:1024])
+    # different lengthscales: the FMA-pipe kernel computes the sum (the tensor-core CTAs leave at once)
+    params2 = params.clone()
+    params2[-1, 0] = 1.1
+    ref2 = O.matmul("spectral", x.expand(B, n), x.expand(B, n), rhs.expand(B, n, k), params2, start.expand(B, -1),
+                    end.expand(B, -1)).sum(0)
+    out2 = ops.matmul_rows(args[0], args[1], args[2], args[3], d(params2), args[5], args[6], sum_batches=True, phases=ws)
+    assert rel_err(out2, ref2) <= 1e-5
+    ops.check()
+    # other kernels and single components have no phase workspace
+    assert ops.prepare_sum_phases("rbf", xd, xd, torch.rand(B, 2).cuda()) is None
+    assert ops.prepare_sum_phases("spectral", xd, xd, pd[0]) is None
+
+
+@pytest.mark.parametrize("B,k", [(2, 1), (7, 8), (64, 8), (33, 11), (64, 16), (100, 8), (130, 3)])
 def test_batch_sum_on_tensor_cores(B, k, sum_kernel_variant):
     """Spectral components with one lengthscale: the batch sum as a tensor-core dot product of
     per-point phase vectors (km_matmul_sum_tc.cu) against the fp64 oracle, incl. row windows."""
