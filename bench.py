@@ -21,7 +21,9 @@ Printed keys (one JSON line, rank 0):
              ``kernel_matmul_b200.host.cg_solve_from_host`` with HOST (pinned) buffers: every rank
              copies x, params and its rows of Y to the device, builds the band, iterates, and copies
              its rows of the solution back;
-  roofline   the dominant kernel (``matmul_sum_tc_kernel``) against the measured dense bf16 rate
+  roofline   the dominant kernel (``matmul_sum_ph_kernel``: the batch sum with the operator's phase
+             vectors written once per solve by a pre-pass; ``KM_SUM_PHASES=0`` selects
+             ``matmul_sum_tc_kernel``, which evaluates them in every product) against the measured dense bf16 rate
              (its three fp16 MMAs per 16 phase values are what bounds it), its time taken with CUDA
              events around the product inside the timed iterations;
   cpu_baseline  the dense PyTorch formulation (materialise every K_b, mask by ranges, matmul, sum)
@@ -773,26 +775,30 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
         peaks = measured_peaks()
         ms_per_step = total_ms / args.steps
         # All components share inputs, band and lengthscale, so the batch sum runs on the tensor
-        # cores (matmul_sum_tc_kernel): sum_b s_b cos(w_b tau) = <phi(x_i), psi(x_j)> with 2B-vectors
-        # of per-point phases.  Per UNIQUE (row, column) entry: three fp16 MMAs of 2B multiply-adds,
-        # one envelope exponential + 2B / 128 SFU operations for the column's phase vector (shared by
-        # the 128 rows of the block), and k + ~6 FP32 operations.  Row windows are equal, so a rank's
-        # launch does 1 / N of it.
+        # cores: sum_b s_b cos(w_b tau) = <phi(x_i), psi(x_j)> with 2B-vectors of per-point phases
+        # (matmul_sum_ph_kernel copies them from images a pre-pass wrote once per operator;
+        # matmul_sum_tc_kernel evaluates psi itself: 2B / 128 more SFU operations per entry).  Per
+        # UNIQUE (row, column) entry: three fp16 MMAs of 2B multiply-adds, one envelope exponential
+        # and k + ~6 FP32 operations.  Row windows are equal, so a rank's launch does 1 / N of it.
         e_unique = E / B / world
         t_prod = product_ms * 1e-3
         tensor_flops = e_unique * 3 * 2 * (2 * B)
         f16_peak = peaks.get("bf16_tflops", 1590.0)
-        traffic = dram_traffic("cg_sum", "matmul_sum_tc_kernel") if args.workload == "cg_sum" else None
+        phase_ws = getattr(op, "phase_workspace", None)
+        kernel_name = "matmul_sum_ph_kernel" if phase_ws is not None else "matmul_sum_tc_kernel"
+        traffic = dram_traffic("cg_sum", kernel_name) if args.workload == "cg_sum" else None
         roofline = {
-            "bound": "tensor", "kernel": "matmul_sum_tc_kernel", "achieved": tensor_flops / t_prod / 1e12, "peak": f16_peak,
+            "bound": "tensor", "kernel": kernel_name, "achieved": tensor_flops / t_prod / 1e12, "peak": f16_peak,
             "unit": "TFLOP/s", "frac": tensor_flops / t_prod / 1e12 / f16_peak,
             "traffic": traffic / world if traffic else None,
             "traffic_source": "profiles/dram_traffic.json: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of "
-                              "the full single-GPU launch (profiles/matmul_sum_tc_kernel_cg_sum.md), copied by hand; divided "
+                              f"the full single-GPU launch (profiles/{kernel_name}_cg_sum.md), copied by hand; divided "
                               "by the number of ranks (traffic grows with the rows of a launch)",
             "product_ms": product_ms, "algorithmic_tensor_flops_per_launch": tensor_flops,
             "frac_of_sustained_bf16": tensor_flops / t_prod / 1e12 / peaks.get("bf16_tflops_sustained", 1400.0),
-            "frac_sfu": e_unique * (1 + 2 * B / 128) / t_prod / 1e12 / sfu_peak,
+            # SFU operations per unique entry: the envelope, plus (without precomputed phase vectors) the
+            # column's phase vector shared by the 128 rows of the block
+            "frac_sfu": e_unique * (1 + (0 if phase_ws is not None else 2 * B / 128)) / t_prod / 1e12 / sfu_peak,
             "frac_fp32": 2.0 * e_unique * (k + 6) / t_prod / 1e12 / fp32_peak,
             "fp32_peak_tflops": fp32_peak, "sfu_peak_tops": sfu_peak,
             "peak_source": ("MEASURED_PEAKS.json bf16_tflops (burst; kind::f16 MMAs run at the bf16 rate)" if peaks else
@@ -808,6 +814,9 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
             "config": config_of(w, E),
             "exchange": op.mode,
+            "phase_vectors": ("written once per operator by a pre-pass (%.2f GB workspace per rank; inside the end-to-end "
+                              "figure, outside the timed iterations)" % (phase_ws.numel() / 1e9)) if phase_ws is not None
+                             else "evaluated inside every product (KM_SUM_PHASES=0)",
             "collective": {"single": "none (one rank)",
                            "halo": f"2 NCCL all_gather_into_tensor per iteration: [{op.halo_above} + {op.halo_below} halo rows "
                                    f"of q + segment sums of p.q] and [segment sums of r.r]",

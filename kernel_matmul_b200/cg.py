@@ -267,8 +267,10 @@ class ShardedOperator:
         else:
             mine = torch.stack([torch.zeros((), dtype=torch.int64, device=start.device)] * 2 + [checksum])
         lo, hi, checksum = (int(v) for v in mine.tolist())
-        return cls(n, sigma2, matvec_rows, group=group, device=x.device, col_range=(lo, hi) if count > 0 else (0, 0),
-                   band_checksum=checksum, mode=mode)
+        op = cls(n, sigma2, matvec_rows, group=group, device=x.device, col_range=(lo, hi) if count > 0 else (0, 0),
+                 band_checksum=checksum, mode=mode)
+        op.phase_workspace = phase_ws  # (None: the products evaluate the phase vectors themselves)
+        return op
 
     # ---- the operator applied to a full vector (tests, diagnostics)
 

@@ -160,11 +160,19 @@ int sum_phases_prepare(const Batch &batch, const View<const float> &params, cons
 // (tensor-memory lanes) and alternate tiles, each with its own C stage and partial sums (added at
 // the end); a control warp fetches the inputs of the tiles (x2 values and rhs rows by cp.async, the
 // psi image by one bulk copy) and issues the MMAs.
-template <int KB>
+//
+// MS (KB = 8): the contraction with the rhs tile on the warp-level tensor path (mma.sync m16n8k8,
+// 3xTF32) instead of the FMA pipe, as in km_matmul_sum_tc.cu: a thread reads C in the register
+// layout of an m16n8 accumulator, multiplies by the envelope and uses the products as the A
+// fragment; per 128 entries a warp issues three MMAs and reads 8 bytes of rhs per thread, where the
+// FMA form issues 16 packed FMAs and reads 128 bytes.
+template <int KB, bool MS>
 __global__ void __launch_bounds__(288, 2) matmul_sum_ph_kernel(const SumTcArgs a) {
+    static_assert(!MS || KB == 8, "the warp-level contraction is written for 8 rhs columns");
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_in[PH_IN_STAGES];     // x2 + rhs tile landed
     __shared__ __align__(8) uint64_t bar_psi[PH_PSI_STAGES];   // psi image landed
+    __shared__ __align__(8) uint64_t bar_pfree[PH_PSI_STAGES]; // psi image read by its MMAs (tcgen05.commit)
     __shared__ __align__(8) uint64_t bar_cfull[2];             // C tile complete (tcgen05.commit)
     __shared__ __align__(8) uint64_t bar_cfree[2];             // C tile consumed
     __shared__ __align__(8) uint64_t bar_drain;                // give-up path: every issued MMA has completed
@@ -196,7 +204,10 @@ __global__ void __launch_bounds__(288, 2) matmul_sum_ph_kernel(const SumTcArgs a
     const int b_part_bytes = (2 * Bp / 8) * PH_COLS * 16;
     const int b_stage_bytes = 2 * b_part_bytes;
     unsigned char *in_base = smem_raw + PH_PSI_STAGES * b_stage_bytes;
-    constexpr int IN_STAGE_FLOATS = PH_COLS + PH_COLS * KB;  // x2 values, then rhs rows
+    // rhs rows lie in shared memory as pairs of band columns: rs[((jj / 2) * RS + c) * 2 + (jj & 1)];
+    // RS = 12 spreads the warp-level form's reads over the banks
+    constexpr int RS = MS ? 12 : KB;
+    constexpr int IN_STAGE_FLOATS = PH_COLS + PH_COLS * RS;  // x2 values, then rhs rows
     auto b_stage = [&](int st) { return smem_raw + st * b_stage_bytes; };
     auto in_x2 = [&](int st) { return reinterpret_cast<float *>(in_base) + st * IN_STAGE_FLOATS; };
     auto in_rhs = [&](int st) { return reinterpret_cast<float *>(in_base) + st * IN_STAGE_FLOATS + PH_COLS; };
@@ -214,7 +225,10 @@ __global__ void __launch_bounds__(288, 2) matmul_sum_ph_kernel(const SumTcArgs a
 #pragma unroll
         for (int s = 0; s < PH_IN_STAGES; s++) mbar_init(&bar_in[s], 32);  // one cp.async arrival per lane
 #pragma unroll
-        for (int s = 0; s < PH_PSI_STAGES; s++) mbar_init(&bar_psi[s], 1);  // the expect_tx arrival
+        for (int s = 0; s < PH_PSI_STAGES; s++) {
+            mbar_init(&bar_psi[s], 1);  // the expect_tx arrival
+            mbar_init(&bar_pfree[s], 1);
+        }
 #pragma unroll
         for (int s = 0; s < 2; s++) {
             mbar_init(&bar_cfull[s], 1);
@@ -233,6 +247,9 @@ __global__ void __launch_bounds__(288, 2) matmul_sum_ph_kernel(const SumTcArgs a
     f32x2 acc2[KB];  // per output column: (sum over even band columns, sum over odd band columns)
 #pragma unroll
     for (int c = 0; c < KB; c++) acc2[c] = 0ull;
+    // warp-level form: accumulator fragments of the warp's two 16-row tiles (thread lane: rows
+    // lane / 4 and lane / 4 + 8 of a tile, output columns 2 (lane % 4) and 2 (lane % 4) + 1)
+    float dacc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
 
     if (is_ctl_warp) {
         // --------------------------------------------- input fetches (all lanes) + MMA issue (lane 0)
@@ -247,11 +264,11 @@ __global__ void __launch_bounds__(288, 2) matmul_sum_ph_kernel(const SumTcArgs a
                 const bool valid = j0 + jj < n;
                 cp_async4_zfill(xs + jj, x2 + (valid ? j0 + jj : 0) * a.x2.s0, valid);
             }
-            // rhs rows in pairs: rs[((jj / 2) * KB + c) * 2 + (jj & 1)] = rhs[j0 + jj][c]
+            // rhs rows in pairs: rs[((jj / 2) * RS + c) * 2 + (jj & 1)] = rhs[j0 + jj][c]
             for (int q = lane; q < PH_COLS * KB; q += 32) {
                 const int jj = q / KB, c = q % KB;
                 const bool valid = j0 + jj < n && c < a.k;
-                cp_async4_zfill(rs + (((jj >> 1) * KB + c) << 1) + (jj & 1),
+                cp_async4_zfill(rs + (((jj >> 1) * RS + c) << 1) + (jj & 1),
                                 rhs + (valid ? (j0 + jj) * a.rhs.s0 + c * a.rhs.s1 : 0), valid);
             }
             cp_async_mbar_arrive(&bar_in[st]);
@@ -265,7 +282,9 @@ __global__ void __launch_bounds__(288, 2) matmul_sum_ph_kernel(const SumTcArgs a
                 bulk_copy_g2s(b_stage(ps), a.psi_img + (int64_t)(tile_lo + t) * b_stage_bytes, (unsigned)b_stage_bytes, &bar_psi[ps]);
             }
         };
-        if (tiles > 0) fetch_psi(0);
+        // psi images are fetched two tiles ahead (three stages): tile t + 2 as soon as the MMAs of tile
+        // t - 1, which read the same stage, have completed
+        for (int t = 0; t < min(tiles, 2); t++) fetch_psi(t);
         for (int t = 0; t < min(tiles, PH_IN_STAGES); t++) fetch_inputs(t);
 
         // D fp32, A / B fp16, K-major, M = 128, N = 64
@@ -282,12 +301,10 @@ __global__ void __launch_bounds__(288, 2) matmul_sum_ph_kernel(const SumTcArgs a
             const int st = t & 1, ps = t % PH_PSI_STAGES;
             bool ok = true;
             if (t >= 2) {
-                // C stage free = tile t - 2 consumed: its MMAs are complete, so its input stage and its
-                // psi stage (that of tile t + 1) can be filled again
+                // C stage free = tile t - 2 consumed, which also frees its input stage
                 ok = mbar_wait(&bar_cfree[st], (unsigned)(((t >> 1) - 1) & 1), a.wait_polls);
                 if (__all_sync(0xffffffffu, ok) && t + 2 < tiles) fetch_inputs(t + 2);
             }
-            if (__all_sync(0xffffffffu, ok) && t + 1 < tiles) fetch_psi(t + 1);
             if (ok) ok = mbar_wait(&bar_psi[ps], (unsigned)((t / PH_PSI_STAGES) & 1), a.wait_polls);
             if (!__all_sync(0xffffffffu, ok)) {
                 failed = true;
@@ -323,8 +340,18 @@ __global__ void __launch_bounds__(288, 2) matmul_sum_ph_kernel(const SumTcArgs a
                     default: issue(std::integral_constant<int, 8>{}); break;
                 }
                 mma_commit(&bar_cfull[st]);
+                mma_commit(&bar_pfree[ps]);
             }
             __syncwarp();
+            if (t + 2 < tiles) {
+                // the stage of tile t + 2 is that of tile t - 1, whose MMAs were issued an iteration ago
+                if (t >= 1 && !__all_sync(0xffffffffu, mbar_wait(&bar_pfree[(t - 1) % PH_PSI_STAGES],
+                                                                  (unsigned)(((t - 1) / PH_PSI_STAGES) & 1), a.wait_polls))) {
+                    failed = true;
+                    break;
+                }
+                fetch_psi(t + 2);
+            }
         }
         if (failed) {
             // give-up path: the bulk copies that were issued and not yet seen complete are awaited (with
@@ -364,6 +391,15 @@ __global__ void __launch_bounds__(288, 2) matmul_sum_ph_kernel(const SumTcArgs a
         asm volatile("bar.sync 1, 288;" ::: "memory");
 
         const f32x2 x1v2 = splat2(x1v), c02 = splat2(c0);
+        // warp-level form: x1 of this thread's four rows 32 (warp % 4) + 16 mt + lane / 4 + 8 hh, as pairs
+        f32x2 xi2[2][2];
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+            for (int hh = 0; hh < 2; hh++) {
+                const int64_t ri = r * KM_BLOCK_SIZE + (warp & 3) * 32 + 16 * mt + (lane >> 2) + 8 * hh;
+                xi2[mt][hh] = splat2((MS && ri < a.m) ? a.x1.data[ri * a.x1.s0] : 0.0f);
+            }
         for (int t = g; t < tiles && !failed; t += 2) {
             const int st = t & 1;
             if (!mbar_wait_warp(&bar_in[t % PH_IN_STAGES], (unsigned)((t / PH_IN_STAGES) & 1), a.wait_polls) ||
@@ -414,10 +450,65 @@ __global__ void __launch_bounds__(288, 2) matmul_sum_ph_kernel(const SumTcArgs a
                     if (p + 1 < PH_COLS / 16) tmem_ld_wait16(cbuf[(p + 1) & 1]);
                 }
             };
-            if (j0 < band_lo || j0 + PH_COLS > band_hi)
-                consume(std::true_type{});
-            else
-                consume(std::false_type{});
+            auto consume_ms = [&](auto masked_tag) {
+                constexpr bool MASKED = decltype(masked_tag)::value;
+                const int gq = lane >> 2, tq = lane & 3;
+                constexpr f32x2 HI2 = 0xffffe000ffffe000ull;  // the tf32 part of both values of a pair
+                const uint32_t c_tile = tmem_lane + (uint32_t)(PH_C_COL + st * PH_COLS);
+                // the loads of the next 8 columns are in flight while these are processed
+                uint32_t cv[2][2][4];  // [buffer][16-row tile][fragment]
+                tmem_ld_m16n8_nowait(c_tile, cv[0][0]);
+                tmem_ld_m16n8_nowait(c_tile + (16u << 16), cv[0][1]);
+                tmem_ld_wait4x2(cv[0][0], cv[0][1]);
+#pragma unroll
+                for (int cb = 0; cb < PH_COLS / 8; cb++) {
+                    if (cb + 1 < PH_COLS / 8) {
+                        tmem_ld_m16n8_nowait(c_tile + (uint32_t)((cb + 1) * 8), cv[(cb + 1) & 1][0]);
+                        tmem_ld_m16n8_nowait(c_tile + (16u << 16) + (uint32_t)((cb + 1) * 8), cv[(cb + 1) & 1][1]);
+                    }
+                    const int jj = cb * 8 + 2 * tq;  // this thread's band columns jj, jj + 1 of the tile
+                    const f32x2 xj2 = *reinterpret_cast<const f32x2 *>(xs + jj);
+                    // B fragment: rhs[jj][gq], rhs[jj + 1][gq], split into tf32 hi and lo
+                    const f32x2 b2 = *reinterpret_cast<const f32x2 *>(rs + ((((jj >> 1) * RS) + gq) << 1));
+                    const f32x2 bh2 = b2 & HI2, bl2 = sub2(b2, bh2);
+                    const uint32_t bh0 = (uint32_t)bh2, bh1 = (uint32_t)(bh2 >> 32), bl0 = (uint32_t)bl2, bl1 = (uint32_t)(bl2 >> 32);
+#pragma unroll
+                    for (int mt = 0; mt < 2; mt++) {
+                        const uint32_t(&c4)[4] = cv[cb & 1][mt];
+                        f32x2 wh[2], wl[2];
+#pragma unroll
+                        for (int hh = 0; hh < 2; hh++) {
+                            const f32x2 tau2 = sub2(xi2[mt][hh], xj2);
+                            const f32x2 e2 = ex2_approx2(mul2(mul2(tau2, tau2), c02));
+                            uint32_t ca = c4[2 * hh], cbv = c4[2 * hh + 1];
+                            if (MASKED) {
+                                if (j0 + jj < band_lo || j0 + jj >= band_hi) ca = 0u;
+                                if (j0 + jj + 1 < band_lo || j0 + jj + 1 >= band_hi) cbv = 0u;
+                            }
+                            const f32x2 w2 = mul2((f32x2)ca | ((f32x2)cbv << 32), e2);
+                            wh[hh] = w2 & HI2;
+                            wl[hh] = sub2(w2, wh[hh]);
+                        }
+                        // A fragment: (row, k) = (hh, band column parity): a0 = (0, 0), a1 = (1, 0), a2 = (0, 1), a3 = (1, 1)
+                        mma_sync_tf32(dacc[mt], (uint32_t)wl[0], (uint32_t)wl[1], (uint32_t)(wl[0] >> 32), (uint32_t)(wl[1] >> 32), bh0, bh1);
+                        mma_sync_tf32(dacc[mt], (uint32_t)wh[0], (uint32_t)wh[1], (uint32_t)(wh[0] >> 32), (uint32_t)(wh[1] >> 32), bl0, bl1);
+                        mma_sync_tf32(dacc[mt], (uint32_t)wh[0], (uint32_t)wh[1], (uint32_t)(wh[0] >> 32), (uint32_t)(wh[1] >> 32), bh0, bh1);
+                    }
+                    if (cb + 1 < PH_COLS / 8) tmem_ld_wait4x2(cv[(cb + 1) & 1][0], cv[(cb + 1) & 1][1]);
+                }
+            };
+            const bool edge = j0 < band_lo || j0 + PH_COLS > band_hi;
+            if constexpr (MS) {
+                if (edge)
+                    consume_ms(std::true_type{});
+                else
+                    consume_ms(std::false_type{});
+            } else {
+                if (edge)
+                    consume(std::true_type{});
+                else
+                    consume(std::false_type{});
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bar_cfree[st]);
@@ -434,7 +525,27 @@ __global__ void __launch_bounds__(288, 2) matmul_sum_ph_kernel(const SumTcArgs a
         unpack2(acc2[c], even, odd);
         acc[c] = even + odd;
     }
-    {
+    if constexpr (MS) {
+        // both groups' accumulator fragments go through shared memory (the pipelines are done) into
+        // row-per-thread order; group 0 adds the two
+        float *xch = reinterpret_cast<float *>(smem_raw);
+        if (!is_ctl_warp) {
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                for (int hh = 0; hh < 2; hh++)
+#pragma unroll
+                    for (int e = 0; e < 2; e++) {
+                        const int row_in_block = (warp & 3) * 32 + 16 * mt + (lane >> 2) + 8 * hh, c = 2 * (lane & 3) + e;
+                        xch[(g * KB + c) * 128 + row_in_block] = dacc[mt][2 * hh + e];
+                    }
+        }
+        __syncthreads();
+        if (!is_ctl_warp && g == 0) {
+#pragma unroll
+            for (int c = 0; c < KB; c++) acc[c] = xch[c * 128 + row_local] + xch[(KB + c) * 128 + row_local];
+        }
+    } else {
         // the second group hands its partial sums over through shared memory (the pipelines are done)
         float *xch = reinterpret_cast<float *>(smem_raw);
         if (!is_ctl_warp && g == 1) {
@@ -475,19 +586,26 @@ __global__ void __launch_bounds__(288, 2) matmul_sum_ph_kernel(const SumTcArgs a
     }
 }
 
-template <int KB>
+template <int KB, bool MS>
 static int launch_sum_ph_kb(const SumTcArgs &a, cudaStream_t stream) {
     const int Bp = ((int)a.comp_count + 7) & ~7;
     const size_t b_stage = (size_t)Bp * 512;
-    size_t smem = PH_PSI_STAGES * b_stage + (size_t)PH_IN_STAGES * (PH_COLS + PH_COLS * KB) * sizeof(float);
+    size_t smem = PH_PSI_STAGES * b_stage + (size_t)PH_IN_STAGES * (PH_COLS + PH_COLS * (MS ? 12 : KB)) * sizeof(float);
     // two CTAs of 256 tensor-memory columns fill an SM: keep a third from being scheduled
     smem = std::max<size_t>(smem, 80 * 1024);
-    auto kernel = matmul_sum_ph_kernel<KB>;
+    auto kernel = matmul_sum_ph_kernel<KB, MS>;
     cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return cuda_fail(err, "cudaFuncSetAttribute(matmul_sum_ph)");
     kernel<<<(unsigned)a.row_blocks, 288, smem, stream>>>(a);
     KM_CHECK_LAUNCH("km_matmul_rows_phases_f32 (tensor-core batch sum, precomputed phases) launch");
     return KM_OK;
+}
+
+// Contraction with the rhs tile (k <= 8): on the FMA pipe, or on the warp-level tensor path when the
+// environment variable KM_SUM_TC_WARP_MMA is 1 (read at every launch).
+static bool sum_ph_warp_mma() {
+    const char *e = getenv("KM_SUM_TC_WARP_MMA");
+    return e != nullptr && e[0] == '1';
 }
 
 int launch_matmul_sum_ph(const SumTcArgs &a, const void *workspace, size_t workspace_bytes, cudaStream_t stream) {
@@ -511,7 +629,8 @@ int launch_matmul_sum_ph(const SumTcArgs &a, const void *workspace, size_t works
         chunk.comp_count = chunk_comps(a.batch.count, c);
         chunk.psi_img = ws + L.psi_off[c];
         chunk.phi_img = reinterpret_cast<const uint32_t *>(ws + L.phi_off[c]);
-        const int rc = a.k <= 8 ? launch_sum_ph_kb<8>(chunk, stream) : launch_sum_ph_kb<16>(chunk, stream);
+        const int rc = a.k <= 8 ? (sum_ph_warp_mma() ? launch_sum_ph_kb<8, true>(chunk, stream) : launch_sum_ph_kb<8, false>(chunk, stream))
+                                : launch_sum_ph_kb<16, false>(chunk, stream);
         if (rc != KM_OK) return rc;
     }
     return KM_OK;

@@ -188,8 +188,9 @@ def sum_kernel_variant(request, monkeypatch):
     return request.param
 
 
+@pytest.mark.parametrize("contraction", ["FMA pipe", "warp-level tensor path"])
 @pytest.mark.parametrize("B,k", [(2, 1), (7, 8), (64, 8), (33, 11), (64, 16), (100, 8), (130, 3)])
-def test_batch_sum_with_precomputed_phases(B, k):
+def test_batch_sum_with_precomputed_phases(B, k, contraction, monkeypatch):
     """The same sum with the per-point phase vectors written once per operator
     (km_matmul_sum_ph.cu: ``ops.prepare_sum_phases`` + ``matmul_rows(..., phases=...)``) against the
     fp64 oracle: large input offsets (the phases are taken at the points themselves, in fp64),
@@ -198,6 +199,7 @@ def test_batch_sum_with_precomputed_phases(B, k):
     from kernel_matmul_b200 import ops
     from oracle import oracle as O
 
+    monkeypatch.setenv("KM_SUM_TC_WARP_MMA", "1" if contraction.startswith("warp") else "0")
     n = 1400  # ragged last row block
     x = torch.sort(torch.rand(n) * 300 + 50000)[0]
     params = torch.stack([torch.full((B,), 1.3), torch.rand(B) * 1.5, (torch.rand(B) + 0.5) / B], dim=-1)
