@@ -173,9 +173,13 @@ KM_API int km_matmul_rows_f32(int kernel_type, const km_batch *batch, int64_t m,
  * ------------------------------------------------------------------------------------- */
 KM_API size_t km_sum_phases_workspace_bytes(const km_batch *batch, int64_t m, int64_t n);
 
+/* Only the rows [row_begin, row_end) and the columns [col_begin, col_end) (widened to whole tiles of
+ * 64) are written -- what a rank of a row-sharded solve reads: its own rows and the columns of
+ * their bands; row_end / col_end < 0 mean m / n.  The workspace has the full size either way. */
 KM_API int km_sum_phases_prepare_f32(const km_batch *batch, int64_t m, int64_t n, const km_view *x1,
-                                     const km_view *x2, const km_view *params, void *workspace,
-                                     size_t workspace_bytes, void *stream);
+                                     const km_view *x2, const km_view *params, int64_t row_begin,
+                                     int64_t row_end, int64_t col_begin, int64_t col_end,
+                                     void *workspace, size_t workspace_bytes, void *stream);
 
 KM_API int km_matmul_rows_phases_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n,
                                      int64_t k, const km_view *x1, const km_view *x2,

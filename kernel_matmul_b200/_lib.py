@@ -56,7 +56,7 @@ def _load() -> ctypes.CDLL:
     lib.km_sum_phases_workspace_bytes.restype = sz
     lib.km_sum_phases_workspace_bytes.argtypes = [bp, i64, i64]
     lib.km_sum_phases_prepare_f32.restype = ctypes.c_int
-    lib.km_sum_phases_prepare_f32.argtypes = [bp, i64, i64, wp, wp, wp, vp, sz, vp]
+    lib.km_sum_phases_prepare_f32.argtypes = [bp, i64, i64, wp, wp, wp, i64, i64, i64, i64, vp, sz, vp]
     lib.km_matmul_rows_phases_f32.restype = ctypes.c_int
     lib.km_matmul_rows_phases_f32.argtypes = [ctypes.c_int, bp, i64, i64, i64, wp, wp, wp, wp, wp, wp, wp, i64, i64, vp, sz, vp]
     lib.km_matmul_tc_workspace_bytes.restype = sz

@@ -231,7 +231,7 @@ class ShardedOperator:
 
         if phases is None:
             phases = os.environ.get("KM_SUM_PHASES", "1") != "0"
-        phase_ws = ops.prepare_sum_phases(kernel_type, x, x, params) if (phases and batched) else None
+        phase_ws = None  # set below, once this rank's rows and columns are known
         prepared: dict = {}  # (buffers, window) -> launch with all arguments already marshalled
 
         def matvec_rows(v: Tensor, rb_begin: int, rb_count: int, out: Tensor) -> None:
@@ -240,12 +240,14 @@ class ShardedOperator:
             call = prepared.get(key)
             if call is None:
                 rhs = v.expand(*B, *v.shape) if batched else v
+                # (the phase images cover this rank's own row blocks only)
+                ws = phase_ws if (rb_begin >= begin and rb_begin + rb_count <= begin + count) else None
                 call = ops.prepare_matmul_rows(kernel_type, xb, xb, rhs, params, sb, eb, row_block_begin=rb_begin,
-                                               row_block_count=rb_count, sum_batches=batched, out=out, phases=phase_ws)
+                                               row_block_count=rb_count, sum_batches=batched, out=out, phases=ws)
                 if call is None:  # (a product that needs a workspace: the unprepared call)
-                    def call(rhs=rhs, out=out):
+                    def call(rhs=rhs, out=out, ws=ws):
                         ops.matmul_rows(kernel_type, xb, xb, rhs, params, sb, eb, row_block_begin=rb_begin,
-                                        row_block_count=rb_count, sum_batches=batched, out=out, phases=phase_ws)
+                                        row_block_count=rb_count, sum_batches=batched, out=out, phases=ws)
                 if len(prepared) >= 8:
                     prepared.clear()
                 prepared[key] = call
@@ -267,6 +269,9 @@ class ShardedOperator:
         else:
             mine = torch.stack([torch.zeros((), dtype=torch.int64, device=start.device)] * 2 + [checksum])
         lo, hi, checksum = (int(v) for v in mine.tolist())
+        if phases and batched and count > 0:
+            phase_ws = ops.prepare_sum_phases(kernel_type, x, x, params, rows=(begin * BLOCK_SIZE, min(n, (begin + count) * BLOCK_SIZE)),
+                                              cols=(max(0, min(lo, n)), max(0, min(hi, n))))
         op = cls(n, sigma2, matvec_rows, group=group, device=x.device, col_range=(lo, hi) if count > 0 else (0, 0),
                  band_checksum=checksum, mode=mode)
         op.phase_workspace = phase_ws  # (None: the products evaluate the phase vectors themselves)

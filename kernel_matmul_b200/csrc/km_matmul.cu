@@ -676,7 +676,13 @@ extern "C" size_t km_sum_phases_workspace_bytes(const km_batch *batch, int64_t m
 }
 
 extern "C" int km_sum_phases_prepare_f32(const km_batch *batch, int64_t m, int64_t n, const km_view *x1, const km_view *x2,
-                                         const km_view *params, void *workspace, size_t workspace_bytes, void *stream) {
+                                         const km_view *params, int64_t row_begin, int64_t row_end, int64_t col_begin,
+                                         int64_t col_end, void *workspace, size_t workspace_bytes, void *stream) {
+    if (row_end < 0) row_end = m;
+    if (col_end < 0) col_end = n;
+    KM_REQUIRE(0 <= row_begin && row_begin <= row_end && row_end <= m && 0 <= col_begin && col_begin <= col_end && col_end <= n,
+               KM_ERR_INVALID_ARGUMENT, "km_sum_phases_prepare_f32: rows [%lld, %lld) of %lld, columns [%lld, %lld) of %lld",
+               (long long)row_begin, (long long)row_end, (long long)m, (long long)col_begin, (long long)col_end, (long long)n);
     KM_REQUIRE(batch && x1 && x2 && params, KM_ERR_INVALID_ARGUMENT, "km_sum_phases_prepare_f32: null argument");
     KM_REQUIRE(m >= 0 && n >= 0 && n <= 0x7fffffffLL && m <= 0x7fffffffLL * 64, KM_ERR_INVALID_ARGUMENT,
                "km_sum_phases_prepare_f32: bad sizes m=%lld n=%lld", (long long)m, (long long)n);
@@ -692,8 +698,8 @@ extern "C" int km_sum_phases_prepare_f32(const km_batch *batch, int64_t m, int64
     for (int d = 0; d < b.ndim; d++)
         KM_REQUIRE(b.size[d] <= 1 || (v1.bs[d] == 0 && v2.bs[d] == 0), KM_ERR_UNSUPPORTED,
                    "km_sum_phases_prepare_f32: x1 and x2 must be shared by all components (batch stride 0)");
-    return km::sum_phases_prepare(b, km::make_view<const float>(params, b), v1, v2, m, n, workspace, workspace_bytes,
-                                  static_cast<cudaStream_t>(stream));
+    return km::sum_phases_prepare(b, km::make_view<const float>(params, b), v1, v2, m, n, row_begin, row_end, col_begin, col_end,
+                                  workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int km_matmul_rows_phases_f32(int kernel_type, const km_batch *batch, int64_t m, int64_t n, int64_t k,

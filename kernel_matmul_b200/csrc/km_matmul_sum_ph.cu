@@ -72,20 +72,22 @@ __device__ __forceinline__ void split_half(float v, unsigned short &hi, unsigned
     lo = __half_as_ushort(__float2half_rn(v - tf32_hi(v)));
 }
 
-// One thread per (chunk-of-4-components, column) of the psi images and per (k-step, row) of the phi images.
+// One thread per (chunk-of-4-components, column) of the psi images and per (k-step, row) of the phi
+// images; only the tiles [tile_begin, tile_end) and the rows [row_begin, row_end) are written.
 __global__ void __launch_bounds__(256) sum_phase_images_kernel(Batch batch, View<const float> params, View<const float> x1,
                                                                 View<const float> x2, int64_t m, int64_t n, int64_t comp_begin,
-                                                                int B, unsigned char *psi_img, uint32_t *phi_img) {
+                                                                int B, unsigned char *psi_img, uint32_t *phi_img,
+                                                                int64_t tile_begin, int64_t tile_end, int64_t row_begin,
+                                                                int64_t row_end) {
     const int Bp = (B + 7) & ~7;
-    const int64_t tiles = (n + PH_COLS - 1) / PH_COLS;
-    const int64_t psi_items = tiles * PH_COLS * (Bp / 4), phi_items = m * (Bp / 8);
+    const int64_t psi_items = (tile_end - tile_begin) * PH_COLS * (Bp / 4), phi_items = (row_end - row_begin) * (Bp / 8);
     const int64_t part_bytes = (int64_t)(2 * Bp / 8) * PH_COLS * 16, stage_bytes = 2 * part_bytes;
     for (int64_t it = blockIdx.x * 256LL + threadIdx.x; it < psi_items + phi_items; it += (int64_t)gridDim.x * 256) {
         if (it < psi_items) {
             const int jj = (int)(it % PH_COLS);
             const int64_t rest = it / PH_COLS;
             const int kc = (int)(rest % (Bp / 4));
-            const int64_t tile = rest / (Bp / 4);
+            const int64_t tile = tile_begin + rest / (Bp / 4);
             const int64_t j = tile * PH_COLS + jj;
             unsigned short h[8], l[8];
 #pragma unroll
@@ -109,7 +111,7 @@ __global__ void __launch_bounds__(256) sum_phase_images_kernel(Batch batch, View
         } else {
             const int64_t pit = it - psi_items;
             const int ks = (int)(pit % (Bp / 8));
-            const int64_t row = pit / (Bp / 8);
+            const int64_t row = row_begin + pit / (Bp / 8);
             uint32_t w[16];
 #pragma unroll
             for (int u = 0; u < 8; u++) {
@@ -137,9 +139,10 @@ __global__ void __launch_bounds__(256) sum_phase_images_kernel(Batch batch, View
 }
 
 int sum_phases_prepare(const Batch &batch, const View<const float> &params, const View<const float> &x1,
-                       const View<const float> &x2, int64_t m, int64_t n, void *workspace, size_t workspace_bytes,
-                       cudaStream_t stream) {
+                       const View<const float> &x2, int64_t m, int64_t n, int64_t row_begin, int64_t row_end,
+                       int64_t col_begin, int64_t col_end, void *workspace, size_t workspace_bytes, cudaStream_t stream) {
     const PhasesLayout L = phases_layout(batch.count, m, n);
+    const int64_t tile_begin = col_begin / PH_COLS, tile_end = ceil_div(col_end, (int64_t)PH_COLS);
     if (workspace == nullptr || workspace_bytes < (size_t)L.bytes || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0) {
         set_error("km_sum_phases_prepare_f32: workspace of %lld bytes, 256-byte aligned, needed", (long long)L.bytes);
         return KM_ERR_WORKSPACE;
@@ -147,10 +150,12 @@ int sum_phases_prepare(const Batch &batch, const View<const float> &params, cons
     unsigned char *ws = static_cast<unsigned char *>(workspace);
     for (int64_t c = 0; c < L.chunks; c++) {
         const int B = chunk_comps(batch.count, c), Bp = (B + 7) & ~7;
-        const int64_t items = L.tiles * PH_COLS * (Bp / 4) + m * (Bp / 8);
+        const int64_t items = (tile_end - tile_begin) * PH_COLS * (Bp / 4) + (row_end - row_begin) * (Bp / 8);
+        if (items <= 0) continue;
         const unsigned grid = (unsigned)std::min<int64_t>(ceil_div(items, (int64_t)256), 148 * 64);
         sum_phase_images_kernel<<<grid, 256, 0, stream>>>(batch, params, x1, x2, m, n, c * SUM_TC_MAX_COMPONENTS, B, ws + L.psi_off[c],
-                                                           reinterpret_cast<uint32_t *>(ws + L.phi_off[c]));
+                                                           reinterpret_cast<uint32_t *>(ws + L.phi_off[c]), tile_begin, tile_end,
+                                                           row_begin, row_end);
         KM_CHECK_LAUNCH("km_sum_phases_prepare_f32 launch");
     }
     return KM_OK;

@@ -332,8 +332,8 @@ int launch_matmul_sum_tc3(const SumTcArgs &a, cudaStream_t stream);
 // pre-pass, the size of its workspace and the product that reads it.
 size_t sum_phases_workspace_bytes(int64_t components, int64_t m, int64_t n);
 int sum_phases_prepare(const Batch &batch, const View<const float> &params, const View<const float> &x1,
-                       const View<const float> &x2, int64_t m, int64_t n, void *workspace, size_t workspace_bytes,
-                       cudaStream_t stream);
+                       const View<const float> &x2, int64_t m, int64_t n, int64_t row_begin, int64_t row_end,
+                       int64_t col_begin, int64_t col_end, void *workspace, size_t workspace_bytes, cudaStream_t stream);
 int launch_matmul_sum_ph(const SumTcArgs &a, const void *workspace, size_t workspace_bytes, cudaStream_t stream);
 // Which one runs: 1, 2 or 3, from the environment variable KM_SUM_TC_VARIANT (read at every launch; a
 // comparison hook).

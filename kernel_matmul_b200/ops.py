@@ -282,14 +282,17 @@ def tc_status(out: Tensor) -> int:
     return 0
 
 
-def prepare_sum_phases(kernel_type: str, x1: Tensor, x2: Tensor, params: Tensor) -> Tensor | None:
+def prepare_sum_phases(kernel_type: str, x1: Tensor, x2: Tensor, params: Tensor, *, rows: tuple[int, int] | None = None,
+                       cols: tuple[int, int] | None = None) -> Tensor | None:
     """Phase images for the batch sum of spectral components (``km_sum_phases_prepare_f32``): the
     per-point vectors ``(cos, sin)(2 pi f_b x)`` of all rows and columns, written once per operator
     in the layouts the tensor-core kernel takes them.  Pass the returned workspace to
     ``matmul_rows(..., sum_batches=True, phases=...)``: products with the same ``x1``, ``x2`` and
     ``params`` (frequencies and output scales; one common lengthscale) then copy the vectors instead
     of evaluating them again for every row block.  ``None`` where it does not apply (another kernel
-    type, fewer than 2 or more than 1024 components); ``x1`` / ``x2`` of shape ``(m,)`` / ``(n,)``."""
+    type, fewer than 2 or more than 1024 components); ``x1`` / ``x2`` of shape ``(m,)`` / ``(n,)``.
+    ``rows`` / ``cols``: write only these rows and columns (what the products of one rank of a
+    row-sharded solve read: its own rows and the columns of their bands)."""
     if kernel_type != "spectral" or params.dim() < 2:
         return None
     batch = tuple(params.shape[:-1])
@@ -312,7 +315,9 @@ def prepare_sum_phases(kernel_type: str, x1: Tensor, x2: Tensor, params: Tensor)
     raw = torch.empty(max(nbytes, 256) + 256, dtype=torch.uint8, device=dev)
     ws = raw[(-raw.data_ptr()) % 256:][:max(nbytes, 256)]
     with torch.cuda.device(dev):
-        _check(lib.km_sum_phases_prepare_f32(kb, m, n, _view(x1e, 1), _view(x2e, 1), _view(params, 1),
+        r0, r1 = rows if rows is not None else (0, m)
+        c0, c1 = cols if cols is not None else (0, n)
+        _check(lib.km_sum_phases_prepare_f32(kb, m, n, _view(x1e, 1), _view(x2e, 1), _view(params, 1), r0, r1, c0, c1,
                                              ctypes.c_void_p(ws.data_ptr()), ws.numel(), _stream(dev)))
     return ws
 

@@ -220,6 +220,10 @@ def test_batch_sum_with_precomputed_phases(B, k, contraction, monkeypatch):
         assert rel_err(out, ref) <= 1e-5
         win = ops.matmul_rows(*args, sum_batches=True, row_block_begin=3, row_block_count=5, phases=ws)
         assert torch.equal(win, out[384:1024])
+    # images written for one window's rows and columns only (a rank of a row-sharded solve)
+    ws_part = ops.prepare_sum_phases("spectral", xd, xd, pd, rows=(384, 1024), cols=(int(start[3:8].min()), int(end[3:8].max())))
+    win = ops.matmul_rows(*args, sum_batches=True, row_block_begin=3, row_block_count=5, phases=ws_part)
+    assert torch.equal(win, out[384:1024])
     # different lengthscales: the FMA-pipe kernel computes the sum (the tensor-core CTAs leave at once)
     params2 = params.clone()
     params2[-1, 0] = 1.1
