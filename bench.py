@@ -749,15 +749,19 @@ def run_cg(args, rank: int, world: int, local: int) -> None:
         if world > 1:
             dist.barrier()
         e2e_runs = []
-        e2e_solver = None
         for _ in range(2):
             box = []
             e2e_runs.append(cuda_ms(lambda: box.append(solve_e2e()[0])))
-            e2e_solver = box[0]
+            # (a solve's buffers -- 4.3 GB of phase images among them -- are released before the next
+            # one starts, as a caller's would be: with the previous solver still alive the second
+            # solve sometimes spent 100-300 ms in the allocator)
+            e2e_solver = box.pop()
+            e2e_solver.check_finite()
+            e2e_residual = float(e2e_solver.residual_norms()[-1].max())
+            del e2e_solver
+        trace("end-to-end solves (ms): " + " ".join(f"{v:.1f}" for v in e2e_runs))
         e2e_ms = statistics.mean(e2e_runs)
-        e2e_solver.check_finite()
-        e2e_residual = float(e2e_solver.residual_norms()[-1].max())
-        del e2e_solver, box
+        del box
     trace("end-to-end solves done")
     h2d = (hx.numel() + hp.numel() + (op.hi - op.lo) * k) * 4
     d2h = op.rows * k * 4
