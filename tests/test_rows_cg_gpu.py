@@ -188,6 +188,45 @@ def sum_kernel_variant(request, monkeypatch):
     return request.param
 
 
+def test_phase_entry_points_validate_their_arguments():
+    """The C entry points of the phase workspace refuse what they cannot do, with a message and
+    without launching anything."""
+    import ctypes
+
+    from kernel_matmul_b200 import ops
+    from kernel_matmul_b200._lib import lib
+
+    B, n = 4, 300
+    x = torch.sort(torch.rand(n) * 30)[0].cuda()
+    params = torch.stack([torch.full((B,), 1.3), torch.rand(B), torch.full((B,), 0.25)], dim=-1).cuda()
+    kb = ops._km_batch((B,))
+    xe = x.expand(B, n)
+    need = lib.km_sum_phases_workspace_bytes(kb, n, n)
+    assert need == -(-n // 64) * 8 * 512 + -(-(n * 8 * 8) // 256) * 256  # psi tiles of 8 padded components, phi rows
+    ws = torch.empty(need + 256, dtype=torch.uint8, device="cuda")
+    ws = ws[(-ws.data_ptr()) % 256:]
+    args = (kb, n, n, ops._view(xe, 1), ops._view(xe, 1), ops._view(params, 1))
+    # too small, misaligned, null
+    assert lib.km_sum_phases_prepare_f32(*args, 0, -1, 0, -1, ctypes.c_void_p(ws.data_ptr()), need - 1, None) == 3
+    assert b"workspace" in lib.km_last_error()
+    assert lib.km_sum_phases_prepare_f32(*args, 0, -1, 0, -1, ctypes.c_void_p(ws.data_ptr() + 16), need, None) == 3
+    assert lib.km_sum_phases_prepare_f32(*args, 0, -1, 0, -1, None, need, None) == 3
+    # ranges outside the operator
+    assert lib.km_sum_phases_prepare_f32(*args, 0, n + 1, 0, -1, ctypes.c_void_p(ws.data_ptr()), need, None) == 1
+    assert lib.km_sum_phases_prepare_f32(*args, 10, 5, 0, -1, ctypes.c_void_p(ws.data_ptr()), need, None) == 1
+    assert b"rows" in lib.km_last_error()
+    # inputs that differ between the components
+    xb = torch.rand(B, n).cuda()
+    assert lib.km_sum_phases_prepare_f32(kb, n, n, ops._view(xb, 1), ops._view(xe, 1), ops._view(params, 1), 0, -1, 0, -1,
+                                         ctypes.c_void_p(ws.data_ptr()), need, None) == 2
+    assert b"shared by all components" in lib.km_last_error()
+    # more components than the sum kernel takes: no workspace size
+    assert lib.km_sum_phases_workspace_bytes(ops._km_batch((2000,)), n, n) == 0
+    # a good call
+    assert lib.km_sum_phases_prepare_f32(*args, 0, -1, 0, -1, ctypes.c_void_p(ws.data_ptr()), need, None) == 0
+    torch.cuda.synchronize()
+
+
 @pytest.mark.parametrize("contraction", ["FMA pipe", "warp-level tensor path"])
 @pytest.mark.parametrize("B,k", [(2, 1), (7, 8), (64, 8), (33, 11), (64, 16), (100, 8), (130, 3)])
 def test_batch_sum_with_precomputed_phases(B, k, contraction, monkeypatch):
