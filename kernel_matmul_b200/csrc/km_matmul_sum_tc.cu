@@ -555,8 +555,9 @@ static int sum_tc_groups() {
 
 // Contraction with the rhs tile (two row groups, k <= 8): on the FMA pipe, or on the warp-level
 // tensor path when the environment variable KM_SUM_TC_WARP_MMA is 1 (read at every launch; measured
-// slower on the 64-component benchmark, 12.6 against 11.6 ms, although it issues 40 % fewer
-// instructions per entry and reads an eighth of the shared-memory bytes: a comparison hook).
+// slower on the 64-component benchmark, 12.6 against 11.6 ms: it reads an eighth of the
+// shared-memory bytes, but issues as many instructions, and mma.sync shares the tensor pipe with
+// tcgen05.mma: a comparison hook).
 static bool sum_tc_warp_mma() {
     const char *e = getenv("KM_SUM_TC_WARP_MMA");
     return e != nullptr && e[0] == '1';
