@@ -105,9 +105,9 @@ __global__ void __launch_bounds__(256) sum_phase_images_kernel(Batch batch, View
                 split_half(s, h[2 * u + 1], l[2 * u + 1]);
             }
             unsigned char *dst = psi_img + tile * stage_bytes + (int64_t)kc * (PH_COLS * 16) + jj * 16;
-            *reinterpret_cast<uint4 *>(dst) = make_uint4(h[0] | (h[1] << 16), h[2] | (h[3] << 16), h[4] | (h[5] << 16), h[6] | (h[7] << 16));
-            *reinterpret_cast<uint4 *>(dst + part_bytes) =
-                make_uint4(l[0] | (l[1] << 16), l[2] | (l[3] << 16), l[4] | (l[5] << 16), l[6] | (l[7] << 16));
+            auto word = [](unsigned short lo16, unsigned short hi16) { return (uint32_t)lo16 | ((uint32_t)hi16 << 16); };
+            *reinterpret_cast<uint4 *>(dst) = make_uint4(word(h[0], h[1]), word(h[2], h[3]), word(h[4], h[5]), word(h[6], h[7]));
+            *reinterpret_cast<uint4 *>(dst + part_bytes) = make_uint4(word(l[0], l[1]), word(l[2], l[3]), word(l[4], l[5]), word(l[6], l[7]));
         } else {
             const int64_t pit = it - psi_items;
             const int ks = (int)(pit % (Bp / 8));
